@@ -1,0 +1,5 @@
+"""``neuron`` namespace: spiking neuron modules."""
+from .base_node import *  # noqa: F401,F403
+from .integrate_and_fire import *  # noqa: F401,F403
+from .lif import *  # noqa: F401,F403
+from .nonlinear_if import *  # noqa: F401,F403

@@ -1,0 +1,50 @@
+// Surrogate derivative table.  Ids match SURROGATES in activation_based/surrogate.py.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace sjb200 {
+
+enum SurrogateId : int {
+    SG_SIGMOID = 0, SG_ATAN = 1, SG_PIECEWISE_QUADRATIC = 2, SG_PIECEWISE_EXP = 3, SG_SOFT_SIGN = 4,
+    SG_SUPER_SPIKE = 5, SG_ERF = 6, SG_NONZERO_SIGN_LOG_ABS = 7, SG_PIECEWISE_LEAKY_RELU = 8,
+    SG_SQUAREWAVE = 9, SG_S2NN = 10, SG_Q_PSEUDO_SPIKE = 11, SG_LEAKY_K_RELU = 12,
+    SG_FAKE_NUMERICAL = 13, SG_LOG_TAILED_RELU = 14, SG_DETERMINISTIC_PASS = 15, SG_RECT = 16,
+};
+
+// g'(x) for surrogate `id` with parameters (p0, p1).  `id` is uniform across the
+// grid, so the switch costs one predictable branch.
+__device__ __forceinline__ float surrogate_grad(int id, float x, float p0, float p1) {
+    const float PI = 3.14159265358979323846f;
+    switch (id) {
+    case SG_SIGMOID: { float s = 1.0f / (1.0f + expf(-p0 * x)); return (1.0f - s) * s * p0; }
+    case SG_ATAN: { float a = p0 * 0.5f; float ax = PI * a * x; return a / (1.0f + ax * ax); }
+    case SG_PIECEWISE_QUADRATIC: { float xa = fabsf(x); return xa > (1.0f / p0) ? 0.0f : (-(p0 * p0) * xa + p0); }
+    case SG_PIECEWISE_EXP: return p0 * 0.5f * expf(-p0 * fabsf(x));
+    case SG_SOFT_SIGN: { float d = 1.0f / p0 + fabsf(x); return 1.0f / (2.0f * p0 * d * d); }
+    case SG_SUPER_SPIKE: { float d = fabsf(x) + 1.0f; return p0 / (d * d); }
+    case SG_ERF: { float ax = x * p0; return expf(-ax * ax) * (p0 * 0.5641895835477563f); }
+    case SG_NONZERO_SIGN_LOG_ABS: return 1.0f / (1.0f / p0 + fabsf(x));
+    case SG_PIECEWISE_LEAKY_RELU: return fabsf(x) < p0 ? 1.0f / (2.0f * p0) : p1;
+    case SG_SQUAREWAVE: {
+        float w = 2.0f * PI / p1, g = 0.0f; int n = (int)p0;
+        for (int i = 1; i < n; ++i) g += cosf((2.0f * i - 1.0f) * w * x);
+        return g * (4.0f / p1);
+    }
+    case SG_S2NN: {
+        if (x < 0.0f) { float s = 1.0f / (1.0f + expf(-p0 * x)); return p0 * s * (1.0f - s); }
+        return p1 / (x + 1.0f);
+    }
+    case SG_Q_PSEUDO_SPIKE: return powf(1.0f + 2.0f / (p0 - 1.0f) * fabsf(x), -p0);
+    case SG_LEAKY_K_RELU: return x >= 0.0f ? p1 : p0;
+    case SG_FAKE_NUMERICAL: return fminf((x >= 0.0f ? 1.0f : -1.0f) / x, p0);
+    case SG_LOG_TAILED_RELU: return x <= 0.0f ? p0 : (x > 1.0f ? 1.0f / x : 1.0f);
+    case SG_DETERMINISTIC_PASS: return 1.0f;
+    case SG_RECT: return fabsf(x) < 0.5f / p0 ? p0 : 0.0f;
+    default: return 0.0f;
+    }
+}
+
+template <int ID>
+__device__ __forceinline__ float surrogate_grad(float x, float p0, float p1) { return surrogate_grad(ID, x, p0, p1); }
+
+}  // namespace sjb200
