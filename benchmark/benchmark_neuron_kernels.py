@@ -1,0 +1,125 @@
+#!/usr/bin/env python
+"""Neuron-kernel sweep: multi-step IF / LIF / PLIF forward+backward on one GPU.
+
+For every (neuron, reset, dtype, T, N) it times forward+backward of
+  * ours:      spikingjelly_b200 native kernels (backend="cuda")
+  * reference: the unmodified reference's torch and triton backends (from baseline/_ref),
+and reports microseconds, achieved GB/s against the algorithmic traffic of OUR kernels
+(read x, write spikes; read x, read grad, write grad_x) and the speed-up over the
+reference's fastest backend.  Inputs x ~ N(0.5, 1), upstream gradients ~ N(0, 1); each
+timed iteration follows an L2 flush; CUDA-event timing after warm-up.
+
+    python benchmark/benchmark_neuron_kernels.py --out gpurun_out/neuron_sweep.json
+"""
+import argparse
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+
+
+def time_fn(fn, flush, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2] * 1e3  # us
+
+
+def make(ns, kind, soft, backend):
+    kw = dict(v_reset=None if soft else 0.0, surrogate_function=ns.surrogate.ATan(), step_mode="m", backend=backend)
+    if kind == "if":
+        return ns.neuron.IFNode(**kw)
+    if kind == "lif":
+        return ns.neuron.LIFNode(tau=2.0, decay_input=True, **kw)
+    if kind == "lif_ndi":
+        return ns.neuron.LIFNode(tau=2.0, decay_input=False, **kw)
+    return ns.neuron.ParametricLIFNode(init_tau=2.0, **kw)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", default="")
+    ap.add_argument("--T", default="4,8,16,32")
+    ap.add_argument("--logN", default="16,20,24")
+    ap.add_argument("--dtypes", default="fp32,bf16")
+    ap.add_argument("--neurons", default="if,lif,lif_ndi,plif")
+    ap.add_argument("--no-reference", action="store_true")
+    ap.add_argument("--ref-backends", default="torch,triton")
+    args = ap.parse_args()
+    dev = torch.device("cuda")
+    from spikingjelly_b200.activation_based import functional, neuron, surrogate
+
+    class Ours:
+        pass
+    Ours.neuron, Ours.surrogate, Ours.functional = neuron, surrogate, functional
+    Ref = None
+    if not args.no_reference:
+        try:
+            sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
+            from spikingjelly.activation_based import functional as rf, neuron as rn, surrogate as rs
+
+            class Ref:
+                pass
+            Ref.neuron, Ref.surrogate, Ref.functional = rn, rs, rf
+        except Exception as exc:
+            print("reference unavailable:", exc, file=sys.stderr)
+    dts = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+    for kind in args.neurons.split(","):
+        for soft in (False, True):
+            for dname in args.dtypes.split(","):
+                dt = dts[dname]
+                for T in map(int, args.T.split(",")):
+                    for logn in map(int, args.logN.split(",")):
+                        N = 1 << logn
+                        x = (torch.randn(T, N, device=dev) + 0.5).to(dt).requires_grad_(True)
+                        g = torch.randn(T, N, device=dev).to(dt)
+
+                        def run(net, ns):
+                            def f():
+                                x.grad = None
+                                net(x).backward(g)
+                                ns.functional.reset_net(net)
+                            return f
+                        row = {"neuron": kind, "soft_reset": soft, "dtype": dname, "T": T, "N": N}
+                        net = make(Ours, kind, soft, "cuda").to(dev)
+                        row["ours_us"] = round(time_fn(run(net, Ours), flush), 2)
+                        bytes_moved = 5 * T * N * x.element_size()
+                        row["ours_GBps"] = round(bytes_moved / row["ours_us"] / 1e3, 1)
+                        if Ref is not None:
+                            for be in args.ref_backends.split(","):
+                                if be == "torch" and T * N > (1 << 27):
+                                    continue
+                                try:
+                                    rnet = make(Ref, kind, soft, be).to(dev)
+                                    row[f"ref_{be}_us"] = round(time_fn(run(rnet, Ref), flush, iters=5, warmup=2), 2)
+                                except Exception as exc:
+                                    row[f"ref_{be}_err"] = f"{type(exc).__name__}: {exc}"[:120]
+                            best = min([row[k] for k in row if k.startswith("ref_") and k.endswith("_us")], default=None)
+                            if best:
+                                row["speedup_vs_best_ref"] = round(best / row["ours_us"], 2)
+                        print(json.dumps(row), flush=True)
+                        rows.append(row)
+                        del x, g
+    if args.out:
+        Path(args.out).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.out).write_text(json.dumps(rows, indent=1))
+
+
+if __name__ == "__main__":
+    main()

@@ -12,7 +12,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from . import require
+from . import counters, require
 
 __all__ = ["NeuronSpec", "multistep_neuron", "KIND"]
 
@@ -37,10 +37,10 @@ class NeuronSpec:
 
 class _Scan(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x_seq, v_init, r, spec: NeuronSpec, v_init_scalar: float, store_v_seq: bool, pack_bits: bool):
-        need_grad = torch.is_grad_enabled() and (
-            x_seq.requires_grad or (v_init is not None and v_init.requires_grad) or (r is not None and r.requires_grad))
+    def forward(ctx, x_seq, v_init, r, spec: NeuronSpec, v_init_scalar: float, store_v_seq: bool, pack_bits: bool,
+                need_grad: bool):
         vr = 0.0 if spec.soft else float(spec.v_reset)
+        counters.bump("scan_forward")
         spike, v_last, v_seq, packed, ckpt = torch.ops.sjb200.scan_forward(
             x_seq, v_init, v_init_scalar, r, spec.kind, spec.tau, spec.q[0], spec.q[1], spec.q[2],
             spec.v_threshold, vr, spec.soft, store_v_seq, pack_bits, need_grad)
@@ -62,13 +62,14 @@ class _Scan(torch.autograd.Function):
         if g_spike is None:
             g_spike = torch.zeros_like(x_seq)
         need_gvi = ctx.has_v_init and ctx.needs_input_grad[1]
+        counters.bump("scan_backward")
         gx, gvi, gr = torch.ops.sjb200.scan_backward(
             g_spike, g_v_last, g_v_seq if ctx.store_v_seq else None, x_seq,
             v_init if ctx.has_v_init else None, ctx.v_init_scalar, r if ctx.has_r else None,
             ckpt if ckpt.numel() > 0 else None, spec.kind, spec.tau, spec.q[0], spec.q[1], spec.q[2],
             spec.v_threshold, vr, spec.soft, spec.sg[0], spec.sg[1], spec.sg[2], spec.detach_reset, need_gvi)
         g_r = gr.reshape(r.shape).to(r.dtype) if (ctx.has_r and ctx.needs_input_grad[2]) else None
-        return gx, (gvi if need_gvi else None), g_r, None, None, None, None
+        return gx, (gvi if need_gvi else None), g_r, None, None, None, None, None
 
 
 def multistep_neuron(x_seq: torch.Tensor, v_init, spec: NeuronSpec, r: Optional[torch.Tensor] = None,
@@ -84,5 +85,8 @@ def multistep_neuron(x_seq: torch.Tensor, v_init, spec: NeuronSpec, r: Optional[
         v_t, v_s = v_init, 0.0
     else:
         v_t, v_s = None, float(v_init)
-    spike, v_last, v_seq, packed = _Scan.apply(x_seq, v_t, r, spec, v_s, store_v_seq, pack_bits)
+    # grad mode is off inside Function.forward, so decide here whether backward can happen
+    need_grad = torch.is_grad_enabled() and (
+        x_seq.requires_grad or (v_t is not None and v_t.requires_grad) or (r is not None and r.requires_grad))
+    spike, v_last, v_seq, packed = _Scan.apply(x_seq, v_t, r, spec, v_s, store_v_seq, pack_bits, need_grad)
     return spike, v_last, (v_seq if store_v_seq else None), (packed if pack_bits else None)
