@@ -163,19 +163,10 @@ class Spikformer(nn.Module, base.MultiStepModule):
             x_seq = blk(x_seq)
         return x_seq.flatten(3).mean(dim=-1)
 
-    def _can_fuse(self, x) -> bool:
-        if not (self.fused and x.is_cuda):
-            return False
-        lif = self.patch_embed.stages[0].neuron
-        return lif.native
-
     def forward(self, x):
-        if self._can_fuse(x):
-            try:
-                from . import _spikformer_fused
-            except ImportError:
-                _spikformer_fused = None
-            if _spikformer_fused is not None:
+        if self.fused and x.is_cuda:
+            from . import _spikformer_fused
+            if _spikformer_fused.eligible(self, x):
                 return _spikformer_fused.forward(self, x)
         return self.head(self.forward_features(self._to_sequence(x)))
 

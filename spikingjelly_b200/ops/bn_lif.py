@@ -1,0 +1,66 @@
+"""BatchNorm + multi-step neuron as one differentiable op on channels-last activations.
+
+``bn_lif(y, bn, spec, residual=None)`` takes the pre-normalisation tensor ``y``
+``[T, ..., C]`` (e.g. a GEMM output), computes batch statistics (or uses the running ones
+when ``bn`` is in eval mode), and returns ``LIF_T(BN(y)) (+ residual)`` without ever writing
+the normalised tensor.  Backward is two kernels (BPTT + per-channel sums, then the BN
+backward in closed form)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import counters, require
+from .neuron_scan import NeuronSpec
+
+__all__ = ["bn_lif", "BNLIFFunction"]
+
+
+class BNLIFFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, gamma, beta, running_mean, running_var, residual, training: bool, momentum: float,
+                eps: float, spec: NeuronSpec, v_init: float, need_grad: bool):
+        vr = 0.0 if spec.soft else float(spec.v_reset)
+        counters.bump("bn_stats", 2 if training else 1)
+        mean, invstd, scale, shift = torch.ops.sjb200.bn_coefficients(
+            y, gamma, beta, running_mean, running_var, training, momentum, eps)
+        counters.bump("bn_lif_forward")
+        out, ckpt = torch.ops.sjb200.bn_lif_forward(y, scale, shift, residual, spec.kind, spec.tau, spec.v_threshold,
+                                                    vr, spec.soft, v_init, need_grad)
+        ctx.spec, ctx.training, ctx.v_init = spec, training, v_init
+        ctx.has_residual = residual is not None
+        ctx.has_affine = gamma is not None
+        ctx.save_for_backward(y, scale, shift, mean, invstd, gamma if gamma is not None else y.new_empty(0), ckpt)
+        ctx.mark_dirty()  # running stats are updated through the op's mutable arguments
+        return out
+
+    @staticmethod
+    def backward(ctx, g_out):
+        y, scale, shift, mean, invstd, gamma, ckpt = ctx.saved_tensors
+        spec: NeuronSpec = ctx.spec
+        vr = 0.0 if spec.soft else float(spec.v_reset)
+        counters.bump("bn_lif_backward", 3)
+        dy, g_gamma, g_beta = torch.ops.sjb200.bn_lif_backward(
+            g_out, y, scale, shift, mean, invstd, gamma if ctx.has_affine else None,
+            ckpt if ckpt.numel() > 0 else None, ctx.training, spec.kind, spec.tau, spec.v_threshold, vr, spec.soft,
+            ctx.v_init, spec.sg[0], spec.sg[1], spec.sg[2], spec.detach_reset)
+        return (dy, g_gamma if ctx.has_affine else None, g_beta if ctx.has_affine else None, None, None,
+                g_out if ctx.has_residual else None, None, None, None, None, None, None)
+
+
+def bn_lif(y: torch.Tensor, bn: torch.nn.modules.batchnorm._BatchNorm, spec: NeuronSpec,
+           residual: Optional[torch.Tensor] = None, v_init: float = 0.0) -> torch.Tensor:
+    """``y``: contiguous ``[T, ..., C]`` with ``C == bn.num_features`` (channels last)."""
+    require()
+    training = bn.training or bn.running_mean is None
+    momentum = 0.0 if bn.momentum is None else float(bn.momentum)
+    if bn.training and bn.track_running_stats and bn.num_batches_tracked is not None:
+        bn.num_batches_tracked.add_(1)
+        if bn.momentum is None:
+            momentum = 1.0 / float(bn.num_batches_tracked)
+    rm = bn.running_mean if (bn.track_running_stats and bn.training) or not training else None
+    rv = bn.running_var if (bn.track_running_stats and bn.training) or not training else None
+    need_grad = torch.is_grad_enabled() and (y.requires_grad or (bn.weight is not None and bn.weight.requires_grad))
+    return BNLIFFunction.apply(y.contiguous(), bn.weight, bn.bias, rm, rv, residual, training, momentum, float(bn.eps),
+                               spec, float(v_init), need_grad)

@@ -39,6 +39,9 @@ __device__ __forceinline__ void load_vec_stream(const T* __restrict__ p, float (
     if constexpr (sizeof(T) * V == 16) {
         int4 r = __ldcs(reinterpret_cast<const int4*>(p));
         raw = *reinterpret_cast<Pack<T, V>*>(&r);
+    } else if constexpr (sizeof(T) * V == 8) {
+        int2 r = __ldcs(reinterpret_cast<const int2*>(p));
+        raw = *reinterpret_cast<Pack<T, V>*>(&r);
     } else {
         raw = *reinterpret_cast<const Pack<T, V>*>(p);
     }
@@ -52,9 +55,32 @@ __device__ __forceinline__ void store_vec(T* __restrict__ p, const float (&in)[V
     for (int i = 0; i < V; ++i) raw.e[i] = from_f32<T>(in[i]);
     if constexpr (sizeof(T) * V == 16) {
         __stcs(reinterpret_cast<int4*>(p), *reinterpret_cast<int4*>(&raw));
+    } else if constexpr (sizeof(T) * V == 8) {
+        __stcs(reinterpret_cast<int2*>(p), *reinterpret_cast<int2*>(&raw));
     } else {
         *reinterpret_cast<Pack<T, V>*>(p) = raw;
     }
+}
+
+// raw (unconverted) vector load: keeps V elements in V*sizeof(T)/4 registers until they are needed
+template <typename T, int V>
+__device__ __forceinline__ Pack<T, V> load_raw_stream(const T* __restrict__ p) {
+    Pack<T, V> raw;
+    if constexpr (sizeof(T) * V == 16) {
+        int4 r = __ldcs(reinterpret_cast<const int4*>(p));
+        raw = *reinterpret_cast<Pack<T, V>*>(&r);
+    } else if constexpr (sizeof(T) * V == 8) {
+        int2 r = __ldcs(reinterpret_cast<const int2*>(p));
+        raw = *reinterpret_cast<Pack<T, V>*>(&r);
+    } else {
+        raw = *reinterpret_cast<const Pack<T, V>*>(p);
+    }
+    return raw;
+}
+template <typename T, int V>
+__device__ __forceinline__ void unpack(const Pack<T, V>& raw, float (&out)[V]) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) out[i] = to_f32<T>(raw.e[i]);
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

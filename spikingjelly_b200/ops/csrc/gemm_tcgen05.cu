@@ -1,0 +1,410 @@
+// Persistent, warp-specialised 16-bit GEMM on the 5th-generation tensor cores.
+//
+//   D[M, N] = sum_k A[m, k] * B[n, k]          (fp32 accumulation in TMEM)
+//
+// * one CTA per SM, static round-robin over 128 x BN output tiles (n fastest, so the
+//   CTAs that run together share the same rows of A through L2);
+// * warp 0: TMA producer (one thread) filling a STAGES-deep ring of 128B-swizzled
+//   A/B tiles; warp 1: tcgen05.mma issuer (one thread), accumulator double-buffered in
+//   TMEM (2 x BN columns) so the epilogue of tile i overlaps the main loop of tile
+//   i+1; warps 2-5: epilogue (tcgen05.ld -> convert -> global);
+// * either operand may be stored "MN-major" (memory is [K, M] or [K, N] with the
+//   non-contracted index contiguous), which is what dgrad/wgrad of a linear layer
+//   need, so no transposes are ever materialised;
+// * split-K for skinny outputs (wgrad): partial sums go to an fp32 scratch
+//   [splits, M, N]; `splitk_reduce_kernel` adds them in a fixed order;
+// * all mbarrier waits are bounded; on expiry the kernel records where it gave
+//   up in a KernelStatus word, lets in-flight copies land, frees TMEM and returns.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <torch/library.h>
+
+#include "tc_common.cuh"
+
+namespace sjb200 {
+namespace {
+
+using namespace tc;
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // 64 x 2 B = one 128 B swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;   // 6 warps: producer, mma, 4 x epilogue
+
+template <int BN, int STAGES>
+struct SmemLayout {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;   // barriers + slack for 1024 B alignment
+};
+
+struct GemmArgs {
+    int M, N, K;            // logical sizes (K = contraction)
+    int ldd;                // leading dimension of D (elements)
+    int split_k;            // >= 1
+    int kb_per_split;       // k-blocks (of BK) per split
+    int out_f32;            // D is fp32 (always when split_k > 1)
+    int ab_format;          // 0 = fp16, 1 = bf16
+};
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Dptr,
+            GemmArgs g, KernelStatus* __restrict__ status) {
+    using L = SmemLayout<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tfull_bar = empty_bar + STAGES;
+    uint64_t* tempty_bar = tfull_bar + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
+    const int tiles_mn = tiles_m * tiles_n;
+    const int total_tiles = tiles_mn * g.split_k;
+    const int kb_total = (g.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar + a, 1); mbar_init(tempty_bar + a, 4); }
+        *abort_flag = 0;
+        mbar_init_fence();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 2 * BN);
+        tmem_relinquish();
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+                const int split = tile / tiles_mn, mn = tile % tiles_mn;
+                const int m0 = (mn / tiles_n) * BM, n0 = (mn % tiles_n) * BN;
+                const int kb0 = split * g.kb_per_split;
+                const int kb1 = min(kb_total, kb0 + g.kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait_bounded(empty_bar + s, ph ^ 1)) { report(status, WAIT_EMPTY, s); *abort_flag = 1; break; }
+                    uint8_t* sa = smem + s * L::STAGE_BYTES;
+                    uint8_t* sb = sa + L::A_BYTES;
+                    mbar_expect_tx(full_bar + s, L::STAGE_BYTES);
+                    const int k0 = kb * BK;
+                    if (A_MN) {
+#pragma unroll
+                        for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmA, m0 + c * 64, k0, full_bar + s);
+                    } else {
+                        tma_load_2d(sa, &tmA, k0, m0, full_bar + s);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), &tmB, n0 + c * 64, k0, full_bar + s);
+                    } else {
+                        tma_load_2d(sb, &tmB, k0, n0, full_bar + s);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_f16(g.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
+            uint32_t it = 0, tl = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tl) {
+                const int split = tile / tiles_mn;
+                const int kb0 = split * g.kb_per_split;
+                const int kb1 = min(kb_total, kb0 + g.kb_per_split);
+                const uint32_t acc = tl & 1, acc_ph = (tl >> 1) & 1;
+                if (!mbar_wait_bounded(tempty_bar + acc, acc_ph ^ 1)) { report(status, WAIT_TMEM_EMPTY, tile); *abort_flag = 1; break; }
+                fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait_bounded(full_bar + s, ph)) { report(status, WAIT_FULL, s); *abort_flag = 1; break; }
+                    fence_after_sync();
+                    const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+                    const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+                    for (int j = 0; j < BK / UMMA_K; ++j) {
+                        // K-major: 16 elements = 32 B further along the swizzled row;
+                        // MN-major: 16 k-rows of 128 B further down.
+                        const uint64_t da = A_MN ? make_smem_desc(sa + j * (UMMA_K * 128), BK * 128, 1024)
+                                                 : make_smem_desc(sa + j * (UMMA_K * 2), 16, 1024);
+                        const uint64_t db = B_MN ? make_smem_desc(sb + j * (UMMA_K * 128), BK * 128, 1024)
+                                                 : make_smem_desc(sb + j * (UMMA_K * 2), 16, 1024);
+                        mma_f16_ss(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+                    }
+                    mma_commit(empty_bar + s);     // stage reusable once these MMAs have read it
+                }
+                mma_commit(tfull_bar + acc);       // accumulator complete
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const int quarter = warp & 3;              // TMEM lane quarter this warp may read
+        uint32_t tl = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tl) {
+            const int split = tile / tiles_mn, mn = tile % tiles_mn;
+            const int m0 = (mn / tiles_n) * BM, n0 = (mn % tiles_n) * BN;
+            const uint32_t acc = tl & 1, acc_ph = (tl >> 1) & 1;
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait_bounded(tfull_bar + acc, acc_ph);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { if (lane == 0) { report(status, WAIT_TMEM_FULL, tile); *abort_flag = 1; } break; }
+            fence_after_sync();
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + c * 32, r);
+                tmem_ld_wait();
+                const int col0 = n0 + c * 32;
+                if (row < g.M && col0 < g.N) {
+                    if (g.out_f32) {
+                        float* dst = reinterpret_cast<float*>(Dptr) + ((size_t)split * g.M + row) * g.ldd + col0;
+                        if (col0 + 32 <= g.N) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                reinterpret_cast<uint4*>(dst)[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                        } else {
+                            for (int q = 0; q < 32 && col0 + q < g.N; ++q) dst[q] = __uint_as_float(r[q]);
+                        }
+                    } else {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int q = 0; q < 16; ++q) {
+                            const float lo = __uint_as_float(r[2 * q]), hi = __uint_as_float(r[2 * q + 1]);
+                            if (g.ab_format == 1) {
+                                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+                                packed[q] = *reinterpret_cast<uint32_t*>(&v);
+                            } else {
+                                __half2 v = __floats2half2_rn(lo, hi);
+                                packed[q] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                        }
+                        uint16_t* dst = reinterpret_cast<uint16_t*>(Dptr) + (size_t)row * g.ldd + col0;
+                        if (col0 + 32 <= g.N) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                                reinterpret_cast<uint4*>(dst)[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                        } else {
+                            for (int q = 0; q < 32 && col0 + q < g.N; ++q)
+                                dst[q] = (uint16_t)((q & 1) ? (packed[q >> 1] >> 16) : (packed[q >> 1] & 0xFFFF));
+                        }
+                    }
+                }
+            }
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar + acc);
+        }
+    }
+
+    // -------------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        // let copies that are still in flight land before the CTA's shared memory goes away
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+}
+
+// out[m, n] = sum_s partial[s, m, n]   (fixed order), cast to OUT
+template <typename OUT>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, OUT* __restrict__ out, long long mn, int splits,
+                                     float beta, const OUT* __restrict__ prev) {
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= mn) return;
+    float4 acc = *reinterpret_cast<const float4*>(partial + i);
+    for (int s = 1; s < splits; ++s) {
+        const float4 p = *reinterpret_cast<const float4*>(partial + (long long)s * mn + i);
+        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    }
+    float v[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        if (i + q < mn) {
+            float r = v[q];
+            if (prev != nullptr) r += beta * (float)prev[i + q];
+            out[i + q] = (OUT)r;
+        }
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = []() -> EncodeFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+        TORCH_CHECK(e == cudaSuccess && q == cudaDriverEntryPointSuccess && p != nullptr,
+                    "cuTensorMapEncodeTiled is not available from the driver");
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return fn;
+}
+
+// 2-D map over a row-major [rows, cols] 16-bit matrix with `ld` elements per row; box = [box_rows, 64 cols]
+CUtensorMap make_map(const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, bool bf16) {
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(base) % 16 == 0, "TMA: base address must be 16-byte aligned");
+    TORCH_CHECK((ld * 2) % 16 == 0, "TMA: row pitch must be a multiple of 16 bytes (leading dimension % 8 == 0)");
+    CUtensorMap m;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = encode_fn()(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+    return m;
+}
+
+at::Tensor& status_word(const at::Device& dev) {
+    // deliberately leaked: tensors must not be destroyed after the CUDA context at process exit
+    static auto* words = new std::vector<at::Tensor>(64);
+    at::Tensor& w = (*words)[dev.index()];
+    if (!w.defined()) w = at::zeros({4}, at::TensorOptions().dtype(at::kInt).device(dev));
+    return w;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+void launch(const CUtensorMap& ta, const CUtensorMap& tb, void* d, const GemmArgs& g, KernelStatus* st, int grid,
+            cudaStream_t stream) {
+    using L = SmemLayout<BN, STAGES>;
+    auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN>;
+    static bool configured = false;
+    if (!configured) {
+        C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        configured = true;
+    }
+    kern<<<grid, kThreads, L::TOTAL, stream>>>(ta, tb, d, g, st);
+}
+
+}  // namespace
+
+// D = A (.) B with fp32 accumulation.
+//   a_mn == false: `a` is [M, K] (K contiguous);  a_mn == true: `a` is [K, M] (M contiguous)
+//   b_mn == false: `b` is [N, K] (K contiguous);  b_mn == true: `b` is [K, N] (N contiguous)
+//   out_f32: result dtype fp32 instead of the input dtype;  split_k: 0 = choose, else forced
+at::Tensor gemm_16bit(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, bool out_f32, int64_t split_k) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda(), "gemm_16bit: CUDA tensors required");
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm_16bit: 2-D operands required");
+    TORCH_CHECK(a.scalar_type() == b.scalar_type() && (a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf),
+                "gemm_16bit: both operands must be bf16 or both fp16");
+    const c10::cuda::CUDAGuard guard(a.device());
+    // Autograd worker threads may not have the primary context bound yet; the driver-level
+    // tensor-map encoder needs one.  A null free binds it and does nothing else.
+    C10_CUDA_CHECK(cudaFree(nullptr));
+    at::Tensor A = a.stride(1) == 1 ? a : a.contiguous();
+    at::Tensor B = b.stride(1) == 1 ? b : b.contiguous();
+    const int64_t M = a_mn ? A.size(1) : A.size(0), K = a_mn ? A.size(0) : A.size(1);
+    const int64_t N = b_mn ? B.size(1) : B.size(0), Kb = b_mn ? B.size(0) : B.size(1);
+    TORCH_CHECK(K == Kb, "gemm_16bit: contraction sizes differ (", K, " vs ", Kb, ")");
+    TORCH_CHECK(N % 8 == 0, "gemm_16bit: N must be a multiple of 8");
+    const bool bf16 = a.scalar_type() == at::kBFloat16;
+
+    const int BN = N > 128 ? 256 : 128;
+    const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
+    const int kb_total = (int)((K + BK - 1) / BK);
+    const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    int splits = (int)split_k;
+    if (splits <= 0) {
+        splits = 1;
+        if (tiles * 2 <= sms && kb_total >= 16) splits = std::min(std::max(1, sms / tiles), kb_total / 4);
+    }
+    splits = std::max(1, std::min(splits, kb_total));
+    int kb_per = (kb_total + splits - 1) / splits;
+    splits = (kb_total + kb_per - 1) / kb_per;
+
+    GemmArgs g{};
+    g.M = (int)M; g.N = (int)N; g.K = (int)K; g.ldd = (int)N;
+    g.split_k = splits; g.kb_per_split = kb_per;
+    g.out_f32 = (out_f32 || splits > 1) ? 1 : 0;
+    g.ab_format = bf16 ? 1 : 0;
+
+    const CUtensorMap ta = a_mn ? make_map(A.data_ptr(), K, M, A.stride(0), BK, bf16)
+                                : make_map(A.data_ptr(), M, K, A.stride(0), BM, bf16);
+    const CUtensorMap tb = b_mn ? make_map(B.data_ptr(), K, N, B.stride(0), BK, bf16)
+                                : make_map(B.data_ptr(), N, K, B.stride(0), BN, bf16);
+
+    auto opts = a.options();
+    at::Tensor out = at::empty({M, N}, out_f32 ? opts.dtype(at::kFloat) : opts);
+    at::Tensor scratch;
+    void* dptr = out.data_ptr();
+    if (splits > 1) {
+        scratch = at::empty({splits, M, N}, opts.dtype(at::kFloat));
+        dptr = scratch.data_ptr();
+    }
+    at::Tensor& st = status_word(a.device());
+    KernelStatus* stp = reinterpret_cast<KernelStatus*>(st.data_ptr<int>());
+    const int grid = std::min(tiles * splits, sms);
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+
+#define SJ_LAUNCH(BN_, ST_)                                                                          \
+    do {                                                                                             \
+        if (a_mn && b_mn) launch<BN_, ST_, true, true>(ta, tb, dptr, g, stp, grid, stream);          \
+        else if (a_mn) launch<BN_, ST_, true, false>(ta, tb, dptr, g, stp, grid, stream);            \
+        else if (b_mn) launch<BN_, ST_, false, true>(ta, tb, dptr, g, stp, grid, stream);            \
+        else launch<BN_, ST_, false, false>(ta, tb, dptr, g, stp, grid, stream);                     \
+    } while (0)
+    if (BN == 256) SJ_LAUNCH(256, 4); else SJ_LAUNCH(128, 6);
+#undef SJ_LAUNCH
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+
+    if (splits > 1) {
+        const long long mn = (long long)M * N;
+        const int threads = 256;
+        const unsigned blocks = (unsigned)((mn / 4 + threads) / threads);
+        if (out_f32) splitk_reduce_kernel<float><<<blocks, threads, 0, stream>>>(scratch.data_ptr<float>(), out.data_ptr<float>(), mn, splits, 0.f, nullptr);
+        else if (bf16) splitk_reduce_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(scratch.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), mn, splits, 0.f, nullptr);
+        else splitk_reduce_kernel<__half><<<blocks, threads, 0, stream>>>(scratch.data_ptr<float>(), reinterpret_cast<__half*>(out.data_ptr()), mn, splits, 0.f, nullptr);
+        C10_CUDA_KERNEL_LAUNCH_CHECK();
+    }
+    return out;
+}
+
+// (code, block, detail) of the first bounded wait that gave up since the last call; resets it.
+std::vector<int64_t> gemm_status(const at::Tensor& like) {
+    at::Tensor& st = status_word(like.device());
+    at::Tensor h = st.cpu();
+    st.zero_();
+    auto acc = h.accessor<int, 1>();
+    return {acc[0], acc[1], acc[2]};
+}
+
+}  // namespace sjb200
+
+TORCH_LIBRARY_FRAGMENT(sjb200, m) {
+    m.def("gemm_16bit(Tensor a, Tensor b, bool a_mn, bool b_mn, bool out_f32, int split_k) -> Tensor");
+    m.def("gemm_status(Tensor like) -> int[]");
+}
+TORCH_LIBRARY_IMPL(sjb200, CUDA, m) {
+    m.impl("gemm_16bit", &sjb200::gemm_16bit);
+    m.impl("gemm_status", &sjb200::gemm_status);
+}

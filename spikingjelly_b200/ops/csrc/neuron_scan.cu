@@ -4,7 +4,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
-#include "neuron_scan.cuh"
+#include "neuron_scan_launch.cuh"
 
 namespace sjb200 {
 namespace {
@@ -29,7 +29,7 @@ ScanParams make_params(const Dims& d, int64_t kind, double tau, double q0, doubl
                        const c10::optional<at::Tensor>& v_init, double v_init_scalar) {
     ScanParams p{};
     p.T = d.T; p.N = d.N; p.kind = (int)kind;
-    p.tau = (float)tau; p.q0 = (float)q0; p.q1 = (float)q1; p.q2 = (float)q2;
+    p.inv_tau = 1.0f / (float)tau; p.q0 = (float)q0; p.q1 = (float)q1; p.q2 = (float)q2;
     p.r_ptr = nullptr;
     if (kind == NK_PLIF_DI || kind == NK_PLIF_NDI) {
         TORCH_CHECK(r.has_value() && r->is_cuda() && r->scalar_type() == at::kFloat && r->numel() == 1,
@@ -40,31 +40,6 @@ ScanParams make_params(const Dims& d, int64_t kind, double tau, double q0, doubl
     p.v_init = (v_init.has_value() && v_init->defined() && v_init->numel() > 0) ? v_init->data_ptr() : nullptr;
     p.v_init_scalar = (float)v_init_scalar;
     return p;
-}
-
-// TX: x / grad_x storage, TV: membrane potential storage, TS: spikes / grad of spikes
-template <typename TX, typename TS, int V, int TC>
-void launch_forward(const ScanParams& p, const at::Tensor& x, at::Tensor& spike, at::Tensor& v_last,
-                    const c10::optional<at::Tensor>& v_seq, const c10::optional<at::Tensor>& packed,
-                    const c10::optional<at::Tensor>& ckpt, cudaStream_t stream) {
-    const long long threads_needed = (p.N + V - 1) / V;
-    const unsigned grid = (unsigned)((threads_needed + kThreads - 1) / kThreads);
-    scan_forward_kernel<TX, TS, V, TC><<<grid, kThreads, 0, stream>>>(
-        p, reinterpret_cast<const TX*>(x.data_ptr()), reinterpret_cast<TS*>(spike.data_ptr()),
-        reinterpret_cast<TX*>(v_last.data_ptr()),
-        v_seq.has_value() ? reinterpret_cast<TX*>(v_seq->data_ptr()) : nullptr,
-        packed.has_value() ? reinterpret_cast<uint32_t*>(packed->data_ptr()) : nullptr,
-        ckpt.has_value() ? ckpt->data_ptr<float>() : nullptr);
-}
-
-template <typename TX, typename TS, int V, int TC>
-void launch_backward(const ScanParams& p, const at::Tensor& x, const at::Tensor& gs, const void* gv_last,
-                     const void* gv_seq, const float* ckpt, at::Tensor& gx, void* gv_init, float* grad_r,
-                     float* partial, unsigned int* ticket, unsigned grid, cudaStream_t stream) {
-    scan_backward_kernel<TX, TS, V, TC><<<grid, kThreads, 0, stream>>>(
-        p, reinterpret_cast<const TX*>(x.data_ptr()), reinterpret_cast<const TS*>(gs.data_ptr()),
-        reinterpret_cast<const TX*>(gv_last), reinterpret_cast<const TX*>(gv_seq), ckpt,
-        reinterpret_cast<TX*>(gx.data_ptr()), reinterpret_cast<TX*>(gv_init), grad_r, partial, ticket);
 }
 
 #define SJ_DISPATCH_FLOATING(DTYPE, ...)                                                   \
@@ -100,6 +75,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> scan_forw
     at::Tensor spike = at::empty_like(x);
     std::vector<int64_t> state_shape(x.sizes().begin() + 1, x.sizes().end());
     at::Tensor v_last = at::empty(state_shape, x.options());
+    // a zero-element tensor stands for an absent optional output (each output gets its own)
+    auto none = [&]() { return at::empty({0}, x.options()); };
     c10::optional<at::Tensor> v_seq, packed, ckpt;
     if (store_v_seq) v_seq = at::empty_like(x);
     if (pack_bits) packed = at::empty({d.T, (d.N + 31) / 32}, x.options().dtype(at::kInt));
@@ -107,7 +84,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> scan_forw
     const int n_ckpt = (d.T + TC - 1) / TC - 1;
     if (save_ckpt && n_ckpt > 0) ckpt = at::empty({n_ckpt, d.N}, x.options().dtype(at::kFloat));
     if (d.N == 0 || d.T == 0) {
-        return {spike, v_last, v_seq.value_or(at::Tensor()), packed.value_or(at::Tensor()), ckpt.value_or(at::Tensor())};
+        return {spike, v_last, v_seq.has_value() ? *v_seq : none(), packed.has_value() ? *packed : none(), ckpt.has_value() ? *ckpt : none()};
     }
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
     SJ_DISPATCH_FLOATING(x.scalar_type(), {
@@ -116,16 +93,17 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> scan_forw
                          aligned<scalar_t>(v_last.data_ptr(), VV) && aligned<scalar_t>(p.v_init, VV) &&
                          (!v_seq.has_value() || aligned<scalar_t>(v_seq->data_ptr(), VV)) &&
                          (!ckpt.has_value() || aligned<float>(ckpt->data_ptr(), VV));
-        if (vec) {
-            if (TC == 4) launch_forward<scalar_t, scalar_t, VV, 4>(p, x, spike, v_last, v_seq, packed, ckpt, stream);
-            else launch_forward<scalar_t, scalar_t, VV, 8>(p, x, spike, v_last, v_seq, packed, ckpt, stream);
-        } else {
-            if (TC == 4) launch_forward<scalar_t, scalar_t, 1, 4>(p, x, spike, v_last, v_seq, packed, ckpt, stream);
-            else launch_forward<scalar_t, scalar_t, 1, 8>(p, x, spike, v_last, v_seq, packed, ckpt, stream);
-        }
+        const int V = vec ? (TC == 8 ? 4 : VV) : 1;
+        const long long threads_needed = (d.N + V - 1) / V;
+        const unsigned grid = (unsigned)((threads_needed + kThreads - 1) / kThreads);
+        ScanFwdPtrs io{x.data_ptr(), spike.data_ptr(), v_last.data_ptr(),
+                       v_seq.has_value() ? v_seq->data_ptr() : nullptr,
+                       packed.has_value() ? reinterpret_cast<uint32_t*>(packed->data_ptr()) : nullptr,
+                       ckpt.has_value() ? ckpt->data_ptr<float>() : nullptr};
+        scan_forward_launch<scalar_t>(p, io, vec, TC, grid, stream);
     });
     C10_CUDA_KERNEL_LAUNCH_CHECK();
-    return {spike, v_last, v_seq.value_or(at::Tensor()), packed.value_or(at::Tensor()), ckpt.value_or(at::Tensor())};
+    return {spike, v_last, v_seq.has_value() ? *v_seq : none(), packed.has_value() ? *packed : none(), ckpt.has_value() ? *ckpt : none()};
 }
 
 // returns (grad_x_seq, grad_v_init | empty, grad_r | empty)
@@ -162,9 +140,9 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> scan_backward(
     }
     at::Tensor gx = at::empty_like(x);
     std::vector<int64_t> state_shape(x.sizes().begin() + 1, x.sizes().end());
-    at::Tensor gvi = need_grad_v_init ? at::empty(state_shape, x.options()) : at::Tensor();
+    at::Tensor gvi = need_grad_v_init ? at::empty(state_shape, x.options()) : at::empty({0}, x.options());
     const bool plif = (kind == NK_PLIF_DI || kind == NK_PLIF_NDI);
-    at::Tensor grad_r = plif ? at::zeros({1}, x.options().dtype(at::kFloat)) : at::Tensor();
+    at::Tensor grad_r = plif ? at::zeros({1}, x.options().dtype(at::kFloat)) : at::empty({0}, x.options());
     if (d.N == 0 || d.T == 0) return {gx, gvi, grad_r};
 
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
@@ -174,8 +152,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> scan_backward(
                          aligned<scalar_t>(gx.data_ptr(), VV) && aligned<scalar_t>(p.v_init, VV) &&
                          (!gvl.has_value() || aligned<scalar_t>(gvl->data_ptr(), VV)) &&
                          (!gvs.has_value() || aligned<scalar_t>(gvs->data_ptr(), VV)) &&
-                         (!gvi.defined() || aligned<scalar_t>(gvi.data_ptr(), VV)) && aligned<float>(ckpt_ptr, VV);
-        const int V = vec ? VV : 1;
+                         (!need_grad_v_init || aligned<scalar_t>(gvi.data_ptr(), VV)) && aligned<float>(ckpt_ptr, VV);
+        const int V = vec ? (TC == 8 ? 4 : VV) : 1;
         const long long threads_needed = (d.N + V - 1) / V;
         const unsigned grid = (unsigned)((threads_needed + kThreads - 1) / kThreads);
         at::Tensor scratch;
@@ -188,15 +166,10 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> scan_backward(
         }
         const void* gvl_p = gvl.has_value() ? gvl->data_ptr() : nullptr;
         const void* gvs_p = gvs.has_value() ? gvs->data_ptr() : nullptr;
-        void* gvi_p = gvi.defined() ? gvi.data_ptr() : nullptr;
+        void* gvi_p = need_grad_v_init ? gvi.data_ptr() : nullptr;
         float* gr_p = plif ? grad_r.data_ptr<float>() : nullptr;
-        if (vec) {
-            if (TC == 4) launch_backward<scalar_t, scalar_t, VV, 4>(p, x, gs, gvl_p, gvs_p, ckpt_ptr, gx, gvi_p, gr_p, partial, ticket, grid, stream);
-            else launch_backward<scalar_t, scalar_t, VV, 8>(p, x, gs, gvl_p, gvs_p, ckpt_ptr, gx, gvi_p, gr_p, partial, ticket, grid, stream);
-        } else {
-            if (TC == 4) launch_backward<scalar_t, scalar_t, 1, 4>(p, x, gs, gvl_p, gvs_p, ckpt_ptr, gx, gvi_p, gr_p, partial, ticket, grid, stream);
-            else launch_backward<scalar_t, scalar_t, 1, 8>(p, x, gs, gvl_p, gvs_p, ckpt_ptr, gx, gvi_p, gr_p, partial, ticket, grid, stream);
-        }
+        ScanBwdPtrs io{x.data_ptr(), gs.data_ptr(), gvl_p, gvs_p, ckpt_ptr, gx.data_ptr(), gvi_p, gr_p, partial, ticket};
+        scan_backward_launch<scalar_t>(p, io, vec, TC, grid, stream);
     });
     C10_CUDA_KERNEL_LAUNCH_CHECK();
     return {gx, gvi, grad_r};

@@ -34,7 +34,7 @@ struct ScanParams {
     long long N;
     // neuron
     int kind;
-    float tau;          // LIF/QIF/EIF time constant
+    float inv_tau;      // fp32 reciprocal of the LIF/QIF/EIF time constant
     float q0, q1, q2;   // QIF: a0, v_rest, v_c   EIF: delta_T, theta_rh, v_rest
     const float* r_ptr; // PLIF: device scalar r = sigmoid(w)
     float v_th, v_reset;
@@ -48,54 +48,53 @@ struct ScanParams {
     float v_init_scalar;
 };
 
+// Dynamics of one neuron model, resolved at compile time.  Division by the python
+// scalar tau is a multiplication by the fp32 reciprocal, exactly as PyTorch's CUDA
+// `tensor / scalar` kernel evaluates it; the __f*_rn intrinsics are never contracted
+// into FMAs, so every intermediate is rounded like a separate eager fp32 op.
+template <int KIND>
 struct Neuron {
-    int kind;
-    float tau, r, q0, q1, q2, vr, v_th, v_reset;
+    float inv_tau, r, inv_r, q0, q1, q2, vr, v_th, v_reset;
     int soft;
 
     __device__ __forceinline__ Neuron(const ScanParams& p)
-        : kind(p.kind), tau(p.tau), q0(p.q0), q1(p.q1), q2(p.q2), v_th(p.v_th), v_reset(p.v_reset), soft(p.soft_reset) {
+        : inv_tau(p.inv_tau), q0(p.q0), q1(p.q1), q2(p.q2), v_th(p.v_th), v_reset(p.v_reset), soft(p.soft_reset) {
         vr = p.soft_reset ? 0.0f : p.v_reset;
-        r = (p.kind == NK_PLIF_DI || p.kind == NK_PLIF_NDI) ? *p.r_ptr : 0.0f;
+        r = (KIND == NK_PLIF_DI || KIND == NK_PLIF_NDI) ? *p.r_ptr : 0.0f;
+        inv_r = (KIND == NK_PLIF_DI) ? 1.0f / r : 0.0f;
     }
-    // The round-to-nearest intrinsics are never contracted into FMAs, so every
-    // intermediate is rounded exactly like a separate eager fp32 op.
     __device__ __forceinline__ float charge(float x, float v) const {
-        switch (kind) {
-        case NK_IF: return __fadd_rn(v, x);
-        case NK_LIF_DI: return __fadd_rn(v, __fdiv_rn(__fsub_rn(x, __fsub_rn(v, vr)), tau));
-        case NK_LIF_NDI: return __fadd_rn(__fsub_rn(v, __fdiv_rn(__fsub_rn(v, vr), tau)), x);
-        case NK_PLIF_DI: return __fadd_rn(v, __fmul_rn(__fsub_rn(x, __fsub_rn(v, vr)), r));
-        case NK_PLIF_NDI: return __fadd_rn(__fsub_rn(v, __fmul_rn(__fsub_rn(v, vr), r)), x);
-        case NK_QIF:
-            return __fadd_rn(v, __fdiv_rn(__fadd_rn(x, __fmul_rn(__fmul_rn(q0, __fsub_rn(v, q1)), __fsub_rn(v, q2))), tau));
-        case NK_EIF:
-            return __fadd_rn(v, __fdiv_rn(__fadd_rn(__fsub_rn(__fadd_rn(x, q2), v),
-                                                   __fmul_rn(q0, expf(__fdiv_rn(__fsub_rn(v, q1), q0)))), tau));
-        default: return __fadd_rn(v, x);
-        }
+        if constexpr (KIND == NK_IF) return __fadd_rn(v, x);
+        else if constexpr (KIND == NK_LIF_DI) return __fadd_rn(v, __fmul_rn(__fsub_rn(x, __fsub_rn(v, vr)), inv_tau));
+        else if constexpr (KIND == NK_LIF_NDI) return __fadd_rn(__fsub_rn(v, __fmul_rn(__fsub_rn(v, vr), inv_tau)), x);
+        else if constexpr (KIND == NK_PLIF_DI) return __fadd_rn(v, __fmul_rn(__fsub_rn(x, __fsub_rn(v, vr)), r));
+        else if constexpr (KIND == NK_PLIF_NDI) return __fadd_rn(__fsub_rn(v, __fmul_rn(__fsub_rn(v, vr), r)), x);
+        else if constexpr (KIND == NK_QIF)
+            return __fadd_rn(v, __fmul_rn(__fadd_rn(x, __fmul_rn(__fmul_rn(q0, __fsub_rn(v, q1)), __fsub_rn(v, q2))), inv_tau));
+        else  // NK_EIF; q0 = delta_T, q1 = theta_rh, q2 = v_rest
+            return __fadd_rn(v, __fmul_rn(__fadd_rn(__fsub_rn(__fadd_rn(x, q2), v),
+                                                   __fmul_rn(q0, expf(__fmul_rn(__fsub_rn(v, q1), 1.0f / q0)))), inv_tau));
     }
-    __device__ __forceinline__ float fire(float h) const { return (__fsub_rn(h, v_th) >= 0.0f) ? 1.0f : 0.0f; }
-    __device__ __forceinline__ float reset(float h, float s) const {
-        return soft ? __fsub_rn(h, __fmul_rn(s, v_th)) : __fadd_rn(__fmul_rn(s, v_reset), __fmul_rn(__fsub_rn(1.0f, s), h));
+    // h - v_th >= 0 and h >= v_th agree for all finite floats (x - y rounds to zero only if x == y)
+    __device__ __forceinline__ bool fire(float h) const { return h >= v_th; }
+    // soft: h - s v_th;  hard: s v_reset + (1 - s) h  (both reduce to these selects for finite h)
+    __device__ __forceinline__ float reset(float h, bool s) const {
+        return soft ? (s ? __fsub_rn(h, v_th) : h) : (s ? v_reset : h);
     }
+    static constexpr bool kNeedsV = (KIND == NK_PLIF_DI || KIND == NK_PLIF_NDI || KIND == NK_QIF || KIND == NK_EIF);
+    static constexpr bool kPlif = (KIND == NK_PLIF_DI || KIND == NK_PLIF_NDI);
     // dh/dv at membrane potential v (before charging)
     __device__ __forceinline__ float dh_dv(float v) const {
-        switch (kind) {
-        case NK_IF: return 1.0f;
-        case NK_LIF_DI: case NK_LIF_NDI: return 1.0f - 1.0f / tau;
-        case NK_PLIF_DI: case NK_PLIF_NDI: return 1.0f - r;
-        case NK_QIF: return 1.0f + q0 * (2.0f * v - q1 - q2) / tau;
-        case NK_EIF: return 1.0f + (expf((v - q1) / q0) - 1.0f) / tau;
-        default: return 1.0f;
-        }
+        if constexpr (KIND == NK_IF) return 1.0f;
+        else if constexpr (KIND == NK_LIF_DI || KIND == NK_LIF_NDI) return 1.0f - inv_tau;
+        else if constexpr (kPlif) return 1.0f - r;
+        else if constexpr (KIND == NK_QIF) return 1.0f + q0 * (2.0f * v - q1 - q2) * inv_tau;
+        else return 1.0f + (__expf((v - q1) / q0) - 1.0f) * inv_tau;
     }
     __device__ __forceinline__ float dh_dx() const {
-        switch (kind) {
-        case NK_LIF_DI: case NK_QIF: case NK_EIF: return 1.0f / tau;
-        case NK_PLIF_DI: return r;
-        default: return 1.0f;
-        }
+        if constexpr (KIND == NK_LIF_DI || KIND == NK_QIF || KIND == NK_EIF) return inv_tau;
+        else if constexpr (KIND == NK_PLIF_DI) return r;
+        else return 1.0f;
     }
 };
 
@@ -103,15 +102,15 @@ struct Neuron {
 // spike_seq [T,N] (TO), v_last [N] (TIN), optional v_seq [T,N] (TIN),
 // optional packed [T, ceil(N/32)] (bit i of word j = neuron 32 j + i),
 // optional ckpt [ceil(T/TC)-1, N] fp32 (membrane potential after step (j+1)*TC-1).
-template <typename TIN, typename TO, int V, int TC>
-__global__ void __launch_bounds__(256)
+template <typename TIN, typename TO, int V, int TC, int KIND>
+__global__ void __launch_bounds__(256, 3)
 scan_forward_kernel(ScanParams p, const TIN* __restrict__ x_seq, TO* __restrict__ spike_seq,
                     TIN* __restrict__ v_last, TIN* __restrict__ v_seq, uint32_t* __restrict__ packed,
                     float* __restrict__ ckpt) {
     const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long n0 = gtid * V;
     const bool active = n0 < p.N;
-    const Neuron nrn(p);
+    const Neuron<KIND> nrn(p);
     const long long words = (p.N + 31) / 32;
 
     float v[V];
@@ -123,22 +122,24 @@ scan_forward_kernel(ScanParams p, const TIN* __restrict__ x_seq, TO* __restrict_
     }
 
     for (int t0 = 0; t0 < p.T; t0 += TC) {
-        float x[TC][V];
+        Pack<TIN, V> xr[TC];   // all loads of the chunk are in flight before the first use
 #pragma unroll
         for (int i = 0; i < TC; ++i) {
-            if (active && t0 + i < p.T) load_vec_stream<TIN, V>(x_seq + (long long)(t0 + i) * p.N + n0, x[i]);
+            if (active && t0 + i < p.T) xr[i] = load_raw_stream<TIN, V>(x_seq + (long long)(t0 + i) * p.N + n0);
         }
 #pragma unroll
         for (int i = 0; i < TC; ++i) {
             if (t0 + i < p.T) {
-                float s[V];
+                float x[V], s[V];
+                unpack<TIN, V>(xr[i], x);
                 uint32_t bits = 0;
 #pragma unroll
                 for (int j = 0; j < V; ++j) {
-                    const float h = nrn.charge(x[i][j], v[j]);
-                    s[j] = nrn.fire(h);
-                    v[j] = nrn.reset(h, s[j]);
-                    bits |= (s[j] != 0.0f ? 1u : 0u) << j;
+                    const float h = nrn.charge(x[j], v[j]);
+                    const bool f = nrn.fire(h);
+                    s[j] = f ? 1.0f : 0.0f;
+                    v[j] = nrn.reset(h, f);
+                    bits |= (f ? 1u : 0u) << j;
                 }
                 const long long off = (long long)(t0 + i) * p.N + n0;
                 if (active) {
@@ -166,8 +167,8 @@ scan_forward_kernel(ScanParams p, const TIN* __restrict__ x_seq, TO* __restrict_
 // grad_x_seq [T,N] (TIN); optional grad_v_init [N] (TIN); PLIF: block partial sums of
 // dL/dr go to partial[gridDim.x], the last block to finish (ticket counter) adds them
 // in index order into grad_r[0] — a deterministic single-launch reduction.
-template <typename TIN, typename TG, int V, int TC>
-__global__ void __launch_bounds__(256)
+template <typename TIN, typename TG, int V, int TC, int KIND>
+__global__ void __launch_bounds__(256, 2)
 scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __restrict__ grad_spike_seq,
                      const TIN* __restrict__ grad_v_last, const TIN* __restrict__ grad_v_seq,
                      const float* __restrict__ ckpt, TIN* __restrict__ grad_x_seq, TIN* __restrict__ grad_v_init,
@@ -175,10 +176,15 @@ scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __re
     const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long n0 = gtid * V;
     const bool active = n0 < p.N;
-    const Neuron nrn(p);
-    const bool plif = (p.kind == NK_PLIF_DI || p.kind == NK_PLIF_NDI);
-    const bool need_v = plif || p.kind == NK_QIF || p.kind == NK_EIF;
+    const Neuron<KIND> nrn(p);
+    constexpr bool plif = Neuron<KIND>::kPlif;
+    constexpr bool need_v = Neuron<KIND>::kNeedsV;
     const float dhdx = nrn.dh_dx();
+    const float dhdv_const = nrn.dh_dv(0.0f);   // used when dh/dv does not depend on v
+    const float kd = p.detach_reset ? 0.0f : 1.0f;
+    const float k_s = p.soft_reset ? 0.0f : 1.0f;
+    const float k_a = kd * (p.soft_reset ? -p.v_th : p.v_reset);
+    const float k_b = kd * (p.soft_reset ? 0.0f : -1.0f);
 
     float c[V];     // dL/dv_t flowing in from step t+1
     float gr = 0.0f;
@@ -204,12 +210,18 @@ scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __re
 #pragma unroll
             for (int j = 0; j < V; ++j) v0[j] = p.v_init_scalar;
         }
-        // recompute h for the chunk (h overwrites x in place)
-        float h[TC][V];
+        // issue every load of the chunk (inputs and upstream gradients) before any use
+        Pack<TIN, V> xr[TC];
+        Pack<TG, V> gr_raw[TC];
 #pragma unroll
         for (int i = 0; i < TC; ++i) {
-            if (active && t0 + i < p.T) load_vec_stream<TIN, V>(x_seq + (long long)(t0 + i) * p.N + n0, h[i]);
+            if (active && t0 + i < p.T) {
+                xr[i] = load_raw_stream<TIN, V>(x_seq + (long long)(t0 + i) * p.N + n0);
+                gr_raw[i] = load_raw_stream<TG, V>(grad_spike_seq + (long long)(t0 + i) * p.N + n0);
+            }
         }
+        // recompute the membrane trajectory of the chunk
+        float h[TC][V];
         {
             float v[V];
 #pragma unroll
@@ -217,43 +229,51 @@ scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __re
 #pragma unroll
             for (int i = 0; i < TC; ++i) {
                 if (t0 + i < p.T) {
+                    float x[V];
+                    unpack<TIN, V>(xr[i], x);
 #pragma unroll
                     for (int j = 0; j < V; ++j) {
-                        const float hh = nrn.charge(h[i][j], v[j]);
+                        const float hh = nrn.charge(x[j], v[j]);
                         h[i][j] = hh;
                         v[j] = nrn.reset(hh, nrn.fire(hh));
                     }
                 }
             }
         }
-        // reverse walk
+        // reverse walk.  d v_t / d h_t = 1 - k_s s + sg (k_a + k_b h) with uniform constants:
+        //   soft reset: k_s = 0, k_a = -v_th, k_b = 0;  hard: k_s = 1, k_a = v_reset, k_b = -1;
+        //   detach_reset zeroes k_a and k_b.
 #pragma unroll
         for (int i = TC - 1; i >= 0; --i) {
             if (t0 + i < p.T) {
                 const long long off = (long long)(t0 + i) * p.N + n0;
-                float gs[V], gv[V], gx[V];
+                float gs[V], gv[V], gx[V], sg[V];
                 if (active) {
-                    load_vec_stream<TG, V>(grad_spike_seq + off, gs);
+                    unpack<TG, V>(gr_raw[i], gs);
                     if (grad_v_seq != nullptr) load_vec_stream<TIN, V>(grad_v_seq + off, gv);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < V; ++j) gs[j] = 0.0f;
                 }
 #pragma unroll
+                for (int j = 0; j < V; ++j) sg[j] = h[i][j] - p.v_th;
+                surrogate_grad_vec<V>(p.sg_id, sg, p.sg_p0, p.sg_p1);   // one switch per V elements
+#pragma unroll
                 for (int j = 0; j < V; ++j) {
-                    if (!active) { gs[j] = 0.0f; }
                     const float hh = h[i][j];
-                    const float s = nrn.fire(hh);
-                    const float sg = surrogate_grad(p.sg_id, hh - p.v_th, p.sg_p0, p.sg_p1);
+                    const float s = nrn.fire(hh) ? 1.0f : 0.0f;
                     const float g = c[j] + ((active && grad_v_seq != nullptr) ? gv[j] : 0.0f);
-                    float dv_dh;  // d v_t / d h_t through the reset
-                    if (p.soft_reset) dv_dh = 1.0f - (p.detach_reset ? 0.0f : p.v_th * sg);
-                    else dv_dh = (1.0f - s) + (p.detach_reset ? 0.0f : (p.v_reset - hh) * sg);
-                    const float gh = gs[j] * sg + g * dv_dh;
-                    float vprev = 0.0f;
-                    if (need_v) {
+                    const float dv_dh = fmaf(sg[j], fmaf(k_b, hh, k_a), fmaf(-k_s, s, 1.0f));
+                    const float gh = fmaf(gs[j], sg[j], g * dv_dh);
+                    if constexpr (need_v) {
+                        float vprev;
                         if (i == 0) vprev = v0[j];
                         else { const float hp = h[i > 0 ? i - 1 : 0][j]; vprev = nrn.reset(hp, nrn.fire(hp)); }
+                        if constexpr (plif) gr += (KIND == NK_PLIF_DI) ? gh * (hh - vprev) * nrn.inv_r : gh * (nrn.vr - vprev);
+                        c[j] = gh * nrn.dh_dv(vprev);
+                    } else {
+                        c[j] = gh * dhdv_const;
                     }
-                    if (plif) gr += (p.kind == NK_PLIF_DI) ? gh * (hh - vprev) / nrn.r : gh * (nrn.vr - vprev);
-                    c[j] = gh * nrn.dh_dv(vprev);
                     gx[j] = gh * dhdx;
                 }
                 if (active) store_vec<TIN, V>(grad_x_seq + off, gx);
@@ -262,7 +282,7 @@ scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __re
     }
     if (active && grad_v_init != nullptr) store_vec<TIN, V>(grad_v_init + n0, c);
 
-    if (plif) {  // uniform
+    if constexpr (plif) {
         __shared__ float warp_part[8];
         __shared__ bool last_block;
         gr = warp_sum(active ? gr : 0.0f);

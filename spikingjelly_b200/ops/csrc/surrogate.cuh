@@ -16,8 +16,8 @@ enum SurrogateId : int {
 __device__ __forceinline__ float surrogate_grad(int id, float x, float p0, float p1) {
     const float PI = 3.14159265358979323846f;
     switch (id) {
-    case SG_SIGMOID: { float s = 1.0f / (1.0f + expf(-p0 * x)); return (1.0f - s) * s * p0; }
-    case SG_ATAN: { float a = p0 * 0.5f; float ax = PI * a * x; return a / (1.0f + ax * ax); }
+    case SG_SIGMOID: { float s = __fdividef(1.0f, 1.0f + __expf(-p0 * x)); return (1.0f - s) * s * p0; }
+    case SG_ATAN: { float a = p0 * 0.5f; float ax = PI * a * x; return __fdividef(a, 1.0f + ax * ax); }
     case SG_PIECEWISE_QUADRATIC: { float xa = fabsf(x); return xa > (1.0f / p0) ? 0.0f : (-(p0 * p0) * xa + p0); }
     case SG_PIECEWISE_EXP: return p0 * 0.5f * expf(-p0 * fabsf(x));
     case SG_SOFT_SIGN: { float d = 1.0f / p0 + fabsf(x); return 1.0f / (2.0f * p0 * d * d); }
@@ -46,5 +46,22 @@ __device__ __forceinline__ float surrogate_grad(int id, float x, float p0, float
 
 template <int ID>
 __device__ __forceinline__ float surrogate_grad(float x, float p0, float p1) { return surrogate_grad(ID, x, p0, p1); }
+
+// In-place g'(x) for V values.  The two surrogates used by every shipped model get
+// branch-free bodies; the switch for the rest is taken once per call, not per element.
+template <int V>
+__device__ __forceinline__ void surrogate_grad_vec(int id, float (&x)[V], float p0, float p1) {
+    if (id == SG_ATAN) {
+        const float a = p0 * 0.5f, pa = 3.14159265358979323846f * a;
+#pragma unroll
+        for (int j = 0; j < V; ++j) { const float ax = pa * x[j]; x[j] = __fdividef(a, 1.0f + ax * ax); }
+    } else if (id == SG_SIGMOID) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) { const float s = __fdividef(1.0f, 1.0f + __expf(-p0 * x[j])); x[j] = (1.0f - s) * s * p0; }
+    } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) x[j] = surrogate_grad(id, x[j], p0, p1);
+    }
+}
 
 }  // namespace sjb200

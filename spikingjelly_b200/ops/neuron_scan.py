@@ -52,6 +52,7 @@ class _Scan(torch.autograd.Function):
         ctx.save_for_backward(x_seq, v_init if v_init is not None else x_seq.new_empty(0),
                               r if r is not None else x_seq.new_empty(0), ckpt)
         ctx.mark_non_differentiable(packed)
+        ctx.set_materialize_grads(False)
         return spike, v_last, v_seq, packed
 
     @staticmethod
