@@ -25,7 +25,8 @@ import torch.nn.functional as F
 
 from ..activation_based import neuron, surrogate
 from ..ops import gemm as G
-from ..ops.bn_lif import bn_lif
+from ..ops.bn_lif import bn_lif, bn_pool_lif
+from ..ops.ssa import ssa as ssa_op
 from ..ops.neuron_scan import KIND, NeuronSpec, multistep_neuron
 
 __all__ = ["forward", "eligible"]
@@ -41,8 +42,8 @@ def _spec(lif: neuron.LIFNode) -> Optional[NeuronSpec]:
 
 
 def _compute_dtype(x: torch.Tensor) -> Optional[torch.dtype]:
-    if torch.is_autocast_enabled():
-        dt = torch.get_autocast_gpu_dtype()
+    if torch.is_autocast_enabled("cuda"):
+        dt = torch.get_autocast_dtype("cuda")
         return dt if dt in (torch.bfloat16, torch.float16) else None
     return x.dtype if x.dtype in (torch.bfloat16, torch.float16) else None
 
@@ -84,6 +85,10 @@ def _stem_stage(stage, h: torch.Tensor, T: int, static: bool, dt) -> torch.Tenso
         res = h.permute(0, 2, 3, 1).reshape(T, (n // T) * hh * ww, c)
         out = bn_lif(rows, bn, spec, residual=res, v_init=_init_v(lif))
         return out.reshape(n, hh, ww, c).permute(0, 3, 1, 2)
+    if (pool.kernel_size, pool.stride, pool.padding) in ((3, 2, 1), ((3, 3), (2, 2), (1, 1))) and T <= 8:
+        n, c, hh, ww = y.shape
+        out = bn_pool_lif(y.permute(0, 2, 3, 1), bn, spec, T, static, v_init=_init_v(lif))   # [T, B, OH, OW, C]
+        return out.flatten(0, 1).permute(0, 3, 1, 2)
     z = F.batch_norm(y, bn.running_mean, bn.running_var, bn.weight, bn.bias, bn.training,
                      0.0 if bn.momentum is None else bn.momentum, bn.eps)
     if bn.training and bn.num_batches_tracked is not None:
@@ -105,6 +110,8 @@ def _ssa(S: torch.Tensor, T: int, B: int, L: int, heads: int, scale: float) -> t
     """``S``: spikes ``[T, B*L, 3C]`` -> ``Q (K^T V) * scale`` as ``[T, B*L, C]``."""
     C = S.shape[-1] // 3
     d = C // heads
+    if d in (32, 64) and L * d * 8 + 2 * d * (d + 1) * 4 <= 220 * 1024:
+        return ssa_op(S, L, heads, scale)
     qkv = S.view(T, B, L, 3, heads, d)
     q, k, v = qkv.unbind(3)
     kv = torch.einsum("tblhd,tblhe->tbhde", k, v)

@@ -64,3 +64,54 @@ def bn_lif(y: torch.Tensor, bn: torch.nn.modules.batchnorm._BatchNorm, spec: Neu
     need_grad = torch.is_grad_enabled() and (y.requires_grad or (bn.weight is not None and bn.weight.requires_grad))
     return BNLIFFunction.apply(y.contiguous(), bn.weight, bn.bias, rm, rv, residual, training, momentum, float(bn.eps),
                                spec, float(v_init), need_grad)
+
+
+class BNPoolLIFFunction(torch.autograd.Function):
+    """``LIF_T(maxpool3x3s2(BN(y)))`` on an NHWC conv output (see ``csrc/bn_pool_lif.cu``)."""
+
+    @staticmethod
+    def forward(ctx, y, gamma, beta, running_mean, running_var, training: bool, momentum: float, eps: float,
+                spec: NeuronSpec, v_init: float, T: int, is_static: bool):
+        vr = 0.0 if spec.soft else float(spec.v_reset)
+        counters.bump("bn_stats", 2 if training else 1)
+        mean, invstd, scale, shift = torch.ops.sjb200.bn_coefficients(
+            y, gamma, beta, running_mean, running_var, training, momentum, eps)
+        counters.bump("bn_pool_lif_forward")
+        out, idx = torch.ops.sjb200.bn_pool_lif_forward(y, scale, shift, T, is_static, spec.kind, spec.tau,
+                                                        spec.v_threshold, vr, spec.soft, v_init)
+        ctx.spec, ctx.training, ctx.v_init, ctx.T, ctx.is_static = spec, training, v_init, T, is_static
+        ctx.has_affine = gamma is not None
+        ctx.save_for_backward(y, idx, scale, shift, mean, invstd, gamma if gamma is not None else y.new_empty(0))
+        return out
+
+    @staticmethod
+    def backward(ctx, g_out):
+        y, idx, scale, shift, mean, invstd, gamma = ctx.saved_tensors
+        spec: NeuronSpec = ctx.spec
+        vr = 0.0 if spec.soft else float(spec.v_reset)
+        counters.bump("bn_pool_lif_backward", 3)
+        dy, g_gamma, g_beta = torch.ops.sjb200.bn_pool_lif_backward(
+            g_out, y, idx, scale, shift, mean, invstd, gamma if ctx.has_affine else None, ctx.training, ctx.T,
+            ctx.is_static, spec.kind, spec.tau, spec.v_threshold, vr, spec.soft, ctx.v_init, spec.sg[0], spec.sg[1],
+            spec.sg[2], spec.detach_reset)
+        return (dy, g_gamma if ctx.has_affine else None, g_beta if ctx.has_affine else None) + (None,) * 9
+
+
+def _bn_args(bn):
+    training = bn.training or bn.running_mean is None
+    momentum = 0.0 if bn.momentum is None else float(bn.momentum)
+    if bn.training and bn.track_running_stats and bn.num_batches_tracked is not None:
+        bn.num_batches_tracked.add_(1)
+        if bn.momentum is None:
+            momentum = 1.0 / float(bn.num_batches_tracked)
+    use_running = (bn.track_running_stats and bn.training) or not training
+    return training, momentum, (bn.running_mean if use_running else None), (bn.running_var if use_running else None)
+
+
+def bn_pool_lif(y_nhwc: torch.Tensor, bn, spec: NeuronSpec, T: int, is_static: bool, v_init: float = 0.0):
+    """``y_nhwc``: contiguous ``[NB, H, W, C]`` (``NB = B`` when ``is_static`` else ``T*B``), 16-bit.
+    Returns spikes ``[T, B, OH, OW, C]`` with ``OH = (H - 1) // 2 + 1``."""
+    require()
+    training, momentum, rm, rv = _bn_args(bn)
+    return BNPoolLIFFunction.apply(y_nhwc, bn.weight, bn.bias, rm, rv, training, momentum, float(bn.eps), spec,
+                                   float(v_init), int(T), bool(is_static))

@@ -12,6 +12,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
+#include "bn_lif.h"
 #include "neuron_scan.cuh"
 
 namespace sjb200 {
@@ -70,19 +71,37 @@ bn_stats_partial_kernel(const T* __restrict__ y, long long rows, int C, float* _
     }
 }
 
-// one thread per channel: fixed-order sum of the block partials, then the BN coefficients
+// Sum partial[b][which][c] over b for 32 channels per block: 8 slices of blocks are summed by
+// different threads and combined in a fixed order (deterministic), instead of one long serial loop.
+__device__ __forceinline__ void reduce_partials_32x8(const float* __restrict__ partial, int nblk, int C, int c,
+                                                     double& s1, double& s2) {
+    __shared__ double sh1[8][32], sh2[8][32];
+    const int lane_c = threadIdx.x & 31, slice = threadIdx.x >> 5;   // blockDim.x == 256
+    double a1 = 0.0, a2 = 0.0;
+    if (c < C) {
+        for (int b = slice; b < nblk; b += 8) {
+            a1 += (double)partial[(size_t)b * 2 * C + c];
+            a2 += (double)partial[(size_t)b * 2 * C + C + c];
+        }
+    }
+    sh1[slice][lane_c] = a1;
+    sh2[slice][lane_c] = a2;
+    __syncthreads();
+    s1 = 0.0; s2 = 0.0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { s1 += sh1[k][lane_c]; s2 += sh2[k][lane_c]; }
+}
+
+// 32 channels per block: fixed-order sum of the block partials, then the BN coefficients
 __global__ void bn_finalize_forward_kernel(const float* __restrict__ partial, int nblk, int C, double count, float eps,
                                            float momentum, const float* __restrict__ gamma, const float* __restrict__ beta,
                                            float* __restrict__ running_mean, float* __restrict__ running_var,
                                            float* __restrict__ mean_out, float* __restrict__ invstd_out,
                                            float* __restrict__ scale, float* __restrict__ shift) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
-    double s1 = 0.0, s2 = 0.0;
-    for (int b = 0; b < nblk; ++b) {
-        s1 += (double)partial[(size_t)b * 2 * C + c];
-        s2 += (double)partial[(size_t)b * 2 * C + C + c];
-    }
+    const int c = blockIdx.x * 32 + (threadIdx.x & 31);
+    double s1, s2;
+    reduce_partials_32x8(partial, nblk, C, c, s1, s2);
+    if (c >= C || threadIdx.x >= 32) return;
     const double mean = s1 / count;
     double var = s2 / count - mean * mean;
     if (var < 0.0) var = 0.0;
@@ -284,13 +303,10 @@ __global__ void bn_finalize_backward_kernel(const float* __restrict__ partial, i
                                             const float* __restrict__ invstd, float* __restrict__ grad_gamma,
                                             float* __restrict__ grad_beta, float* __restrict__ coefA,
                                             float* __restrict__ coefB, float* __restrict__ coefD) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
-    double s1 = 0.0, s2 = 0.0;
-    for (int b = 0; b < nblk; ++b) {
-        s1 += (double)partial[(size_t)b * 2 * C + c];
-        s2 += (double)partial[(size_t)b * 2 * C + C + c];
-    }
+    const int c = blockIdx.x * 32 + (threadIdx.x & 31);
+    double s1, s2;
+    reduce_partials_32x8(partial, nblk, C, c, s1, s2);
+    if (c >= C || threadIdx.x >= 32) return;
     s2 = (double)invstd[c] * (s2 - (double)mean[c] * s1);   // sum gx * xhat
     grad_beta[c] = (float)s1;
     grad_gamma[c] = (float)s2;
@@ -344,7 +360,7 @@ bn_backward2_kernel(long long total, int C, const T* __restrict__ gx, const T* _
 int stats_grid(long long rows) {
     const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
     const long long want = (rows + 31) / 32;
-    return (int)std::max<long long>(1, std::min<long long>(want, (long long)sms * 4));
+    return (int)std::max<long long>(1, std::min<long long>(want, (long long)sms * 2));
 }
 
 ScanParams lif_params(int64_t T, int64_t N, int64_t kind, double tau, double v_th, double v_reset, bool soft,
@@ -357,6 +373,13 @@ ScanParams lif_params(int64_t T, int64_t N, int64_t kind, double tau, double v_t
 }
 
 }  // namespace
+
+void launch_bn_finalize_backward(const float* partial, int nblk, int C, double count, int training, const float* gamma,
+                                 const float* mean, const float* invstd, float* grad_gamma, float* grad_beta, float* coefA,
+                                 float* coefB, float* coefD, cudaStream_t stream) {
+    bn_finalize_backward_kernel<<<(C + 31) / 32, 256, 0, stream>>>(partial, nblk, C, count, training, gamma, mean, invstd,
+                                                                  grad_gamma, grad_beta, coefA, coefB, coefD);
+}
 
 // Training-mode or frozen BN coefficients of a channels-last tensor y [*, C].
 // returns (mean, invstd, scale, shift) fp32 [C]; updates running stats in place when training.
@@ -386,7 +409,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> bn_coefficients(
                 reinterpret_cast<const scalar_t*>(y.data_ptr()), rows, C, partial.data_ptr<float>());
         });
         C10_CUDA_KERNEL_LAUNCH_CHECK();
-        bn_finalize_forward_kernel<<<cb, 128, 0, stream>>>(partial.data_ptr<float>(), grid, C, (double)rows, (float)eps,
+        bn_finalize_forward_kernel<<<(C + 31) / 32, 256, 0, stream>>>(partial.data_ptr<float>(), grid, C, (double)rows, (float)eps,
                                                            (float)momentum, fptr(gamma), fptr(beta), fptr(running_mean),
                                                            fptr(running_var), mean.data_ptr<float>(), invstd.data_ptr<float>(),
                                                            scale.data_ptr<float>(), shift.data_ptr<float>());
@@ -481,7 +504,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> bn_lif_backward(
                 reinterpret_cast<scalar_t*>(gx.data_ptr()), partial.data_ptr<float>());
         });
         C10_CUDA_KERNEL_LAUNCH_CHECK();
-        bn_finalize_backward_kernel<<<(C + 127) / 128, 128, 0, stream>>>(
+        bn_finalize_backward_kernel<<<(C + 31) / 32, 256, 0, stream>>>(
             partial.data_ptr<float>(), grid1, C, (double)(y.numel() / C), training ? 1 : 0, gam, mean.data_ptr<float>(),
             invstd.data_ptr<float>(), grad_gamma.data_ptr<float>(), grad_beta.data_ptr<float>(), coef.data_ptr<float>(),
             coef.data_ptr<float>() + C, coef.data_ptr<float>() + 2 * C);
