@@ -2,4 +2,7 @@
 from .base_node import *  # noqa: F401,F403
 from .integrate_and_fire import *  # noqa: F401,F403
 from .lif import *  # noqa: F401,F403
+from .lif_variants import *  # noqa: F401,F403
 from .nonlinear_if import *  # noqa: F401,F403
+from .psn import *  # noqa: F401,F403
+from .training_variants import *  # noqa: F401,F403

@@ -110,7 +110,7 @@ def _ssa(S: torch.Tensor, T: int, B: int, L: int, heads: int, scale: float) -> t
     """``S``: spikes ``[T, B*L, 3C]`` -> ``Q (K^T V) * scale`` as ``[T, B*L, C]``."""
     C = S.shape[-1] // 3
     d = C // heads
-    if d in (32, 64) and L * d * 8 + 2 * d * (d + 1) * 4 <= 220 * 1024:
+    if d in (32, 64) and (4 * ((L + 15) // 16 * 16) + 2 * d) * (d + 8) * 2 <= 220 * 1024:
         return ssa_op(S, L, heads, scale)
     qkv = S.view(T, B, L, 3, heads, d)
     q, k, v = qkv.unbind(3)

@@ -188,7 +188,7 @@ bn_lif_forward_kernel(ScanParams p, int C, const T* __restrict__ y, const float*
 // partial[blk][0][c] = sum gx, partial[blk][1][c] = sum gx * y   (the finalize kernel turns the latter
 // into sum gx * xhat = invstd * (sum gx y - mean * sum gx))
 template <typename T, int V, int KIND>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, (V <= 4 ? 3 : 2))
 bn_lif_backward1_kernel(ScanParams p, int C, const T* __restrict__ y, const T* __restrict__ g_out,
                         const float* __restrict__ scale, const float* __restrict__ shift,
                         const float* __restrict__ ckpt, T* __restrict__ gx_out, float* __restrict__ partial) {
@@ -489,16 +489,19 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> bn_lif_backward(
     const float* gam = (gamma.has_value() && gamma->defined()) ? gamma->data_ptr<float>() : nullptr;
     SJ_BN_DISPATCH(y.scalar_type(), {
         constexpr int V = 16 / sizeof(scalar_t) > 8 ? 8 : 16 / sizeof(scalar_t);
-        const long long n_vec = N / V;
-        // gridDim * blockDim * V must be a multiple of C (see the kernel); m = C / gcd(C, blockDim * V)
-        long long gcd_a = C, gcd_b = (long long)kThreads * V;
+        // pass 1 keeps a whole 4-step trajectory per element in registers: 4 elements per thread
+        // (8-byte accesses for 16-bit types) leave room for three resident CTAs per SM
+        constexpr int V1 = 4;
+        const long long n_vec = N / V1;
+        // gridDim * blockDim * V1 must be a multiple of C (see the kernel); m = C / gcd(C, blockDim * V1)
+        long long gcd_a = C, gcd_b = (long long)kThreads * V1;
         while (gcd_b) { const long long t = gcd_a % gcd_b; gcd_a = gcd_b; gcd_b = t; }
         const long long m = C / gcd_a;
-        const long long want = std::max<long long>(1, std::min<long long>((n_vec + kThreads - 1) / kThreads, (long long)sms * 2));
+        const long long want = std::max<long long>(1, std::min<long long>((n_vec + kThreads - 1) / kThreads, (long long)sms * 3));
         const int grid1 = (int)(std::max<long long>(1, want / m) * m);
         at::Tensor partial = at::empty({grid1, 2, C}, fopt);
         SJ_BN_KIND(kind, {
-            bn_lif_backward1_kernel<scalar_t, V, KIND><<<grid1, kThreads, kThreads * 2 * V * sizeof(float), stream>>>(
+            bn_lif_backward1_kernel<scalar_t, V1, KIND><<<grid1, kThreads, kThreads * 2 * V1 * sizeof(float), stream>>>(
                 p, C, reinterpret_cast<const scalar_t*>(y.data_ptr()), reinterpret_cast<const scalar_t*>(g.data_ptr()),
                 scale.data_ptr<float>(), shift.data_ptr<float>(), ck,
                 reinterpret_cast<scalar_t*>(gx.data_ptr()), partial.data_ptr<float>());

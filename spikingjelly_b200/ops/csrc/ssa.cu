@@ -6,8 +6,12 @@
 // the D x D matrix K^T V once and applies it to all L tokens — O(L D^2) work instead of the
 // O(L^2 D) of softmax attention, and nothing of size L x L ever exists.
 //   backward:  dKV = scale Q^T dO;  dQ = scale dO (K^T V)^T;  dK = V dKV^T;  dV = K dKV.
-// fp32 accumulation; operands may be any 16-bit floats (spikes after a residual add need not be
-// binary), so the arithmetic is exact for spike inputs whenever L < 2^24.
+//
+// All six products are warp-level m16n8k16 tensor-core MMAs (16-bit operands, fp32 accumulation)
+// fed by ldmatrix from padded shared-memory tiles; the per-head problems (64 x 64 x L and
+// L x 64 x 64) are far below one tcgen05 tile, so the CTA-wide UMMA path would idle most of its
+// 128 x 256 datapath here.  K^T V of binary spikes is an integer <= L and therefore exact in bf16 for
+// L <= 256; dKV is rounded to the operand dtype once, like the batched-matmul formulation it replaces.
 #include <ATen/ATen.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -19,138 +23,189 @@ namespace sjb200 {
 namespace {
 
 constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
 
+template <int D> struct Geo {
+    static constexpr int LD = D + 8;          // padded row length (elements): 16-byte rows shifted by 4 banks
+};
+
+// ---- fragment helpers -----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t s_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+template <typename T> __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Stage `rows` rows of D contiguous elements (row stride `gstride` in global) into a padded tile and
+// zero rows [rows, rows_pad).
 template <typename T, int D>
-__device__ __forceinline__ void stage_rows(const T* __restrict__ g, long long row_stride, int L, T* __restrict__ s) {
-    constexpr int CH = D / 8;   // 16-byte chunks per row
-    for (int i = threadIdx.x; i < L * CH; i += blockDim.x) {
+__device__ __forceinline__ void stage(const T* __restrict__ g, long long gstride, int rows, int rows_pad, T* __restrict__ s) {
+    constexpr int CH = D / 8, LD = Geo<D>::LD;
+    for (int i = threadIdx.x; i < rows_pad * CH; i += blockDim.x) {
         const int l = i / CH, c = i % CH;
-        *reinterpret_cast<int4*>(s + l * D + c * 8) = *reinterpret_cast<const int4*>(g + (long long)l * row_stride + c * 8);
+        int4 v = make_int4(0, 0, 0, 0);
+        if (l < rows) v = *reinterpret_cast<const int4*>(g + (long long)l * gstride + c * 8);
+        *reinterpret_cast<int4*>(s + l * LD + c * 8) = v;
     }
 }
 
-// out[i][j] = alpha * sum_l A[l][i] * Bm[l][j]   (A, Bm: [L][D] in smem; out: [D][D+1] fp32 in smem)
+// out[i][j] = alpha * sum_l X[l][i] * Y[l][j]  for i, j in [0, D);  X, Y: padded tiles with Lp rows (Lp % 16 == 0).
+// Result rounded to T and stored in the padded tile `out` ([D][LD]).
 template <typename T, int D>
-__device__ __forceinline__ void outer_accumulate(const T* __restrict__ A, const T* __restrict__ Bm, int L, float alpha,
-                                                 float* __restrict__ out) {
-    constexpr int TD = D / 4;
-    for (int tile = threadIdx.x; tile < TD * TD; tile += blockDim.x) {
-        const int i0 = (tile / TD) * 4, j0 = (tile % TD) * 4;
-        float acc[4][4] = {};
-        for (int l = 0; l < L; ++l) {
-            float a[4], b[4];
+__device__ __forceinline__ void gram(const T* __restrict__ X, const T* __restrict__ Y, int Lp, float alpha, T* __restrict__ out) {
+    constexpr int LD = Geo<D>::LD;
+    constexpr int MT = D / 16, NT = D / 8;               // m16 / n8 tiles of the D x D result
+    constexpr int NT_W = (MT * NT) / kWarps;             // n8 tiles per warp (4 for D = 64, 1 for D = 32)
+    static_assert((MT * NT) % kWarps == 0 && NT_W >= 1, "tile split");
+    constexpr int W_PER_M = NT / NT_W;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = (warp / W_PER_M) * 16, n0 = (warp % W_PER_M) * NT_W * 8;
+    float acc[NT_W][4] = {};
+    const int sub = lane >> 3, r = lane & 7;             // ldmatrix: lane supplies row r of 8x8 matrix `sub`
+    for (int k0 = 0; k0 < Lp; k0 += 16) {
+        // A fragment of X^T: stored block (k-half, m-half) -> a0:(k0,m0) a1:(k0,m0+8) a2:(k0+8,m0) a3:(k0+8,m0+8)
+        uint32_t a[4];
+        ldsm_x4_t(s_addr(X + (k0 + (sub >> 1) * 8 + r) * LD + m0 + (sub & 1) * 8), a);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) { a[q] = to_f32<T>(A[l * D + i0 + q]); b[q] = to_f32<T>(Bm[l * D + j0 + q]); }
-#pragma unroll
-            for (int p = 0; p < 4; ++p)
-#pragma unroll
-                for (int q = 0; q < 4; ++q) acc[p][q] = fmaf(a[p], b[q], acc[p][q]);
+        for (int nt = 0; nt < NT_W; nt += 2) {
+            // B fragments of Y (stored [k][n]): matrices (k0,n) (k0+8,n) (k0,n+8) (k0+8,n+8)
+            uint32_t b[4];
+            ldsm_x4_t(s_addr(Y + (k0 + (sub & 1) * 8 + r) * LD + n0 + nt * 8 + (sub >> 1) * 8), b);
+            mma16816<T>(acc[nt], a, b[0], b[1]);
+            if (nt + 1 < NT_W) mma16816<T>(acc[nt + 1 < NT_W ? nt + 1 : nt], a, b[2], b[3]);
         }
+    }
+    const int row = m0 + (lane >> 2), col = (lane & 3) * 2;
 #pragma unroll
-        for (int p = 0; p < 4; ++p)
-#pragma unroll
-            for (int q = 0; q < 4; ++q) out[(i0 + p) * (D + 1) + j0 + q] = alpha * acc[p][q];
+    for (int nt = 0; nt < NT_W; ++nt) {
+        *reinterpret_cast<uint32_t*>(out + row * LD + n0 + nt * 8 + col) = pack2<T>(alpha * acc[nt][0], alpha * acc[nt][1]);
+        *reinterpret_cast<uint32_t*>(out + (row + 8) * LD + n0 + nt * 8 + col) = pack2<T>(alpha * acc[nt][2], alpha * acc[nt][3]);
     }
 }
 
-// dst[l][j] = alpha * sum_i A[l][i] * M[i][j]  (TRANS = false)   or   alpha * sum_i A[l][i] * M[j][i]  (TRANS = true)
-// A: [L][D] smem; M: [D][D+1] fp32 smem; dst: global, row stride `dst_stride`
+// dst[l][j] = alpha * sum_c X[l][c] * M[c][j]  (TRANS = false)   or   alpha * sum_c X[l][c] * M[j][c]  (TRANS = true)
+// X: padded tile (Lp rows), M: padded [D][LD] tile; dst: global, row stride `dstride`, rows l < L.
 template <typename T, int D, bool TRANS>
-__device__ __forceinline__ void apply_matrix(const T* __restrict__ A, const float* __restrict__ M, int L, float alpha,
-                                             T* __restrict__ dst, long long dst_stride) {
-    constexpr int TD = D / 4;
-    const int row_tiles = (L + 3) / 4;
-    for (int tile = threadIdx.x; tile < row_tiles * TD; tile += blockDim.x) {
-        const int l0 = (tile / TD) * 4, j0 = (tile % TD) * 4;
-        float acc[4][4] = {};
-        for (int i = 0; i < D; ++i) {
-            float a[4], m[4];
+__device__ __forceinline__ void apply(const T* __restrict__ X, const T* __restrict__ M, int L, int Lp, float alpha,
+                                      T* __restrict__ dst, long long dstride) {
+    constexpr int LD = Geo<D>::LD, NT = D / 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane >> 3, r = lane & 7;
+    for (int m0 = warp * 16; m0 < Lp; m0 += kWarps * 16) {
+        float acc[NT][4] = {};
 #pragma unroll
-            for (int p = 0; p < 4; ++p) a[p] = (l0 + p < L) ? to_f32<T>(A[(l0 + p) * D + i]) : 0.0f;
+        for (int k0 = 0; k0 < D; k0 += 16) {
+            uint32_t a[4];   // a0:(m0,k0) a1:(m0+8,k0) a2:(m0,k0+8) a3:(m0+8,k0+8)
+            ldsm_x4(s_addr(X + (m0 + (sub & 1) * 8 + r) * LD + k0 + (sub >> 1) * 8), a);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) m[q] = TRANS ? M[(j0 + q) * (D + 1) + i] : M[i * (D + 1) + j0 + q];
-#pragma unroll
-            for (int p = 0; p < 4; ++p)
-#pragma unroll
-                for (int q = 0; q < 4; ++q) acc[p][q] = fmaf(a[p], m[q], acc[p][q]);
-        }
-#pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            if (l0 + p < L) {
-                Pack<T, 4> o;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) o.e[q] = from_f32<T>(alpha * acc[p][q]);
-                *reinterpret_cast<Pack<T, 4>*>(dst + (long long)(l0 + p) * dst_stride + j0) = o;
+            for (int nt = 0; nt < NT; nt += 2) {
+                uint32_t b[4];   // b0,b1: n-tile nt (k0, k0+8);  b2,b3: n-tile nt+1
+                if (TRANS) ldsm_x4(s_addr(M + (nt * 8 + (sub >> 1) * 8 + r) * LD + k0 + (sub & 1) * 8), b);
+                else ldsm_x4_t(s_addr(M + (k0 + (sub & 1) * 8 + r) * LD + nt * 8 + (sub >> 1) * 8), b);
+                mma16816<T>(acc[nt], a, b[0], b[1]);
+                mma16816<T>(acc[nt + 1], a, b[2], b[3]);
             }
         }
+        const int row = m0 + (lane >> 2), col = (lane & 3) * 2;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            if (row < L) *reinterpret_cast<uint32_t*>(dst + (long long)row * dstride + nt * 8 + col) = pack2<T>(alpha * acc[nt][0], alpha * acc[nt][1]);
+            if (row + 8 < L) *reinterpret_cast<uint32_t*>(dst + (long long)(row + 8) * dstride + nt * 8 + col) = pack2<T>(alpha * acc[nt][2], alpha * acc[nt][3]);
+        }
     }
 }
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads)
-ssa_forward_kernel(const T* __restrict__ S, T* __restrict__ O, int L, int H, float scale) {
+ssa_forward_kernel(const T* __restrict__ S, T* __restrict__ O, int L, int Lp, int H, float scale) {
     extern __shared__ __align__(16) uint8_t smem[];
+    constexpr int LD = Geo<D>::LD;
     T* Qs = reinterpret_cast<T*>(smem);
-    T* Ks = Qs + L * D;
-    T* Vs = Ks + L * D;
-    float* KV = reinterpret_cast<float*>(Vs + L * D);
+    T* Ks = Qs + Lp * LD;
+    T* Vs = Ks + Lp * LD;
+    T* KV = Vs + Lp * LD;            // [D][LD]
     const int C = H * D;
     const int head = blockIdx.x % H;
     const long long tb = blockIdx.x / H;
     const T* base = S + tb * L * 3 * C + head * D;
-    stage_rows<T, D>(base, 3LL * C, L, Qs);
-    stage_rows<T, D>(base + C, 3LL * C, L, Ks);
-    stage_rows<T, D>(base + 2 * C, 3LL * C, L, Vs);
+    stage<T, D>(base, 3LL * C, L, Lp, Qs);
+    stage<T, D>(base + C, 3LL * C, L, Lp, Ks);
+    stage<T, D>(base + 2 * C, 3LL * C, L, Lp, Vs);
     __syncthreads();
-    outer_accumulate<T, D>(Ks, Vs, L, 1.0f, KV);
+    gram<T, D>(Ks, Vs, Lp, 1.0f, KV);
     __syncthreads();
-    apply_matrix<T, D, false>(Qs, KV, L, scale, O + tb * L * C + head * D, C);
+    apply<T, D, false>(Qs, KV, L, Lp, scale, O + tb * L * C + head * D, C);
 }
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads)
-ssa_backward_kernel(const T* __restrict__ S, const T* __restrict__ dO, T* __restrict__ dS, int L, int H, float scale) {
+ssa_backward_kernel(const T* __restrict__ S, const T* __restrict__ dO, T* __restrict__ dS, int L, int Lp, int H, float scale) {
     extern __shared__ __align__(16) uint8_t smem[];
+    constexpr int LD = Geo<D>::LD;
     T* Qs = reinterpret_cast<T*>(smem);
-    T* Ks = Qs + L * D;
-    T* Vs = Ks + L * D;
-    T* Gs = Vs + L * D;
-    float* KV = reinterpret_cast<float*>(Gs + L * D);
-    float* dKV = KV + D * (D + 1);
+    T* Ks = Qs + Lp * LD;
+    T* Vs = Ks + Lp * LD;
+    T* Gs = Vs + Lp * LD;
+    T* KV = Gs + Lp * LD;
+    T* dKV = KV + D * LD;
     const int C = H * D;
     const int head = blockIdx.x % H;
     const long long tb = blockIdx.x / H;
     const T* base = S + tb * L * 3 * C + head * D;
-    stage_rows<T, D>(base, 3LL * C, L, Qs);
-    stage_rows<T, D>(base + C, 3LL * C, L, Ks);
-    stage_rows<T, D>(base + 2 * C, 3LL * C, L, Vs);
-    stage_rows<T, D>(dO + tb * L * C + head * D, C, L, Gs);
+    stage<T, D>(base, 3LL * C, L, Lp, Qs);
+    stage<T, D>(base + C, 3LL * C, L, Lp, Ks);
+    stage<T, D>(base + 2 * C, 3LL * C, L, Lp, Vs);
+    stage<T, D>(dO + tb * L * C + head * D, C, L, Lp, Gs);
     __syncthreads();
-    outer_accumulate<T, D>(Ks, Vs, L, 1.0f, KV);        // K^T V
-    outer_accumulate<T, D>(Qs, Gs, L, scale, dKV);      // scale Q^T dO
+    gram<T, D>(Ks, Vs, Lp, 1.0f, KV);         // K^T V
+    gram<T, D>(Qs, Gs, Lp, scale, dKV);       // scale Q^T dO
     __syncthreads();
     T* dbase = dS + tb * L * 3 * C + head * D;
-    apply_matrix<T, D, true>(Gs, KV, L, scale, dbase, 3LL * C);          // dQ = scale dO KV^T
-    apply_matrix<T, D, true>(Vs, dKV, L, 1.0f, dbase + C, 3LL * C);      // dK = V dKV^T
-    apply_matrix<T, D, false>(Ks, dKV, L, 1.0f, dbase + 2 * C, 3LL * C); // dV = K dKV
+    apply<T, D, true>(Gs, KV, L, Lp, scale, dbase, 3LL * C);           // dQ[l][i] = scale sum_j dO[l][j] KV[i][j]
+    apply<T, D, true>(Vs, dKV, L, Lp, 1.0f, dbase + C, 3LL * C);       // dK[l][i] = sum_j V[l][j] dKV[i][j]
+    apply<T, D, false>(Ks, dKV, L, Lp, 1.0f, dbase + 2 * C, 3LL * C);  // dV[l][j] = sum_i K[l][i] dKV[i][j]
 }
 
-size_t smem_bytes(int L, int D, int n_mats, int n_sq) { return (size_t)n_mats * L * D * 2 + (size_t)n_sq * D * (D + 1) * 4; }
+int pad16(int64_t L) { return (int)((L + 15) / 16 * 16); }
+size_t smem_bytes(int Lp, int D, int n_mats, int n_sq) { return ((size_t)n_mats * Lp + (size_t)n_sq * D) * (D + 8) * 2; }
 
 template <typename T, int D>
 void launch_fwd(const at::Tensor& S, at::Tensor& O, int TB, int L, int H, float scale, cudaStream_t st) {
-    const size_t sm = smem_bytes(L, D, 3, 1);
+    const int Lp = pad16(L);
+    const size_t sm = smem_bytes(Lp, D, 3, 1);
     auto k = ssa_forward_kernel<T, D>;
     C10_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-    k<<<TB * H, kThreads, sm, st>>>(reinterpret_cast<const T*>(S.data_ptr()), reinterpret_cast<T*>(O.data_ptr()), L, H, scale);
+    k<<<TB * H, kThreads, sm, st>>>(reinterpret_cast<const T*>(S.data_ptr()), reinterpret_cast<T*>(O.data_ptr()), L, Lp, H, scale);
 }
 template <typename T, int D>
 void launch_bwd(const at::Tensor& S, const at::Tensor& dO, at::Tensor& dS, int TB, int L, int H, float scale, cudaStream_t st) {
-    const size_t sm = smem_bytes(L, D, 4, 2);
+    const int Lp = pad16(L);
+    const size_t sm = smem_bytes(Lp, D, 4, 2);
     auto k = ssa_backward_kernel<T, D>;
     C10_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
     k<<<TB * H, kThreads, sm, st>>>(reinterpret_cast<const T*>(S.data_ptr()), reinterpret_cast<const T*>(dO.data_ptr()),
-                                    reinterpret_cast<T*>(dS.data_ptr()), L, H, scale);
+                                    reinterpret_cast<T*>(dS.data_ptr()), L, Lp, H, scale);
 }
 
 void check(const at::Tensor& S, int64_t L, int64_t H) {
@@ -161,7 +216,7 @@ void check(const at::Tensor& S, int64_t L, int64_t H) {
     const int64_t D = C3 / (3 * H);
     TORCH_CHECK(D == 32 || D == 64, "ssa: head_dim must be 32 or 64");
     TORCH_CHECK(S.numel() % (L * C3) == 0, "ssa: tokens per sample do not divide the tensor");
-    TORCH_CHECK(smem_bytes((int)L, (int)D, 4, 2) <= 220 * 1024, "ssa: sequence too long for the shared-memory kernel");
+    TORCH_CHECK(smem_bytes(pad16(L), (int)D, 4, 2) <= 220 * 1024, "ssa: sequence too long for the shared-memory kernel");
 }
 
 }  // namespace
