@@ -6,3 +6,5 @@ from .lif_variants import *  # noqa: F401,F403
 from .nonlinear_if import *  # noqa: F401,F403
 from .psn import *  # noqa: F401,F403
 from .training_variants import *  # noqa: F401,F403
+from .conversion import *  # noqa: F401,F403
+from .population import *  # noqa: F401,F403

@@ -71,15 +71,16 @@ bn_stats_partial_kernel(const T* __restrict__ y, long long rows, int C, float* _
     }
 }
 
-// Sum partial[b][which][c] over b for 32 channels per block: 8 slices of blocks are summed by
+// Sum partial[b][which][c] over b for 8 channels per block: 32 slices of blocks are summed by
 // different threads and combined in a fixed order (deterministic), instead of one long serial loop.
-__device__ __forceinline__ void reduce_partials_32x8(const float* __restrict__ partial, int nblk, int C, int c,
-                                                     double& s1, double& s2) {
-    __shared__ double sh1[8][32], sh2[8][32];
-    const int lane_c = threadIdx.x & 31, slice = threadIdx.x >> 5;   // blockDim.x == 256
+constexpr int kFinCh = 8, kFinSlices = 32;     // blockDim.x == kFinCh * kFinSlices == 256
+__device__ __forceinline__ void reduce_partials(const float* __restrict__ partial, int nblk, int C, int c,
+                                                double& s1, double& s2) {
+    __shared__ double sh1[kFinSlices][kFinCh], sh2[kFinSlices][kFinCh];
+    const int lane_c = threadIdx.x % kFinCh, slice = threadIdx.x / kFinCh;
     double a1 = 0.0, a2 = 0.0;
     if (c < C) {
-        for (int b = slice; b < nblk; b += 8) {
+        for (int b = slice; b < nblk; b += kFinSlices) {
             a1 += (double)partial[(size_t)b * 2 * C + c];
             a2 += (double)partial[(size_t)b * 2 * C + C + c];
         }
@@ -88,20 +89,20 @@ __device__ __forceinline__ void reduce_partials_32x8(const float* __restrict__ p
     sh2[slice][lane_c] = a2;
     __syncthreads();
     s1 = 0.0; s2 = 0.0;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) { s1 += sh1[k][lane_c]; s2 += sh2[k][lane_c]; }
+#pragma unroll 8
+    for (int k = 0; k < kFinSlices; ++k) { s1 += sh1[k][lane_c]; s2 += sh2[k][lane_c]; }
 }
 
-// 32 channels per block: fixed-order sum of the block partials, then the BN coefficients
+// 8 channels per block: fixed-order sum of the block partials, then the BN coefficients
 __global__ void bn_finalize_forward_kernel(const float* __restrict__ partial, int nblk, int C, double count, float eps,
                                            float momentum, const float* __restrict__ gamma, const float* __restrict__ beta,
                                            float* __restrict__ running_mean, float* __restrict__ running_var,
                                            float* __restrict__ mean_out, float* __restrict__ invstd_out,
                                            float* __restrict__ scale, float* __restrict__ shift) {
-    const int c = blockIdx.x * 32 + (threadIdx.x & 31);
+    const int c = blockIdx.x * kFinCh + threadIdx.x % kFinCh;
     double s1, s2;
-    reduce_partials_32x8(partial, nblk, C, c, s1, s2);
-    if (c >= C || threadIdx.x >= 32) return;
+    reduce_partials(partial, nblk, C, c, s1, s2);
+    if (c >= C || threadIdx.x >= kFinCh) return;
     const double mean = s1 / count;
     double var = s2 / count - mean * mean;
     if (var < 0.0) var = 0.0;
@@ -303,10 +304,10 @@ __global__ void bn_finalize_backward_kernel(const float* __restrict__ partial, i
                                             const float* __restrict__ invstd, float* __restrict__ grad_gamma,
                                             float* __restrict__ grad_beta, float* __restrict__ coefA,
                                             float* __restrict__ coefB, float* __restrict__ coefD) {
-    const int c = blockIdx.x * 32 + (threadIdx.x & 31);
+    const int c = blockIdx.x * kFinCh + threadIdx.x % kFinCh;
     double s1, s2;
-    reduce_partials_32x8(partial, nblk, C, c, s1, s2);
-    if (c >= C || threadIdx.x >= 32) return;
+    reduce_partials(partial, nblk, C, c, s1, s2);
+    if (c >= C || threadIdx.x >= kFinCh) return;
     s2 = (double)invstd[c] * (s2 - (double)mean[c] * s1);   // sum gx * xhat
     grad_beta[c] = (float)s1;
     grad_gamma[c] = (float)s2;
@@ -377,7 +378,7 @@ ScanParams lif_params(int64_t T, int64_t N, int64_t kind, double tau, double v_t
 void launch_bn_finalize_backward(const float* partial, int nblk, int C, double count, int training, const float* gamma,
                                  const float* mean, const float* invstd, float* grad_gamma, float* grad_beta, float* coefA,
                                  float* coefB, float* coefD, cudaStream_t stream) {
-    bn_finalize_backward_kernel<<<(C + 31) / 32, 256, 0, stream>>>(partial, nblk, C, count, training, gamma, mean, invstd,
+    bn_finalize_backward_kernel<<<(C + kFinCh - 1) / kFinCh, kFinCh * kFinSlices, 0, stream>>>(partial, nblk, C, count, training, gamma, mean, invstd,
                                                                   grad_gamma, grad_beta, coefA, coefB, coefD);
 }
 
@@ -409,7 +410,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> bn_coefficients(
                 reinterpret_cast<const scalar_t*>(y.data_ptr()), rows, C, partial.data_ptr<float>());
         });
         C10_CUDA_KERNEL_LAUNCH_CHECK();
-        bn_finalize_forward_kernel<<<(C + 31) / 32, 256, 0, stream>>>(partial.data_ptr<float>(), grid, C, (double)rows, (float)eps,
+        bn_finalize_forward_kernel<<<(C + kFinCh - 1) / kFinCh, kFinCh * kFinSlices, 0, stream>>>(partial.data_ptr<float>(), grid, C, (double)rows, (float)eps,
                                                            (float)momentum, fptr(gamma), fptr(beta), fptr(running_mean),
                                                            fptr(running_var), mean.data_ptr<float>(), invstd.data_ptr<float>(),
                                                            scale.data_ptr<float>(), shift.data_ptr<float>());
@@ -507,7 +508,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> bn_lif_backward(
                 reinterpret_cast<scalar_t*>(gx.data_ptr()), partial.data_ptr<float>());
         });
         C10_CUDA_KERNEL_LAUNCH_CHECK();
-        bn_finalize_backward_kernel<<<(C + 31) / 32, 256, 0, stream>>>(
+        bn_finalize_backward_kernel<<<(C + kFinCh - 1) / kFinCh, kFinCh * kFinSlices, 0, stream>>>(
             partial.data_ptr<float>(), grid1, C, (double)(y.numel() / C), training ? 1 : 0, gam, mean.data_ptr<float>(),
             invstd.data_ptr<float>(), grad_gamma.data_ptr<float>(), grad_beta.data_ptr<float>(), coef.data_ptr<float>(),
             coef.data_ptr<float>() + C, coef.data_ptr<float>() + 2 * C);

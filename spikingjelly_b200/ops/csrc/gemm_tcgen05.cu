@@ -40,7 +40,9 @@ struct SmemLayout {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;   // barriers + slack for 1024 B alignment
+    static constexpr int OUT_OFFSET = BAR_OFFSET + 1024;    // epilogue staging: 2 x [128 rows][32 cols] 16-bit
+    static constexpr int OUT_BYTES = BM * 32 * 2;
+    static constexpr int TOTAL = OUT_OFFSET + 2 * OUT_BYTES + 1024;   // + slack for 1024 B alignment
 };
 
 struct GemmArgs {
@@ -54,8 +56,8 @@ struct GemmArgs {
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Dptr,
-            GemmArgs g, KernelStatus* __restrict__ status) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmD, void* __restrict__ Dptr, GemmArgs g, KernelStatus* __restrict__ status) {
     using L = SmemLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -159,7 +161,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     } else {
         // ---------------------------------------------------------------- epilogue
         const int quarter = warp & 3;              // TMEM lane quarter this warp may read
-        uint32_t tl = 0;
+        uint32_t tl = 0, oc = 0;                   // tiles / output chunks handled so far
         for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tl) {
             const int split = tile / tiles_mn, mn = tile % tiles_mn;
             const int m0 = (mn / tiles_n) * BM, n0 = (mn % tiles_n) * BN;
@@ -187,28 +189,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         } else {
                             for (int q = 0; q < 32 && col0 + q < g.N; ++q) dst[q] = __uint_as_float(r[q]);
                         }
-                    } else {
-                        uint32_t packed[16];
+                    }
+                }
+                if (!g.out_f32) {
+                    // 16-bit output: stage the 128 x 32 chunk in shared memory (64-byte rows, 16-byte
+                    // chunks XOR-swizzled by (row >> 1) & 3 = the TMA 64B swizzle) and let TMA write it:
+                    // full-sector, clipped at the matrix edges, asynchronous.
+                    uint8_t* stage_buf = smem + L::OUT_OFFSET + (oc & 1) * L::OUT_BYTES;
+                    if (oc >= 2 && threadIdx.x == 64) tma_store_wait_read<1>();  // the store that last read this buffer is done
+                    ++oc;
+                    named_barrier(1, 128);
+                    const int r_in_tile = quarter * 32 + lane;
 #pragma unroll
-                        for (int q = 0; q < 16; ++q) {
-                            const float lo = __uint_as_float(r[2 * q]), hi = __uint_as_float(r[2 * q + 1]);
-                            if (g.ab_format == 1) {
-                                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-                                packed[q] = *reinterpret_cast<uint32_t*>(&v);
-                            } else {
-                                __half2 v = __floats2half2_rn(lo, hi);
-                                packed[q] = *reinterpret_cast<uint32_t*>(&v);
-                            }
-                        }
-                        uint16_t* dst = reinterpret_cast<uint16_t*>(Dptr) + (size_t)row * g.ldd + col0;
-                        if (col0 + 32 <= g.N) {
+                    for (int q = 0; q < 4; ++q) {
+                        uint32_t w[4];
 #pragma unroll
-                            for (int q = 0; q < 4; ++q)
-                                reinterpret_cast<uint4*>(dst)[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-                        } else {
-                            for (int q = 0; q < 32 && col0 + q < g.N; ++q)
-                                dst[q] = (uint16_t)((q & 1) ? (packed[q >> 1] >> 16) : (packed[q >> 1] & 0xFFFF));
+                        for (int e = 0; e < 4; ++e) {
+                            const float lo = __uint_as_float(r[8 * q + 2 * e]), hi = __uint_as_float(r[8 * q + 2 * e + 1]);
+                            if (g.ab_format == 1) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
+                            else { __half2 v = __floats2half2_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
                         }
+                        const int chunk = q ^ ((r_in_tile >> 1) & 3);
+                        *reinterpret_cast<uint4*>(stage_buf + r_in_tile * 64 + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                    fence_async_smem();
+                    named_barrier(1, 128);
+                    if (threadIdx.x == 64) {
+                        tma_store_2d(&tmD, stage_buf, n0 + c * 32, m0);
+                        tma_store_commit();
                     }
                 }
             }
@@ -216,6 +224,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar + acc);
         }
+        if (threadIdx.x == 64) tma_store_wait_all<0>();   // all output boxes written before the CTA retires
     }
 
     // -------------------------------------------------------------------- teardown
@@ -268,19 +277,20 @@ EncodeFn encode_fn() {
     return fn;
 }
 
-// 2-D map over a row-major [rows, cols] 16-bit matrix with `ld` elements per row; box = [box_rows, 64 cols]
-CUtensorMap make_map(const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, bool bf16) {
+// 2-D map over a row-major [rows, cols] 16-bit matrix with `ld` elements per row; box = [box_rows, box_cols];
+// box_cols * 2 bytes must equal the swizzle span (128 B or 64 B).
+CUtensorMap make_map(const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, bool bf16, int box_cols = 64) {
     TORCH_CHECK(reinterpret_cast<uintptr_t>(base) % 16 == 0, "TMA: base address must be 16-byte aligned");
     TORCH_CHECK((ld * 2) % 16 == 0, "TMA: row pitch must be a multiple of 16 bytes (leading dimension % 8 == 0)");
     CUtensorMap m;
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1u, 1u};
+    const CUtensorMapSwizzle sw = box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     CUresult r = encode_fn()(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
-                             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
     return m;
 }
@@ -294,8 +304,8 @@ at::Tensor& status_word(const at::Device& dev) {
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-void launch(const CUtensorMap& ta, const CUtensorMap& tb, void* d, const GemmArgs& g, KernelStatus* st, int grid,
-            cudaStream_t stream) {
+void launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, void* d, const GemmArgs& g,
+            KernelStatus* st, int grid, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
     auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN>;
     static bool configured = false;
@@ -303,7 +313,7 @@ void launch(const CUtensorMap& ta, const CUtensorMap& tb, void* d, const GemmArg
         C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         configured = true;
     }
-    kern<<<grid, kThreads, L::TOTAL, stream>>>(ta, tb, d, g, st);
+    kern<<<grid, kThreads, L::TOTAL, stream>>>(ta, tb, td, d, g, st);
 }
 
 }  // namespace
@@ -361,6 +371,8 @@ at::Tensor gemm_16bit(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool 
         scratch = at::empty({splits, M, N}, opts.dtype(at::kFloat));
         dptr = scratch.data_ptr();
     }
+    // 16-bit results leave through TMA (box 128 x 32, 64-byte swizzle); fp32 results are stored directly
+    const CUtensorMap td = g.out_f32 ? ta : make_map(out.data_ptr(), M, N, N, BM, bf16, 32);
     at::Tensor& st = status_word(a.device());
     KernelStatus* stp = reinterpret_cast<KernelStatus*>(st.data_ptr<int>());
     const int grid = std::min(tiles * splits, sms);
@@ -368,10 +380,10 @@ at::Tensor gemm_16bit(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool 
 
 #define SJ_LAUNCH(BN_, ST_)                                                                          \
     do {                                                                                             \
-        if (a_mn && b_mn) launch<BN_, ST_, true, true>(ta, tb, dptr, g, stp, grid, stream);          \
-        else if (a_mn) launch<BN_, ST_, true, false>(ta, tb, dptr, g, stp, grid, stream);            \
-        else if (b_mn) launch<BN_, ST_, false, true>(ta, tb, dptr, g, stp, grid, stream);            \
-        else launch<BN_, ST_, false, false>(ta, tb, dptr, g, stp, grid, stream);                     \
+        if (a_mn && b_mn) launch<BN_, ST_, true, true>(ta, tb, td, dptr, g, stp, grid, stream);          \
+        else if (a_mn) launch<BN_, ST_, true, false>(ta, tb, td, dptr, g, stp, grid, stream);            \
+        else if (b_mn) launch<BN_, ST_, false, true>(ta, tb, td, dptr, g, stp, grid, stream);            \
+        else launch<BN_, ST_, false, false>(ta, tb, td, dptr, g, stp, grid, stream);                     \
     } while (0)
     if (BN == 256) SJ_LAUNCH(256, 4); else SJ_LAUNCH(128, 6);
 #undef SJ_LAUNCH
