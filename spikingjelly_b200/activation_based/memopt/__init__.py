@@ -1,1 +1,4 @@
-from .checkpointing import in_gc_1st_forward  # noqa: F401
+"""Memory optimisation: compressed-input gradient checkpointing and its automatic placement."""
+from .checkpointing import *  # noqa: F401,F403
+from .compress import *  # noqa: F401,F403
+from .pipeline import *  # noqa: F401,F403
