@@ -48,8 +48,8 @@ class SymmetricBucket:
             h_sig = symm.rendezvous(self._signal, self.group)
             self._buf_ptrs: List[int] = [int(p) for p in h_buf.buffer_ptrs]
             self._sig_ptrs: List[int] = [int(p) for p in h_sig.buffer_ptrs]
-            self._mc_ptr = int(h_buf.multicast_ptr) if (use_multimem and h_buf.has_multicast_support(
-                self.device.type, self.device.index)) else 0
+            # multicast_ptr is 0 where the fabric offers no NVSwitch multicast mapping
+            self._mc_ptr = int(h_buf.multicast_ptr or 0) if use_multimem else 0
             self._handles = (h_buf, h_sig)
             self._status = torch.zeros(4, dtype=torch.int32, device=self.device)
             torch.cuda.synchronize(self.device)
