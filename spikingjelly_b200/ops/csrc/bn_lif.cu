@@ -136,11 +136,15 @@ __global__ void bn_frozen_coeff_kernel(int C, float eps, const float* __restrict
 
 // -------------------------------------------------------------------- forward
 // y, out, res: [T, N] with N = R * C; scale/shift: [C]; ckpt: [ceil(T/4) - 1, N] fp32 or null
-template <typename T, int V, int KIND>
+// TFIX > 0: sequence length known at compile time and <= TCB (one register chunk, no checkpoints, no
+// per-step bounds predicates); HAS_RES: a residual is added to the spikes.
+template <typename T, int V, int KIND, int TFIX, bool HAS_RES>
 __global__ void __launch_bounds__(kThreads, 3)
-bn_lif_forward_kernel(ScanParams p, int C, const T* __restrict__ y, const float* __restrict__ scale,
+bn_lif_forward_kernel(ScanParams p_in, int C, const T* __restrict__ y, const float* __restrict__ scale,
                       const float* __restrict__ shift, const T* __restrict__ res, T* __restrict__ out,
                       float* __restrict__ ckpt) {
+    ScanParams p = p_in;
+    if constexpr (TFIX > 0) { p.T = TFIX; ckpt = nullptr; }
     const long long n0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * V;
     if (n0 >= p.N) return;
     const Neuron<KIND> nrn(p);
@@ -156,7 +160,7 @@ bn_lif_forward_kernel(ScanParams p, int C, const T* __restrict__ y, const float*
         for (int i = 0; i < TCB; ++i) {
             if (t0 + i < p.T) {
                 yr[i] = load_raw_stream<T, V>(y + (long long)(t0 + i) * p.N + n0);
-                if (res != nullptr) rr[i] = load_raw_stream<T, V>(res + (long long)(t0 + i) * p.N + n0);
+                if constexpr (HAS_RES) rr[i] = load_raw_stream<T, V>(res + (long long)(t0 + i) * p.N + n0);
             }
         }
 #pragma unroll
@@ -171,7 +175,7 @@ bn_lif_forward_kernel(ScanParams p, int C, const T* __restrict__ y, const float*
                     v[j] = nrn.reset(h, f);
                     s[j] = f ? 1.0f : 0.0f;
                 }
-                if (res != nullptr) {
+                if constexpr (HAS_RES) {
                     float r[V];
                     unpack<T, V>(rr[i], r);
 #pragma unroll
@@ -188,14 +192,18 @@ bn_lif_forward_kernel(ScanParams p, int C, const T* __restrict__ y, const float*
 // g_out: dL/d(out) [T, N];  writes gx = dL/d(BN output) [T, N];
 // partial[blk][0][c] = sum gx, partial[blk][1][c] = sum gx * y   (the finalize kernel turns the latter
 // into sum gx * xhat = invstd * (sum gx y - mean * sum gx))
-template <typename T, int V, int KIND>
-__global__ void __launch_bounds__(kThreads, (V <= 4 ? 3 : 2))
-bn_lif_backward1_kernel(ScanParams p, int C, const T* __restrict__ y, const T* __restrict__ g_out,
+template <typename T, int V, int KIND, int TFIX = 0, int OCC = (V <= 4 ? 3 : 2)>
+__global__ void __launch_bounds__(kThreads, OCC)
+bn_lif_backward1_kernel(ScanParams p_in, int C, const T* __restrict__ y, const T* __restrict__ g_out,
                         const float* __restrict__ scale, const float* __restrict__ shift,
                         const float* __restrict__ ckpt, T* __restrict__ gx_out, float* __restrict__ partial) {
     // The host picks gridDim so that (gridDim * blockDim * V) % C == 0: a thread then sees the same
     // channels in every iteration of its grid-stride loop and keeps its sums in registers.
     extern __shared__ float s_buf[];   // [blockDim][2 V]
+    // TFIX > 0: the sequence length is a compile-time constant that fits one register chunk
+    // (no checkpoints, no per-step bounds predicates)
+    ScanParams p = p_in;
+    if constexpr (TFIX > 0) p.T = TFIX;
     const Neuron<KIND> nrn(p);
     const float dhdx = nrn.dh_dx();
     const float dhdv = nrn.dh_dv(0.0f);
@@ -451,10 +459,19 @@ std::tuple<at::Tensor, at::Tensor> bn_lif_forward(const at::Tensor& y, const at:
         constexpr int V = 16 / sizeof(scalar_t) > 8 ? 8 : 16 / sizeof(scalar_t);
         const unsigned grid = (unsigned)((N / V + kThreads - 1) / kThreads);
         SJ_BN_KIND(kind, {
-            bn_lif_forward_kernel<scalar_t, V, KIND><<<grid, kThreads, 0, stream>>>(
-                p, C, reinterpret_cast<const scalar_t*>(y.data_ptr()), scale.data_ptr<float>(), shift.data_ptr<float>(),
-                reinterpret_cast<const scalar_t*>(res), reinterpret_cast<scalar_t*>(out.data_ptr()),
-                ckpt.numel() > 0 ? ckpt.data_ptr<float>() : nullptr);
+            auto launch = [&](auto kern) {
+                kern<<<grid, kThreads, 0, stream>>>(
+                    p, C, reinterpret_cast<const scalar_t*>(y.data_ptr()), scale.data_ptr<float>(), shift.data_ptr<float>(),
+                    reinterpret_cast<const scalar_t*>(res), reinterpret_cast<scalar_t*>(out.data_ptr()),
+                    ckpt.numel() > 0 ? ckpt.data_ptr<float>() : nullptr);
+            };
+            if (T == TCB) {
+                if (res != nullptr) launch(bn_lif_forward_kernel<scalar_t, V, KIND, TCB, true>);
+                else launch(bn_lif_forward_kernel<scalar_t, V, KIND, TCB, false>);
+            } else {
+                if (res != nullptr) launch(bn_lif_forward_kernel<scalar_t, V, KIND, 0, true>);
+                else launch(bn_lif_forward_kernel<scalar_t, V, KIND, 0, false>);
+            }
         });
     });
     C10_CUDA_KERNEL_LAUNCH_CHECK();
@@ -502,10 +519,14 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> bn_lif_backward(
         const int grid1 = (int)(std::max<long long>(1, want / m) * m);
         at::Tensor partial = at::empty({grid1, 2, C}, fopt);
         SJ_BN_KIND(kind, {
-            bn_lif_backward1_kernel<scalar_t, V1, KIND><<<grid1, kThreads, kThreads * 2 * V1 * sizeof(float), stream>>>(
-                p, C, reinterpret_cast<const scalar_t*>(y.data_ptr()), reinterpret_cast<const scalar_t*>(g.data_ptr()),
-                scale.data_ptr<float>(), shift.data_ptr<float>(), ck,
-                reinterpret_cast<scalar_t*>(gx.data_ptr()), partial.data_ptr<float>());
+            auto launch = [&](auto kern) {
+                kern<<<grid1, kThreads, kThreads * 2 * V1 * sizeof(float), stream>>>(
+                    p, C, reinterpret_cast<const scalar_t*>(y.data_ptr()), reinterpret_cast<const scalar_t*>(g.data_ptr()),
+                    scale.data_ptr<float>(), shift.data_ptr<float>(), ck,
+                    reinterpret_cast<scalar_t*>(gx.data_ptr()), partial.data_ptr<float>());
+            };
+            if (T == TCB) launch(bn_lif_backward1_kernel<scalar_t, V1, KIND, TCB>);
+            else launch(bn_lif_backward1_kernel<scalar_t, V1, KIND, 0>);
         });
         C10_CUDA_KERNEL_LAUNCH_CHECK();
         bn_finalize_backward_kernel<<<(C + kFinCh - 1) / kFinCh, kFinCh * kFinSlices, 0, stream>>>(

@@ -102,14 +102,20 @@ struct Neuron {
 // spike_seq [T,N] (TO), v_last [N] (TIN), optional v_seq [T,N] (TIN),
 // optional packed [T, ceil(N/32)] (bit i of word j = neuron 32 j + i),
 // optional ckpt [ceil(T/TC)-1, N] fp32 (membrane potential after step (j+1)*TC-1).
-template <typename TIN, typename TO, int V, int TC, int KIND>
+// LEAN: the common training call, with everything optional compiled out: T is a multiple of TC (no
+// per-step bounds predicates), scalar initial potential, no v_seq, no bit-packed output.
+template <typename TIN, typename TO, int V, int TC, int KIND, bool LEAN = false>
 __global__ void __launch_bounds__(256, 3)
 scan_forward_kernel(ScanParams p, const TIN* __restrict__ x_seq, TO* __restrict__ spike_seq,
                     TIN* __restrict__ v_last, TIN* __restrict__ v_seq, uint32_t* __restrict__ packed,
                     float* __restrict__ ckpt) {
     const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long n0 = gtid * V;
-    const bool active = n0 < p.N;
+    if constexpr (LEAN) {
+        if (n0 >= p.N) return;
+        p.v_init = nullptr; v_seq = nullptr; packed = nullptr;
+    }
+    const bool active = LEAN ? true : (n0 < p.N);
     const Neuron<KIND> nrn(p);
     const long long words = (p.N + 31) / 32;
 
@@ -125,11 +131,11 @@ scan_forward_kernel(ScanParams p, const TIN* __restrict__ x_seq, TO* __restrict_
         Pack<TIN, V> xr[TC];   // all loads of the chunk are in flight before the first use
 #pragma unroll
         for (int i = 0; i < TC; ++i) {
-            if (active && t0 + i < p.T) xr[i] = load_raw_stream<TIN, V>(x_seq + (long long)(t0 + i) * p.N + n0);
+            if (active && (LEAN || t0 + i < p.T)) xr[i] = load_raw_stream<TIN, V>(x_seq + (long long)(t0 + i) * p.N + n0);
         }
 #pragma unroll
         for (int i = 0; i < TC; ++i) {
-            if (t0 + i < p.T) {
+            if (LEAN || t0 + i < p.T) {
                 float x[V], s[V];
                 unpack<TIN, V>(xr[i], x);
                 uint32_t bits = 0;
@@ -167,7 +173,8 @@ scan_forward_kernel(ScanParams p, const TIN* __restrict__ x_seq, TO* __restrict_
 // grad_x_seq [T,N] (TIN); optional grad_v_init [N] (TIN); PLIF: block partial sums of
 // dL/dr go to partial[gridDim.x], the last block to finish (ticket counter) adds them
 // in index order into grad_r[0] — a deterministic single-launch reduction.
-template <typename TIN, typename TG, int V, int TC, int KIND>
+// LEAN: T is a multiple of TC, scalar initial potential, no gradient flowing in through v_last or v_seq.
+template <typename TIN, typename TG, int V, int TC, int KIND, bool LEAN = false>
 __global__ void __launch_bounds__(256, 2)
 scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __restrict__ grad_spike_seq,
                      const TIN* __restrict__ grad_v_last, const TIN* __restrict__ grad_v_seq,
@@ -175,9 +182,13 @@ scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __re
                      float* __restrict__ grad_r, float* __restrict__ partial, unsigned int* __restrict__ ticket) {
     const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long n0 = gtid * V;
-    const bool active = n0 < p.N;
-    const Neuron<KIND> nrn(p);
     constexpr bool plif = Neuron<KIND>::kPlif;
+    if constexpr (LEAN) {
+        p.v_init = nullptr; grad_v_last = nullptr; grad_v_seq = nullptr;
+        if constexpr (!plif) { if (n0 >= p.N) return; }     // the PLIF block reduction needs every thread
+    }
+    const bool active = (LEAN && !plif) ? true : (n0 < p.N);
+    const Neuron<KIND> nrn(p);
     constexpr bool need_v = Neuron<KIND>::kNeedsV;
     const float dhdx = nrn.dh_dx();
     const float dhdv_const = nrn.dh_dv(0.0f);   // used when dh/dv does not depend on v
@@ -215,7 +226,7 @@ scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __re
         Pack<TG, V> gr_raw[TC];
 #pragma unroll
         for (int i = 0; i < TC; ++i) {
-            if (active && t0 + i < p.T) {
+            if (active && (LEAN || t0 + i < p.T)) {
                 xr[i] = load_raw_stream<TIN, V>(x_seq + (long long)(t0 + i) * p.N + n0);
                 gr_raw[i] = load_raw_stream<TG, V>(grad_spike_seq + (long long)(t0 + i) * p.N + n0);
             }
@@ -228,7 +239,7 @@ scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __re
             for (int j = 0; j < V; ++j) v[j] = v0[j];
 #pragma unroll
             for (int i = 0; i < TC; ++i) {
-                if (t0 + i < p.T) {
+                if (LEAN || t0 + i < p.T) {
                     float x[V];
                     unpack<TIN, V>(xr[i], x);
 #pragma unroll
@@ -245,7 +256,7 @@ scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __re
         //   detach_reset zeroes k_a and k_b.
 #pragma unroll
         for (int i = TC - 1; i >= 0; --i) {
-            if (t0 + i < p.T) {
+            if (LEAN || t0 + i < p.T) {
                 const long long off = (long long)(t0 + i) * p.N + n0;
                 float gs[V], gv[V], gx[V], sg[V];
                 if (active) {

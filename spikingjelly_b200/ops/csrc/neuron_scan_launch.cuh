@@ -20,6 +20,9 @@ struct ScanBwdPtrs {
 template <typename T> void scan_forward_launch(const ScanParams& p, const ScanFwdPtrs& io, bool vec, int TC, unsigned grid, cudaStream_t s);
 template <typename T> void scan_backward_launch(const ScanParams& p, const ScanBwdPtrs& io, bool vec, int TC, unsigned grid, cudaStream_t s);
 
+// (the instantiation macro below names its type parameter T, so p.T cannot be spelled inside it)
+inline int scan_steps(const ScanParams& p) { return p.T; }
+
 #define SJ_SCAN_KIND_SWITCH(KIND_VALUE, ...)                                           \
     switch (KIND_VALUE) {                                                              \
     case NK_IF: { constexpr int KIND = NK_IF; __VA_ARGS__; break; }                    \
@@ -41,8 +44,11 @@ template <typename T> void scan_backward_launch(const ScanParams& p, const ScanB
         auto sp = reinterpret_cast<T*>(io.spike_seq);                                                               \
         auto vl = reinterpret_cast<T*>(io.v_last);                                                                  \
         auto vs = reinterpret_cast<T*>(io.v_seq);                                                                   \
+        const bool lean = vec && scan_steps(p) % TC == 0 && p.v_init == nullptr && io.v_seq == nullptr && io.packed == nullptr;   \
         SJ_SCAN_KIND_SWITCH(p.kind, {                                                                               \
-            if (vec && TC == 4) scan_forward_kernel<T, T, VV, 4, KIND><<<grid, 256, 0, s>>>(p, x, sp, vl, vs, io.packed, io.ckpt); \
+            if (lean && TC == 4) scan_forward_kernel<T, T, VV, 4, KIND, true><<<grid, 256, 0, s>>>(p, x, sp, vl, vs, io.packed, io.ckpt); \
+            else if (lean) scan_forward_kernel<T, T, V8, 8, KIND, true><<<grid, 256, 0, s>>>(p, x, sp, vl, vs, io.packed, io.ckpt);       \
+            else if (vec && TC == 4) scan_forward_kernel<T, T, VV, 4, KIND><<<grid, 256, 0, s>>>(p, x, sp, vl, vs, io.packed, io.ckpt); \
             else if (vec) scan_forward_kernel<T, T, V8, 8, KIND><<<grid, 256, 0, s>>>(p, x, sp, vl, vs, io.packed, io.ckpt);       \
             else if (TC == 4) scan_forward_kernel<T, T, 1, 4, KIND><<<grid, 256, 0, s>>>(p, x, sp, vl, vs, io.packed, io.ckpt);    \
             else scan_forward_kernel<T, T, 1, 8, KIND><<<grid, 256, 0, s>>>(p, x, sp, vl, vs, io.packed, io.ckpt);                 \
@@ -59,8 +65,11 @@ template <typename T> void scan_backward_launch(const ScanParams& p, const ScanB
         auto gvs = reinterpret_cast<const T*>(io.grad_v_seq);                                                       \
         auto gx = reinterpret_cast<T*>(io.grad_x_seq);                                                              \
         auto gvi = reinterpret_cast<T*>(io.grad_v_init);                                                            \
+        const bool lean = vec && scan_steps(p) % TC == 0 && p.v_init == nullptr && io.grad_v_last == nullptr && io.grad_v_seq == nullptr; \
         SJ_SCAN_KIND_SWITCH(p.kind, {                                                                               \
-            if (vec && TC == 4) scan_backward_kernel<T, T, VV, 4, KIND><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket); \
+            if (lean && TC == 4) scan_backward_kernel<T, T, VV, 4, KIND, true><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket); \
+            else if (lean) scan_backward_kernel<T, T, V8, 8, KIND, true><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket);       \
+            else if (vec && TC == 4) scan_backward_kernel<T, T, VV, 4, KIND><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket); \
             else if (vec) scan_backward_kernel<T, T, V8, 8, KIND><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket);       \
             else if (TC == 4) scan_backward_kernel<T, T, 1, 4, KIND><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket);    \
             else scan_backward_kernel<T, T, 1, 8, KIND><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket);                 \
