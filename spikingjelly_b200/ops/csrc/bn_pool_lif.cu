@@ -58,10 +58,14 @@ __device__ __forceinline__ void pooled_window(const T* __restrict__ y, const Poo
     }
 }
 
-template <typename T, int KIND>
+// TFIX > 0: sequence length known at compile time; STATIC: one input image feeds every step.
+template <typename T, int KIND, int TFIX, bool STATIC>
 __global__ void __launch_bounds__(kThreads)
-bn_pool_lif_forward_kernel(ScanParams p, PoolGeom g, const T* __restrict__ y, const float* __restrict__ scale,
+bn_pool_lif_forward_kernel(ScanParams p, PoolGeom g_in, const T* __restrict__ y, const float* __restrict__ scale,
                            const float* __restrict__ shift, T* __restrict__ out, uint8_t* __restrict__ idx) {
+    PoolGeom g = g_in;
+    g.is_static = STATIC ? 1 : 0;
+    if constexpr (TFIX > 0) g.T = TFIX;
     const int G = g.C / V;
     const long long vec = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long n_vec = (long long)g.B * g.OH * g.OW * G;
@@ -81,7 +85,9 @@ bn_pool_lif_forward_kernel(ScanParams p, PoolGeom g, const T* __restrict__ y, co
     for (int j = 0; j < V; ++j) v[j] = p.v_init_scalar;
     const long long per_step = (long long)g.B * g.OH * g.OW * g.C;
     const long long o_off = (((long long)b * g.OH + oh) * g.OW + ow) * g.C + c0;
-    for (int t = 0; t < g.T; ++t) {
+#pragma unroll
+    for (int t = 0; t < (TFIX > 0 ? TFIX : kMaxT); ++t) {
+        if (t >= g.T) break;
         if (t == 0 || !g.is_static) {
             const int img = g.is_static ? b : t * g.B + b;
             pooled_window<T>(y, g, img, oh, ow, c0, sc, sh, best, code);
@@ -103,12 +109,16 @@ bn_pool_lif_forward_kernel(ScanParams p, PoolGeom g, const T* __restrict__ y, co
 }
 
 // The host picks gridDim with (gridDim * blockDim) % (C / V) == 0, so a thread keeps its channel group.
-template <typename T, int KIND, int TMAX>
+// EXACT: T == TMAX (no per-step bounds predicates); STATIC: one input image feeds every step.
+template <typename T, int KIND, int TMAX, bool EXACT, bool STATIC>
 __global__ void __launch_bounds__(kThreads, 2)
-bn_pool_lif_backward1_kernel(ScanParams p, PoolGeom g, const T* __restrict__ y, const uint8_t* __restrict__ idx,
+bn_pool_lif_backward1_kernel(ScanParams p, PoolGeom g_in, const T* __restrict__ y, const uint8_t* __restrict__ idx,
                              const T* __restrict__ g_out, const float* __restrict__ scale,
                              const float* __restrict__ shift, T* __restrict__ Gout, float* __restrict__ partial) {
     extern __shared__ float s_buf[];   // [blockDim][2 V]
+    PoolGeom g = g_in;
+    g.is_static = STATIC ? 1 : 0;
+    if constexpr (EXACT) g.T = TMAX;
     const int G = g.C / V;
     const long long n_vec = (long long)g.B * g.OH * g.OW * G;
     const long long first = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -319,9 +329,15 @@ std::tuple<at::Tensor, at::Tensor> bn_pool_lif_forward(const at::Tensor& y, cons
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
     SJ_POOL_DISPATCH(y.scalar_type(), {
         SJ_POOL_KIND(kind, {
-            bn_pool_lif_forward_kernel<scalar_t, KIND><<<grid, kThreads, 0, stream>>>(
-                p, g, reinterpret_cast<const scalar_t*>(y.data_ptr()), scale.data_ptr<float>(), shift.data_ptr<float>(),
-                reinterpret_cast<scalar_t*>(out.data_ptr()), idx.data_ptr<uint8_t>());
+            auto launch = [&](auto kern) {
+                kern<<<grid, kThreads, 0, stream>>>(
+                    p, g, reinterpret_cast<const scalar_t*>(y.data_ptr()), scale.data_ptr<float>(), shift.data_ptr<float>(),
+                    reinterpret_cast<scalar_t*>(out.data_ptr()), idx.data_ptr<uint8_t>());
+            };
+            if (T == 4 && is_static) launch(bn_pool_lif_forward_kernel<scalar_t, KIND, 4, true>);
+            else if (T == 4) launch(bn_pool_lif_forward_kernel<scalar_t, KIND, 4, false>);
+            else if (is_static) launch(bn_pool_lif_forward_kernel<scalar_t, KIND, 0, true>);
+            else launch(bn_pool_lif_forward_kernel<scalar_t, KIND, 0, false>);
         });
     });
     C10_CUDA_KERNEL_LAUNCH_CHECK();
@@ -358,16 +374,22 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> bn_pool_lif_backward(
     const float* gam = (gamma.has_value() && gamma->defined()) ? gamma->data_ptr<float>() : nullptr;
     SJ_POOL_DISPATCH(y.scalar_type(), {
         SJ_POOL_KIND(kind, {
-            if (T <= 4)
-                bn_pool_lif_backward1_kernel<scalar_t, KIND, 4><<<grid1, kThreads, kThreads * 2 * V * sizeof(float), stream>>>(
+            auto launch = [&](auto kern) {
+                kern<<<grid1, kThreads, kThreads * 2 * V * sizeof(float), stream>>>(
                     p, g, reinterpret_cast<const scalar_t*>(y.data_ptr()), idx.data_ptr<uint8_t>(),
                     reinterpret_cast<const scalar_t*>(go.data_ptr()), scale.data_ptr<float>(), shift.data_ptr<float>(),
                     reinterpret_cast<scalar_t*>(Gt.data_ptr()), partial.data_ptr<float>());
-            else
-                bn_pool_lif_backward1_kernel<scalar_t, KIND, 8><<<grid1, kThreads, kThreads * 2 * V * sizeof(float), stream>>>(
-                    p, g, reinterpret_cast<const scalar_t*>(y.data_ptr()), idx.data_ptr<uint8_t>(),
-                    reinterpret_cast<const scalar_t*>(go.data_ptr()), scale.data_ptr<float>(), shift.data_ptr<float>(),
-                    reinterpret_cast<scalar_t*>(Gt.data_ptr()), partial.data_ptr<float>());
+            };
+            if (T == 4) {
+                if (is_static) launch(bn_pool_lif_backward1_kernel<scalar_t, KIND, 4, true, true>);
+                else launch(bn_pool_lif_backward1_kernel<scalar_t, KIND, 4, true, false>);
+            } else if (T < 4) {
+                if (is_static) launch(bn_pool_lif_backward1_kernel<scalar_t, KIND, 4, false, true>);
+                else launch(bn_pool_lif_backward1_kernel<scalar_t, KIND, 4, false, false>);
+            } else {
+                if (is_static) launch(bn_pool_lif_backward1_kernel<scalar_t, KIND, 8, false, true>);
+                else launch(bn_pool_lif_backward1_kernel<scalar_t, KIND, 8, false, false>);
+            }
         });
     });
     C10_CUDA_KERNEL_LAUNCH_CHECK();

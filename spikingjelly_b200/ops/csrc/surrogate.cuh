@@ -47,6 +47,12 @@ __device__ __forceinline__ float surrogate_grad(int id, float x, float p0, float
 template <int ID>
 __device__ __forceinline__ float surrogate_grad(float x, float p0, float p1) { return surrogate_grad(ID, x, p0, p1); }
 
+// Out-of-line copy of the full table for the rarely used surrogates: one body per translation
+// unit instead of one per unrolled call site (the inlined table dominated compile time and code size).
+static __device__ __noinline__ float surrogate_grad_outlined(int id, float x, float p0, float p1) {
+    return surrogate_grad(id, x, p0, p1);
+}
+
 // In-place g'(x) for V values.  The two surrogates used by every shipped model get
 // branch-free bodies; the switch for the rest is taken once per call, not per element.
 template <int V>
@@ -60,7 +66,7 @@ __device__ __forceinline__ void surrogate_grad_vec(int id, float (&x)[V], float 
         for (int j = 0; j < V; ++j) { const float s = __fdividef(1.0f, 1.0f + __expf(-p0 * x[j])); x[j] = (1.0f - s) * s * p0; }
     } else {
 #pragma unroll
-        for (int j = 0; j < V; ++j) x[j] = surrogate_grad(id, x[j], p0, p1);
+        for (int j = 0; j < V; ++j) x[j] = surrogate_grad_outlined(id, x[j], p0, p1);
     }
 }
 
