@@ -1,0 +1,122 @@
+"""Model zoo shapes / state-dict layouts and one tiny end-to-end run of the classification trainer."""
+import os
+
+import pytest
+import torch
+import torch.nn as nn
+
+from spikingjelly_b200.activation_based import functional, layer, neuron, surrogate
+from spikingjelly_b200.activation_based.model import parametric_lif_net, sew_resnet, spiking_resnet, spiking_vgg
+from spikingjelly_b200.models import train_classify
+
+
+def test_alias_package_resolves_to_the_same_modules():
+    import spikingjelly_b200.activation_based.model.sew_resnet as a
+    import spikingjelly_b200.models.sew_resnet as b
+    assert a is b and a is sew_resnet
+
+
+@pytest.mark.parametrize("factory,kw", [(sew_resnet.sew_resnet18, dict(cnf="ADD")), (sew_resnet.sew_resnet50, dict(cnf="AND")),
+                                        (spiking_resnet.spiking_resnet18, {}), (spiking_resnet.spiking_wide_resnet50_2, {})])
+def test_resnets_keep_torchvision_state_dict_layout(factory, kw):
+    import torchvision
+    net = factory(spiking_neuron=neuron.IFNode, surrogate_function=surrogate.ATan(), detach_reset=True, **kw)
+    tv = getattr(torchvision.models, factory.__name__.replace("sew_", "").replace("spiking_", ""))()
+    assert list(net.state_dict().keys()) == list(tv.state_dict().keys())
+    assert [v.shape for v in net.state_dict().values()] == [v.shape for v in tv.state_dict().values()]
+
+
+def test_sew_resnet_event_input_and_step_modes():
+    net = sew_resnet.sew_resnet18(spiking_neuron=neuron.LIFNode, surrogate_function=surrogate.ATan(), cnf="ADD",
+                                  num_classes=11, in_channels=2)
+    x = (torch.rand(3, 2, 2, 64, 64) < 0.1).float()
+    net.eval()
+    with torch.no_grad():
+        y_s = torch.stack([net(x[t]) for t in range(3)])
+        functional.reset_net(net)
+        functional.set_step_mode(net, "m")
+        y_m = net(x)
+    assert y_m.shape == (3, 2, 11) and torch.allclose(y_s, y_m, atol=1e-5)
+    with pytest.raises(NotImplementedError):
+        sew_resnet.sew_function(x, x, "XOR")
+
+
+def test_vgg_and_plif_nets():
+    import torchvision
+    net = spiking_vgg.spiking_vgg11_bn(spiking_neuron=neuron.IFNode, num_classes=10)
+    assert list(net.state_dict().keys()) == list(torchvision.models.vgg11_bn(num_classes=10).state_dict().keys())
+    x = torch.rand(2, 3, 32, 32)
+    assert net(x).shape == (2, 10)
+    functional.reset_net(net)
+    single = spiking_vgg.sequential_forward(nn.Sequential(layer.Linear(4, 4), neuron.IFNode()), torch.rand(3, 2, 4))
+    assert single.shape == (3, 2, 4)
+    for cls, shape, out in [(parametric_lif_net.MNISTNet, (2, 1, 28, 28), 10), (parametric_lif_net.NMNISTNet, (2, 2, 32, 32), 10),
+                            (parametric_lif_net.CIFAR10Net, (2, 3, 32, 32), 10), (parametric_lif_net.DVSGestureNet, (2, 2, 128, 128), 11)]:
+        m = cls(8, neuron.ParametricLIFNode, surrogate_function=surrogate.ATan())
+        assert m(torch.rand(shape)).shape == (2, out)
+
+
+class _TinyTrainer(train_classify.Trainer):
+    def load_data(self, args):
+        import torchvision
+        tf = torchvision.transforms.ToTensor()
+        train = torchvision.datasets.FakeData(32, (3, 16, 16), 4, transform=tf)
+        test = torchvision.datasets.FakeData(16, (3, 16, 16), 4, transform=tf, random_offset=7)
+        train.classes = test.classes = list(range(4))
+        return (train, test, *self._samplers(args, train, test))
+
+    def load_model(self, args, num_classes):
+        net = nn.Sequential(layer.Flatten(), layer.Linear(3 * 16 * 16, 32), neuron.LIFNode(surrogate_function=surrogate.ATan()),
+                            layer.Linear(32, num_classes))
+        functional.set_step_mode(net, "m")
+        return net
+
+    def preprocess_train_sample(self, args, x):
+        return x.unsqueeze(0).repeat(args.T, 1, 1, 1, 1)
+
+    preprocess_test_sample = preprocess_train_sample
+
+    def process_model_output(self, args, y):
+        return y.mean(0)
+
+    def get_args_parser(self, add_help=True):
+        p = super().get_args_parser(add_help)
+        p.add_argument("--T", type=int, default=2)
+        return p
+
+
+def test_trainer_runs_resumes_and_checkpoints(tmp_path):
+    torch.use_deterministic_algorithms(False)
+    t = _TinyTrainer()
+    common = ["--device", "cpu", "--epochs", "2", "-b", "8", "-j", "0", "--output-dir", str(tmp_path), "--opt", "adamw",
+              "--lr", "0.01", "--lr-warmup-epochs", "1", "--disable-uda", "--model-ema", "--model-ema-steps", "1", "--T", "2"]
+    args = t.get_args_parser().parse_args(common)
+    t.main(args)
+    pt_dir = os.path.join(str(tmp_path), "pt", t.get_tb_logdir_name(args))
+    names = set(os.listdir(pt_dir))
+    assert {"checkpoint_latest.pth", "checkpoint_1.pth", "checkpoint_max_test_acc1.pth"} <= names and "checkpoint_0.pth" not in names
+    ckpt = torch.load(os.path.join(pt_dir, "checkpoint_latest.pth"), weights_only=False)
+    assert ckpt["epoch"] == 1 and {"model", "optimizer", "lr_scheduler", "args", "max_test_acc1", "model_ema"} <= set(ckpt)
+    assert not any("v" == k.split(".")[-1] for k in ckpt["model"])          # neuron state is never serialised
+    latest = os.path.join(pt_dir, "checkpoint_latest.pth")
+    args = t.get_args_parser().parse_args(common[:3] + ["3"] + common[4:] + ["--resume", latest])    # one more epoch
+    t.main(args)
+    pt_dir3 = os.path.join(str(tmp_path), "pt", t.get_tb_logdir_name(args))
+    assert torch.load(os.path.join(pt_dir3, "checkpoint_latest.pth"), weights_only=False)["epoch"] == 2
+    args = t.get_args_parser().parse_args(common + ["--resume", "latest", "--test-only"])
+    t.main(args)
+    torch.use_deterministic_algorithms(False)
+
+
+def test_trainer_factories():
+    t = train_classify.Trainer()
+    args = t.get_args_parser().parse_args(["--opt", "sgd_nesterov", "--lr-scheduler", "step", "--lr-warmup-epochs", "0"])
+    lin = nn.Linear(2, 2)
+    opt = t.set_optimizer(args, lin.parameters())
+    assert isinstance(opt, torch.optim.SGD) and opt.defaults["nesterov"]
+    assert isinstance(t.set_lr_scheduler(args, opt), torch.optim.lr_scheduler.StepLR)
+    args.opt = "lamb"
+    with pytest.raises(RuntimeError, match="Invalid optimizer"):
+        t.set_optimizer(args, lin.parameters())
+    with pytest.raises(NotImplementedError):
+        t.load_model(args, 10)
