@@ -64,6 +64,19 @@ def main():
                    "ours_tflops": round(flops / t_o / 1e6, 1), "cublas_tflops": round(flops / t_r / 1e6, 1)}
             print(json.dumps(row), flush=True)
             rows.append(row)
+        # fp8 forward (e4m3 x e4m3 -> bf16) against torch._scaled_mm (cuBLASLt fp8)
+        from spikingjelly_b200.ops import fp8
+        xq, wq = x.to(torch.float8_e4m3fn), w.to(torch.float8_e4m3fn)
+        one = torch.ones(1, device=dev)
+        t_o = timeit(lambda: fp8.matmul_nt(xq, wq, one), flush, a.iters)
+        try:
+            t_r = timeit(lambda: torch._scaled_mm(xq, wq.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16), flush, a.iters)
+        except Exception:
+            t_r = float("nan")
+        row = {"shape": name, "op": "fwd_fp8", "M": m, "N": n, "K": k, "ours_us": round(t_o, 1), "cublas_us": round(t_r, 1),
+               "ours_tflops": round(flops / t_o / 1e6, 1), "cublas_tflops": round(flops / t_r / 1e6, 1)}
+        print(json.dumps(row), flush=True)
+        rows.append(row)
         G.check_status(x)
     if a.out:
         Path(a.out).parent.mkdir(parents=True, exist_ok=True)

@@ -51,10 +51,14 @@ struct GemmArgs {
     int split_k;            // >= 1
     int kb_per_split;       // k-blocks (of BK) per split
     int out_f32;            // D is fp32 (always when split_k > 1)
-    int ab_format;          // 0 = fp16, 1 = bf16
+    int ab_format;          // kind::f16: 0 = fp16, 1 = bf16;  kind::f8f6f4: 0 = e4m3, 1 = e5m2 (A and B alike)
+    int out_bf16;           // 16-bit results are bf16 (else fp16)
+    const float* alpha;     // optional device scalar multiplied into the result (product of the fp8 scales)
 };
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+// ES: operand element size in bytes (2: fp16 / bf16, 1: fp8).  A k-block is always one 128-byte
+// swizzle row, i.e. 128 / ES elements, and is consumed by four MMAs of 32 bytes of K each.
+template <int BN, int STAGES, bool A_MN, bool B_MN, int ES = 2>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmD, void* __restrict__ Dptr, GemmArgs g, KernelStatus* __restrict__ status) {
@@ -72,7 +76,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
     const int tiles_mn = tiles_m * tiles_n;
     const int total_tiles = tiles_mn * g.split_k;
-    const int kb_total = (g.K + BK - 1) / BK;
+    constexpr int BKE = 128 / ES;              // elements per k-block
+    static_assert(ES == 2 || (!A_MN && !B_MN), "8-bit operands are K-major only");
+    const int kb_total = (g.K + BKE - 1) / BKE;
+    const float alpha = g.alpha != nullptr ? __ldg(g.alpha) : 1.0f;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
@@ -107,7 +114,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     uint8_t* sa = smem + s * L::STAGE_BYTES;
                     uint8_t* sb = sa + L::A_BYTES;
                     mbar_expect_tx(full_bar + s, L::STAGE_BYTES);
-                    const int k0 = kb * BK;
+                    const int k0 = kb * BKE;
                     if (A_MN) {
 #pragma unroll
                         for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmA, m0 + c * 64, k0, full_bar + s);
@@ -151,7 +158,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                                  : make_smem_desc(sa + j * (UMMA_K * 2), 16, 1024);
                         const uint64_t db = B_MN ? make_smem_desc(sb + j * (UMMA_K * 128), BK * 128, 1024)
                                                  : make_smem_desc(sb + j * (UMMA_K * 2), 16, 1024);
-                        mma_f16_ss(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+                        if constexpr (ES == 2) mma_f16_ss(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+                        else mma_f8_ss(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
                     }
                     mma_commit(empty_bar + s);     // stage reusable once these MMAs have read it
                 }
@@ -178,6 +186,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + c * 32, r);
                 tmem_ld_wait();
+                if (g.alpha != nullptr) {
+#pragma unroll
+                    for (int q = 0; q < 32; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) * alpha);
+                }
                 const int col0 = n0 + c * 32;
                 if (row < g.M && col0 < g.N) {
                     if (g.out_f32) {
@@ -206,7 +218,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const float lo = __uint_as_float(r[8 * q + 2 * e]), hi = __uint_as_float(r[8 * q + 2 * e + 1]);
-                            if (g.ab_format == 1) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
+                            if (g.out_bf16) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
                             else { __half2 v = __floats2half2_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
                         }
                         const int chunk = q ^ ((r_in_tile >> 1) & 3);
@@ -279,6 +291,22 @@ EncodeFn encode_fn() {
 
 // 2-D map over a row-major [rows, cols] 16-bit matrix with `ld` elements per row; box = [box_rows, box_cols];
 // box_cols * 2 bytes must equal the swizzle span (128 B or 64 B).
+// Same for a [rows, cols] matrix of bytes (fp8): box = [box_rows, 128 bytes], 128-byte swizzle.
+CUtensorMap make_map_u8(const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(base) % 16 == 0, "TMA: base address must be 16-byte aligned");
+    TORCH_CHECK(ld % 16 == 0, "TMA: row pitch must be a multiple of 16 bytes (fp8 leading dimension % 16 == 0)");
+    CUtensorMap m;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld};
+    cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+    return m;
+}
+
 CUtensorMap make_map(const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, bool bf16, int box_cols = 64) {
     TORCH_CHECK(reinterpret_cast<uintptr_t>(base) % 16 == 0, "TMA: base address must be 16-byte aligned");
     TORCH_CHECK((ld * 2) % 16 == 0, "TMA: row pitch must be a multiple of 16 bytes (leading dimension % 8 == 0)");
@@ -303,11 +331,11 @@ at::Tensor& status_word(const at::Device& dev) {
     return w;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int ES = 2>
 void launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, void* d, const GemmArgs& g,
             KernelStatus* st, int grid, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
-    auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN>;
+    auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, ES>;
     static bool configured = false;
     if (!configured) {
         C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
@@ -357,6 +385,8 @@ at::Tensor gemm_16bit(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool 
     g.split_k = splits; g.kb_per_split = kb_per;
     g.out_f32 = (out_f32 || splits > 1) ? 1 : 0;
     g.ab_format = bf16 ? 1 : 0;
+    g.out_bf16 = bf16 ? 1 : 0;
+    g.alpha = nullptr;
 
     const CUtensorMap ta = a_mn ? make_map(A.data_ptr(), K, M, A.stride(0), BK, bf16)
                                 : make_map(A.data_ptr(), M, K, A.stride(0), BM, bf16);
@@ -401,6 +431,74 @@ at::Tensor gemm_16bit(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool 
     return out;
 }
 
+// D[M, N] (bf16) = alpha * A[M, K] (.) B[N, K]^T with fp8 operands (both e4m3 or both e5m2, K contiguous) and fp32
+// accumulation on the tensor cores.  `alpha`: optional fp32 device scalar (the product of the two
+// de-quantisation scales), multiplied in the epilogue so that no host synchronisation is needed.
+at::Tensor gemm_fp8(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& alpha, bool out_f32,
+                    int64_t split_k) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2, "gemm_fp8: 2-D CUDA operands required");
+    const bool e4m3 = a.scalar_type() == at::kFloat8_e4m3fn, e5m2 = a.scalar_type() == at::kFloat8_e5m2;
+    TORCH_CHECK((e4m3 || e5m2) && a.scalar_type() == b.scalar_type(), "gemm_fp8: both operands must be float8_e4m3fn or both float8_e5m2");
+    const c10::cuda::CUDAGuard guard(a.device());
+    C10_CUDA_CHECK(cudaFree(nullptr));
+    at::Tensor A = a.stride(1) == 1 ? a : a.contiguous();
+    at::Tensor B = b.stride(1) == 1 ? b : b.contiguous();
+    const int64_t M = A.size(0), K = A.size(1), N = B.size(0);
+    TORCH_CHECK(B.size(1) == K, "gemm_fp8: contraction sizes differ (", K, " vs ", B.size(1), ")");
+    TORCH_CHECK(N % 8 == 0 && K % 16 == 0, "gemm_fp8: N must be a multiple of 8 and K a multiple of 16");
+    constexpr int BKE = 128;
+    const int BN = N > 128 ? 256 : 128;
+    const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
+    const int kb_total = (int)((K + BKE - 1) / BKE);
+    const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    int splits = (int)split_k;
+    if (splits <= 0) {
+        splits = 1;
+        if (tiles * 2 <= sms && kb_total >= 16) splits = std::min(std::max(1, sms / tiles), kb_total / 4);
+    }
+    splits = std::max(1, std::min(splits, kb_total));
+    const int kb_per = (kb_total + splits - 1) / splits;
+    splits = (kb_total + kb_per - 1) / kb_per;
+
+    GemmArgs g{};
+    g.M = (int)M; g.N = (int)N; g.K = (int)K; g.ldd = (int)N;
+    g.split_k = splits; g.kb_per_split = kb_per;
+    g.out_f32 = (out_f32 || splits > 1) ? 1 : 0;
+    g.ab_format = e4m3 ? 0 : 1;
+    g.out_bf16 = 1;
+    g.alpha = nullptr;
+    if (alpha.has_value() && alpha->defined()) {
+        TORCH_CHECK(alpha->is_cuda() && alpha->scalar_type() == at::kFloat && alpha->numel() == 1, "gemm_fp8: alpha must be one fp32 value on the device");
+        g.alpha = alpha->data_ptr<float>();
+    }
+    const CUtensorMap ta = make_map_u8(A.data_ptr(), M, K, A.stride(0), BM);
+    const CUtensorMap tb = make_map_u8(B.data_ptr(), N, K, B.stride(0), BN);
+    auto opts = a.options();
+    at::Tensor out = at::empty({M, N}, opts.dtype(out_f32 ? at::kFloat : at::kBFloat16));
+    at::Tensor scratch;
+    void* dptr = out.data_ptr();
+    if (splits > 1) {
+        scratch = at::empty({splits, M, N}, opts.dtype(at::kFloat));
+        dptr = scratch.data_ptr();
+    }
+    const CUtensorMap td = g.out_f32 ? ta : make_map(out.data_ptr(), M, N, N, BM, true, 32);
+    at::Tensor& st = status_word(a.device());
+    KernelStatus* stp = reinterpret_cast<KernelStatus*>(st.data_ptr<int>());
+    const int grid = std::min(tiles * splits, sms);
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    if (BN == 256) launch<256, 4, false, false, 1>(ta, tb, td, dptr, g, stp, grid, stream);
+    else launch<128, 6, false, false, 1>(ta, tb, td, dptr, g, stp, grid, stream);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    if (splits > 1) {
+        const long long mn = (long long)M * N;
+        const unsigned blocks = (unsigned)((mn / 4 + 256) / 256);
+        if (out_f32) splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(scratch.data_ptr<float>(), out.data_ptr<float>(), mn, splits, 0.f, nullptr);
+        else splitk_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(scratch.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), mn, splits, 0.f, nullptr);
+        C10_CUDA_KERNEL_LAUNCH_CHECK();
+    }
+    return out;
+}
+
 // (code, block, detail) of the first bounded wait that gave up since the last call; resets it.
 std::vector<int64_t> gemm_status(const at::Tensor& like) {
     at::Tensor& st = status_word(like.device());
@@ -414,9 +512,11 @@ std::vector<int64_t> gemm_status(const at::Tensor& like) {
 
 TORCH_LIBRARY_FRAGMENT(sjb200, m) {
     m.def("gemm_16bit(Tensor a, Tensor b, bool a_mn, bool b_mn, bool out_f32, int split_k) -> Tensor");
+    m.def("gemm_fp8(Tensor a, Tensor b, Tensor? alpha, bool out_f32, int split_k) -> Tensor");
     m.def("gemm_status(Tensor like) -> int[]");
 }
 TORCH_LIBRARY_IMPL(sjb200, CUDA, m) {
     m.impl("gemm_16bit", &sjb200::gemm_16bit);
+    m.impl("gemm_fp8", &sjb200::gemm_fp8);
     m.impl("gemm_status", &sjb200::gemm_status);
 }
