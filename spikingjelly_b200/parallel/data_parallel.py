@@ -27,7 +27,7 @@ from torch.nn.parallel import DistributedDataParallel
 
 from .comm import SymmetricBucket
 
-__all__ = ["SNNDataParallel", "prepare_snn_data_parallel", "unwrap_parallel_module"]
+__all__ = ["SNNDataParallel", "prepare_snn_data_parallel", "unwrap_parallel_module", "materialize_dtensor_output"]
 
 
 class _Bucket:
@@ -169,3 +169,19 @@ def prepare_snn_data_parallel(module: nn.Module, process_group=None, device_ids:
 
 def unwrap_parallel_module(module: nn.Module) -> nn.Module:
     return module.module if isinstance(module, (DistributedDataParallel, SNNDataParallel)) else module
+
+
+def materialize_dtensor_output(output):
+    """Gather sharded (DTensor-like: anything with ``full_tensor()``) outputs, recursively through
+    tuples, named tuples, lists and dicts; other values pass through."""
+    full = getattr(output, "full_tensor", None)
+    if callable(full):
+        return full()
+    if isinstance(output, tuple):
+        items = [materialize_dtensor_output(o) for o in output]
+        return output.__class__(*items) if hasattr(output, "_fields") else tuple(items)
+    if isinstance(output, list):
+        return [materialize_dtensor_output(o) for o in output]
+    if isinstance(output, dict):
+        return {k: materialize_dtensor_output(v) for k, v in output.items()}
+    return output
