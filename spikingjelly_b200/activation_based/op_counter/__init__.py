@@ -1,0 +1,4 @@
+"""Operation, memory-traffic and energy accounting of (spiking) networks."""
+from .base import *  # noqa: F401,F403
+from .compute_energy import *  # noqa: F401,F403
+from .counters import *  # noqa: F401,F403
