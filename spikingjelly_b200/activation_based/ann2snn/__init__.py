@@ -1,0 +1,15 @@
+"""ANN-to-SNN conversion: converters, recipes (rate coding, local threshold balancing, exact
+temporal-difference conversion of transformers), calibration modules and TD operators."""
+from . import operators
+from .converter import Converter, FXConverter, ModuleConverter
+from .delay import estimate_delay_start
+from .factories import NeuronFactory
+from .modules import ChannelVoltageScaler, VoltageHook, VoltageScaler
+from .qcfs import SignedQCFSSequenceEncoder
+from .recipes import (ConversionRecipe, FXConversionRecipe, LocalThresholdBalancingRecipe, ModuleConversionRecipe, RateCodingRecipe,
+                      TransformerTDEquivalentRecipe)
+from .utils import download_url
+
+__all__ = ["Converter", "FXConverter", "ModuleConverter", "ConversionRecipe", "FXConversionRecipe", "ModuleConversionRecipe",
+           "RateCodingRecipe", "LocalThresholdBalancingRecipe", "TransformerTDEquivalentRecipe", "ChannelVoltageScaler", "VoltageHook",
+           "VoltageScaler", "download_url", "NeuronFactory", "operators", "SignedQCFSSequenceEncoder", "estimate_delay_start"]

@@ -1,0 +1,7 @@
+from .base import ConversionRecipe, FXConversionRecipe, ModuleConversionRecipe
+from .local_threshold_balancing import LocalThresholdBalancingRecipe
+from .rate_coding import RateCodingRecipe
+from .transformer_td_equivalent import TransformerTDEquivalentRecipe
+
+__all__ = ["ConversionRecipe", "FXConversionRecipe", "ModuleConversionRecipe", "LocalThresholdBalancingRecipe", "RateCodingRecipe",
+           "TransformerTDEquivalentRecipe"]
