@@ -8,3 +8,4 @@ from .psn import *  # noqa: F401,F403
 from .training_variants import *  # noqa: F401,F403
 from .conversion import *  # noqa: F401,F403
 from .population import *  # noqa: F401,F403
+from .flexsn import *  # noqa: F401,F403
