@@ -170,9 +170,9 @@ def test_kernel_lif_equals_builtin_lif_and_counts_launches():
     m = FlexSN(lif_core, 1, 1, 1, backend="triton")
     ref = neuron.LIFNode(tau=2.0, surrogate_function=surrogate.Sigmoid(), step_mode="m", backend="cuda")
     xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
-    before = counters.snapshot().get("flexsn_forward", 0)
+    before = counters.by_name().get("flexsn_forward", 0)
     ya, yb = m(xa), ref(xb)
-    assert counters.snapshot().get("flexsn_forward", 0) == before + 1
+    assert counters.by_name().get("flexsn_forward", 0) == before + 1
     assert torch.equal(ya, yb)
     g = torch.randn_like(ya)
     ya.backward(g)
