@@ -3,8 +3,8 @@
 //   spike_gemm:  D[M, N] = S[M, K] . W[N, K]^T      S = spikes, stored as 1 bit per element
 //
 // * The A operand never exists as 16-bit data in global memory.  Four "expander" warps read the packed bits of
-//   their 128 rows with plain loads, look every byte up in a 256-entry table (8 bf16 values) kept in shared
-//   memory and write the 128-byte-swizzled K-major tile that tcgen05.mma expects; the weights arrive by TMA.
+//   their 128 rows with plain loads, turn every pair of bits into two bf16 values with integer arithmetic and
+//   write the 128-byte-swizzled K-major tile that tcgen05.mma expects; the weights arrive by TMA.
 //   The rows of one 128-row tile may live on ANOTHER GPU: the tile's base pointer is taken from a table of
 //   peer-mapped symmetric buffers.  That is the all-gather of a column-parallel layer, moved into the GEMM's
 //   operand fetch with a payload of 1 bit per activation (each CTA fetches the rows it needs itself; no TMA
@@ -36,7 +36,7 @@ using namespace tc;
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 320;       // warps: 0 TMA(B), 1 MMA, 2-5 epilogue, 6-9 A expanders
+constexpr int kThreads = 448;       // warps: 0 TMA(B), 1 MMA, 2-5 epilogue, 6-9 A expanders (even k-blocks), 10-13 (odd)
 constexpr int kMaxRanks = 8;
 
 template <int BN, int STAGES>
@@ -44,8 +44,7 @@ struct Smem {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int LUT_OFFSET = STAGES * STAGE_BYTES;          // 256 x 16 B
-    static constexpr int BAR_OFFSET = LUT_OFFSET + 4096;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
     static constexpr int TOTAL = BAR_OFFSET + 1024 + 1024;            // + slack for 1024 B alignment
 };
 
@@ -77,31 +76,21 @@ spike_gemm_kernel(const __grid_constant__ CUtensorMap tmB, const SpikeGemmArgs g
     using L = Smem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint4* lut = reinterpret_cast<uint4*>(smem + L::LUT_OFFSET);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* tfull_bar = empty_bar + STAGES;
     uint64_t* tempty_bar = tfull_bar + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    volatile int* exp_ok = abort_flag + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
     const int total_tiles = tiles_m * tiles_n;
     const int kb_total = (g.K + BK - 1) / BK;
 
-    // byte -> 8 bf16 (1.0 = 0x3F80), bit i of the byte = element i
-    if (threadIdx.x < 256) {
-        const uint32_t b = threadIdx.x;
-        uint32_t w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) w[j] = ((b >> (2 * j)) & 1u) * 0x3F80u + ((b >> (2 * j + 1)) & 1u) * 0x3F800000u;
-        lut[b] = make_uint4(w[0], w[1], w[2], w[3]);
-    }
     if (threadIdx.x == 0) {
-        // full: one arrival from the TMA thread (with the byte count) + one from the expanders
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 2); mbar_init(empty_bar + s, 1); }
+        // full: one arrival from the TMA thread (with the byte count) + one from each of the four expander warps
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 5); mbar_init(empty_bar + s, 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar + a, 1); mbar_init(tempty_bar + a, 4); }
         *abort_flag = 0;
         mbar_init_fence();
@@ -157,48 +146,61 @@ spike_gemm_kernel(const __grid_constant__ CUtensorMap tmB, const SpikeGemmArgs g
         }
     } else if (warp >= 6) {
         // -------------------------------------------------------------- A expanders: bits -> swizzled bf16 tile
-        const int r = threadIdx.x - 192;                 // row of the tile owned by this thread
+        // Two groups of four warps take the even and the odd k-blocks.  Inside a group each warp owns 32 rows and
+        // reports to the stage barrier on its own (no block-wide rendezvous).  A thread
+        // reads its row 32 bytes (= 4 k-blocks) at a time and keeps two such groups in flight ahead of the one
+        // it expands, which covers the latency of a peer load over NVLink.
+        const int r = (threadIdx.x - 192) & 127;         // row of the tile owned by this thread
+        const int parity = (threadIdx.x - 192) >> 7;     // which k-blocks this thread expands
         const uint32_t swz = (uint32_t)(r & 7);
+        const int groups = (kb_total + 3) >> 2;
         uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+        bool dead = false;
+        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag && !dead; tile += gridDim.x) {
             const int m0 = (tile / tiles_n) * BM;
             int src; long long local_row;
             locate(g, g.world > 1, m0, src, local_row);
             const bool live = m0 + r < g.M;
-            const uint8_t* rowp = g.a_src[src] + (local_row + r) * g.a_pitch;
-            uint4 cache0 = make_uint4(0, 0, 0, 0), cache1 = cache0;
-            bool dead = false;
-            for (int kb = 0; kb < kb_total; ++kb, ++it) {
-                const int s = it % STAGES;
-                if ((kb & 3) == 0) {
-                    // 32 bytes = 4 k-blocks of this row in one sector; issued before the wait to overlap it
-                    if (live) {
-                        const uint4* p = reinterpret_cast<const uint4*>(rowp + (size_t)(kb >> 2) * 32);
-                        cache0 = __ldg(p);
-                        cache1 = __ldg(p + 1);
-                    }
-                }
-                // one thread waits for the stage and tells the other 127, so that all of them leave together on expiry
-                if (threadIdx.x == 192) {
-                    const bool ok = mbar_wait_bounded(empty_bar + s, ((it / STAGES) & 1) ^ 1);
-                    if (!ok) { report(status, WAIT_EMPTY, 100 + s); *abort_flag = 1; }
-                    *exp_ok = ok ? 1 : 0;
-                }
-                named_barrier(3, 128);
-                if (!*exp_ok) { dead = true; break; }
-                const uint4 c4 = ((kb >> 1) & 1) ? cache1 : cache0;
-                const uint32_t w0 = (kb & 1) ? c4.z : c4.x, w1 = (kb & 1) ? c4.w : c4.y;
-                uint8_t* arow = smem + s * L::STAGE_BYTES + r * 128;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint32_t byte = ((c < 4 ? w0 : w1) >> (8 * (c & 3))) & 0xFFu;
-                    *reinterpret_cast<uint4*>(arow + ((c ^ swz) << 4)) = lut[byte];
-                }
-                fence_async_smem();                     // generic-proxy writes -> visible to the tensor core's async proxy
-                named_barrier(2, 128);
-                if (threadIdx.x == 192) mbar_arrive(full_bar + s);
+            const uint4* rowp = reinterpret_cast<const uint4*>(g.a_src[src] + (local_row + r) * g.a_pitch);
+            const uint4 zero4 = make_uint4(0, 0, 0, 0);
+            uint4 c0 = zero4, c1 = zero4, n0 = zero4, n1 = zero4, f0 = zero4, f1 = zero4;   // current, next, after next
+            if (live) {
+                c0 = __ldcg(rowp); c1 = __ldcg(rowp + 1);
+                if (groups > 1) { n0 = __ldcg(rowp + 2); n1 = __ldcg(rowp + 3); }
             }
-            if (dead) break;
+            int kb = 0;
+            for (int grp = 0; grp < groups && !dead; ++grp) {
+                if (live && grp + 2 < groups) { f0 = __ldcg(rowp + 2 * (grp + 2)); f1 = __ldcg(rowp + 2 * (grp + 2) + 1); }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (kb >= kb_total) break;
+                    if ((j & 1) != parity) { ++kb; ++it; continue; }
+                    const int s = it % STAGES;
+                    bool ok = true;
+                    if (lane == 0) ok = mbar_wait_bounded(empty_bar + s, ((it / STAGES) & 1) ^ 1);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) { if (lane == 0) { report(status, WAIT_EMPTY, 100 + s); *abort_flag = 1; } dead = true; break; }
+                    const uint4 c4 = (j & 2) ? c1 : c0;
+                    const uint32_t w0 = (j & 1) ? c4.z : c4.x, w1 = (j & 1) ? c4.w : c4.y;
+                    uint8_t* arow = smem + s * L::STAGE_BYTES + r * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const uint32_t byte = ((c < 4 ? w0 : w1) >> (8 * (c & 3))) & 0xFFu;
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t x = (byte >> (2 * e)) & 3u;            // two spikes
+                            w[e] = ((x * 0x8001u) & 0x00010001u) * 0x3F80u;        // -> two bf16 (1.0 = 0x3F80)
+                        }
+                        *reinterpret_cast<uint4*>(arow + ((c ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                    fence_async_smem();                  // generic-proxy writes -> visible to the tensor core's async proxy
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full_bar + s);
+                    ++kb; ++it;
+                }
+                c0 = n0; c1 = n1; n0 = f0; n1 = f1;
+            }
         }
     } else {
         // ---------------------------------------------------------------- epilogue
