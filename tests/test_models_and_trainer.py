@@ -120,3 +120,23 @@ def test_trainer_factories():
         t.set_optimizer(args, lin.parameters())
     with pytest.raises(NotImplementedError):
         t.load_model(args, 10)
+
+
+def test_ottt_vgg_family_builds_and_trains_online():
+    from spikingjelly_b200.activation_based.model import spiking_vggws_ottt as O
+    from spikingjelly_b200.activation_based import functional, layer
+    net = O.ottt_spiking_vggws(num_classes=10)
+    assert isinstance(net.features, layer.OTTTSequential) and sum(isinstance(m, layer.WSConv2d) for m in net.modules()) == 8
+    x = torch.rand(2, 3, 32, 32)
+    net.train()
+    total = 0.0
+    for _ in range(2):                                   # online: one backward per time step
+        y = net(x)
+        loss = y.square().mean()
+        loss.backward()
+        total += loss.item()
+    functional.reset_net(net)
+    assert y.shape == (2, 10) and net.features[0].weight.grad.abs().sum() > 0 and total > 0
+    full = O.ottt_spiking_vgg11_ws(num_classes=7)        # three-layer classifier with weight-standardised linears
+    assert full(torch.rand(1, 3, 32, 32)).shape == (1, 7)
+    assert [k for k in O.ottt_spiking_vgg16(num_classes=3).state_dict()][:2] == ["features.0.weight", "features.0.bias"]
