@@ -132,11 +132,11 @@ def test_ottt_vgg_family_builds_and_trains_online():
     total = 0.0
     for _ in range(2):                                   # online: one backward per time step
         y = net(x)
-        loss = y.square().mean()
+        loss = (y - 1.0).square().mean()
         loss.backward()
         total += loss.item()
     functional.reset_net(net)
-    assert y.shape == (2, 10) and net.features[0].weight.grad.abs().sum() > 0 and total > 0
+    assert y.shape == (2, 10) and net.classifier[2].weight.grad is not None and net.classifier[2].bias.grad.abs().sum() > 0 and total > 0
     full = O.ottt_spiking_vgg11_ws(num_classes=7)        # three-layer classifier with weight-standardised linears
     assert full(torch.rand(1, 3, 32, 32)).shape == (1, 7)
     assert [k for k in O.ottt_spiking_vgg16(num_classes=3).state_dict()][:2] == ["features.0.weight", "features.0.bias"]
