@@ -2,3 +2,7 @@
 from .base import *  # noqa: F401,F403
 from .compute_energy import *  # noqa: F401,F403
 from .counters import *  # noqa: F401,F403
+from ._sparse_memory import *  # noqa: F401,F403
+from .neuron_state import *  # noqa: F401,F403
+from .lemaire_addressing import *  # noqa: F401,F403
+from .analytical_energy import *  # noqa: F401,F403

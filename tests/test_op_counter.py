@@ -59,3 +59,56 @@ def test_energy_estimate_is_dominated_by_accumulates_for_spiking_layers():
     assert dense.counts["mac"] > rep.counts["mac"]            # analog input: the first convolution is all MACs
     cheap = O.estimate_compute_energy(net, spikes, config=O.ComputeEnergyConfig(cost_config=O.ComputeEnergyCostConfig.int8()))
     assert cheap.energy_total_pj < rep.energy_total_pj and "Global" in rep.breakdown_pj
+
+
+def test_neuron_state_counter_classifies_state_traffic():
+    from spikingjelly_b200.activation_based import functional, layer, neuron
+    from spikingjelly_b200.activation_based import op_counter as oc
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(layer.Linear(8, 16), neuron.LIFNode(tau=2.0), layer.Linear(16, 4), neuron.IFNode())
+    functional.set_step_mode(net, "m")
+    c = oc.NeuronStateCounter()
+    with oc.DispatchCounterMode([c]):
+        net(torch.rand(4, 3, 8) * 2)
+    m, p = c.get_metric_counts()["Global"], c.get_projection_counts()["Global"]
+    # LIF: (x - v) , * 1/tau, + v, reset ... per element and step; the IF neuron has no multiply except the reset
+    assert m["state_muls"] == 4 * 3 * 16 * 2 and m["state_comps"] == 4 * 3 * 16
+    assert m["spike_triggered_ops"] == m["state_reset_ops"] > 0 and m["timestep_dense_ops"] > 0
+    assert p["state_acc_like"] == m["state_adds"] + m["state_comps"] + m["state_select_ops"] + m["state_nonlinear_ops"]
+    assert p["potential_buffer_bytes"] == 3 * 16 * 4 and p["read_potential"] == m["state_reads"]
+    assert set(c.get_metric_counts()) >= {"Global"} and c.get_extra_counts() == c.get_projection_counts()
+    c.reset()
+    assert c.get_metric_counts() == {}
+    native = neuron.LIFNode(step_mode="m")
+    native._backend = "cuda"                                         # kernels hide the state arithmetic from ATen
+    with pytest.warns(RuntimeWarning):
+        with oc.DispatchCounterMode([c]):
+            try:
+                native(torch.rand(2, 4))
+            except Exception:
+                pass
+    with pytest.raises(TypeError):
+        oc.NeuronStateCounter(extra_state_rules={neuron.IFNode: 3})
+
+
+def test_lemaire_energy_report_is_consistent():
+    from spikingjelly_b200.activation_based import functional, layer, neuron
+    from spikingjelly_b200.activation_based import op_counter as oc
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(layer.Conv2d(2, 4, 3, padding=1), neuron.LIFNode(), layer.Flatten(), layer.Linear(4 * 36, 16), neuron.IFNode(),
+                              layer.Linear(16, 4))
+    functional.set_step_mode(net, "m")
+    x = (torch.rand(4, 3, 2, 6, 6) > 0.6).float()
+    r = oc.estimate_lemaire_energy(net, x)
+    b = r.breakdown_pj
+    assert abs(r.total_pj - (b["ops_pj"] + b["addressing_pj"] + b["memory_pj"])) < 1e-6
+    assert abs(b["memory_pj"] - (b["inout_pj"] + b["params_pj"] + b["potential_pj"])) < 1e-6
+    spikes_in = int(x.count_nonzero())
+    assert r.counts["read_in_bytes"] >= spikes_in * 4 and r.counts["mac"] == 0 and r.counts["mac_addr"] == 2 * spikes_in
+    cost = oc.LemaireEnergyCostConfig()
+    assert cost.memory_cost_pj(0) == 0 and abs(cost.memory_cost_pj(8192) - 2.5) < 1e-9 and abs(cost.memory_cost_pj(1 << 30) - 25.0) < 1e-9
+    assert abs(cost.memory_cost_pj(20 * 1024) - (2.5 + 2.5 * 12 / 24)) < 1e-9
+    with pytest.raises(ValueError):
+        oc.LemaireEnergyCostConfig(memory_breakpoints=((0.0, 0.0), (1.0, 1.0), (1.0, 2.0), (3.0, 3.0)))
+    dense = oc.estimate_lemaire_energy(torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.ReLU(), torch.nn.Linear(8, 2)), torch.randn(5, 8))
+    assert dense.counts["mac"] == 5 * 8 * 8 + 5 * 8 * 2 and dense.counts["synop"] == 0 and dense.counts["read_potential_bytes"] == 0
