@@ -6,3 +6,4 @@ from ._sparse_memory import *  # noqa: F401,F403
 from .neuron_state import *  # noqa: F401,F403
 from .lemaire_addressing import *  # noqa: F401,F403
 from .analytical_energy import *  # noqa: F401,F403
+from .memory_residency import *  # noqa: F401,F403

@@ -112,3 +112,30 @@ def test_lemaire_energy_report_is_consistent():
         oc.LemaireEnergyCostConfig(memory_breakpoints=((0.0, 0.0), (1.0, 1.0), (1.0, 2.0), (3.0, 3.0)))
     dense = oc.estimate_lemaire_energy(torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.ReLU(), torch.nn.Linear(8, 2)), torch.randn(5, 8))
     assert dense.counts["mac"] == 5 * 8 * 8 + 5 * 8 * 2 and dense.counts["synop"] == 0 and dense.counts["read_potential_bytes"] == 0
+
+
+def test_memory_residency_hierarchy():
+    from spikingjelly_b200.activation_based import op_counter as oc
+    sim = oc.MemoryResidencySimulator(capacity_bits={"reg": 64 * 32, "sram": 256 * 32})
+    a, b, big = torch.zeros(32), torch.zeros(48), torch.zeros(512)
+    sim.on_tensor_read(a, "op")                          # dram -> sram -> reg
+    assert sim.get_move_bits_by_edge() == {"dram->sram": 1024, "sram->reg": 1024}
+    assert sim.get_level_rw_bits()["dram"] == {"read_bits": 1024, "write_bits": 0, "total_bits": 1024}
+    sim.on_tensor_read(a, "op")                          # register hit
+    assert sim.get_level_rw_bits()["reg"]["read_bits"] == 2048 and sim.get_move_bits_by_edge()["sram->reg"] == 1024
+    sim.on_tensor_read(b, "op")                          # evicts a from the register file back to SRAM (already resident there)
+    assert "reg->sram" in sim.get_move_bits_by_edge() and list(sim.reg_cache) == [sim._tensor_key(b)]
+    sim.on_tensor_read(big, "op")                        # larger than every on-chip level: streamed from DRAM
+    assert sim.get_level_rw_bits()["dram"]["read_bits"] == 1024 + 48 * 32 + 512 * 32 and sim._tensor_key(big) not in sim.sram_cache
+    sim.on_tensor_write(torch.zeros(8), "op2")           # a small result is born in the register file
+    assert sim.get_op_level_rw_bits()["op2"]["reg"]["write_bits"] == 256
+    assert sim.usage_bits["reg"] <= 64 * 32 and sim.usage_bits["sram"] <= 256 * 32
+    c = oc.MemoryResidencyCounter(capacity_bits={"reg": 4096 * 8, "sram": 64 * 1024 * 8})
+    net = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
+    with oc.DispatchCounterMode([c]):
+        net(torch.randn(8, 16)).sum().backward()
+    levels = c.get_level_bits()
+    assert levels["reg"] > 0 and c.get_total() > 0 and sum(c.get_move_bits_by_edge().values()) > 0
+    assert "aten.addmm" in next(iter(k for k in c.get_op_level_bits() if "addmm" in k))
+    c.reset()
+    assert c.get_level_bits() == {}
