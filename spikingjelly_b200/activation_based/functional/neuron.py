@@ -171,7 +171,7 @@ def gated_lif_step(x, v, spike, alpha, beta, gamma, tau, v_threshold, linear_dec
 def stbif_step(x, q, acc_q, q_threshold, pos_max, neg_min):
     """SpikeZIP ternary IF: emits +1/-1/0 (times ``q_threshold``), with the running
     count ``acc_q`` clamped to ``[neg_min, pos_max]``."""
-    q_threshold, pos_max, neg_min = q_threshold.to(x), pos_max.to(x), neg_min.to(x)
+    q_threshold, pos_max, neg_min = (t.to(x) if isinstance(t, torch.Tensor) else t for t in (q_threshold, pos_max, neg_min))
     q_next = q + (x / q_threshold).detach()
     acc = torch.round(acc_q)
     pos = (q_next - 1 >= 0) & (acc < pos_max)

@@ -10,6 +10,8 @@ from __future__ import annotations
 import math
 from typing import Optional, Sequence, Union
 
+import weakref
+
 import torch
 import torch.nn as nn
 
@@ -263,9 +265,33 @@ class STBIFNeuron(base.MemoryModule):
         out, q, acc_q, cur = functional.stbif_step(x, q, acc_q, self.q_threshold, self.pos_max, self.neg_min)
         return (out,), (q, acc_q, cur, bool((x != 0).any() | (out != 0).any()))
 
+    def _scalars(self):
+        """Python copies of the three scalar buffers, refreshed when a buffer is written (no sync per call)."""
+        stamp = (self.q_threshold._version, self.pos_max._version, self.neg_min._version, self.q_threshold.data_ptr())
+        if getattr(self, "_scalar_stamp", None) != stamp:
+            self._scalar_values = (float(self.q_threshold), float(self.pos_max), float(self.neg_min))
+            self._scalar_stamp = stamp
+        return self._scalar_values
+
+    def _compiled_run(self, x_seq, q, acc_q, cur):
+        from ._compiled import CompiledSequence, compiled_for
+        ref = weakref.ref(self)
+
+        def step(x, q, acc, c):
+            return functional.stbif_step(x, q, acc, *ref()._scalars())
+
+        seq = compiled_for(self, lambda: CompiledSequence(step, 3, lambda: ("stbif", *ref()._scalars()), "stbif"))
+        with torch.no_grad():
+            return seq.run(x_seq, (q, acc_q, cur))
+
     def multi_step_functional_forward(self, inputs, states, **kwargs):
         x_seq = inputs[0]
         q, acc_q, cur, _ = states
+        if x_seq.is_cuda and not (torch.is_grad_enabled() and x_seq.requires_grad):
+            res = self._compiled_run(x_seq, q, acc_q, cur)
+            if res is not None:
+                out_seq, (q, acc_q, cur), _ = res
+                return (out_seq,), (q, acc_q, cur, bool((x_seq != 0).any() | (out_seq != 0).any()))
         outs = []
         for t in range(x_seq.shape[0]):
             o, q, acc_q, cur = functional.stbif_step(x_seq[t], q, acc_q, self.q_threshold, self.pos_max, self.neg_min)

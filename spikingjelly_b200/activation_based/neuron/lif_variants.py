@@ -9,6 +9,8 @@ import math
 from typing import Callable, Optional
 
 import numpy as np
+import weakref
+
 import torch
 import torch.nn as nn
 
@@ -176,3 +178,18 @@ class ILIFNode(LIFNode):
 
     def _eager_step(self, x, v, sg):
         return functional.ilif_step(x, v, self.tau, self.v_threshold, sg, self.detach_reset)
+
+    def multi_step_functional_forward(self, inputs, states, **kwargs):
+        if self.native and inputs[0].is_cuda:
+            from ._compiled import CompiledSequence, compiled_for, scalar_signature
+            ref = weakref.ref(self)
+
+            def step(x, v):
+                me = ref()
+                return me._eager_step(x, v, me.surrogate_function)
+
+            seq = compiled_for(self, lambda: CompiledSequence(step, 1, lambda: scalar_signature(ref()), "ilif"))
+            res = seq.run(inputs[0], (states[0],))
+            if res is not None:
+                return (res[0],), (res[1][0], *states[1:])
+        return super().multi_step_functional_forward(inputs, states, **kwargs)

@@ -4,6 +4,8 @@ from __future__ import annotations
 
 from typing import Optional
 
+import weakref
+
 import torch
 
 from .. import functional, surrogate
@@ -128,5 +130,20 @@ class IzhikevichNode(AdaptBaseNode):
             self.v_threshold, self.v_reset, self.surrogate_function, self.detach_reset)
         return (spike,), (v, w)
 
+    def _compiled(self):
+        from ._compiled import CompiledSequence, compiled_for, scalar_signature
+        ref = weakref.ref(self)
+
+        def step(x, v, w):
+            (spike,), (v2, w2) = ref().single_step_functional_forward((x,), (v, w))
+            return spike, v2, w2
+
+        return compiled_for(self, lambda: CompiledSequence(step, 2, lambda: scalar_signature(ref()), "izhikevich"))
+
     def multi_step_functional_forward(self, inputs, states, **kwargs):
+        if self.native and inputs[0].is_cuda and getattr(self.surrogate_function, "spiking", True):
+            res = self._compiled().run(inputs[0], (states[0], states[-1]))
+            if res is not None:
+                spike_seq, (v, w), _ = res
+                return (spike_seq,), (v, w)
         return super(BaseNode, self).multi_step_functional_forward(inputs, states, **kwargs)

@@ -183,3 +183,31 @@ def test_kernel_lif_equals_builtin_lif_and_counts_launches():
         assert torch.equal(m(x), yb.detach())
         outs = m.kernel(x, torch.zeros_like(x[0]))
         assert torch.equal(outs[0], yb.detach()) and torch.equal(outs[1][-1], m.states[0])
+
+
+@pytest.mark.gpu
+def test_library_neurons_without_handwritten_kernels_run_compiled():
+    """Izhikevich, integer LIF and the ternary IF neuron: compiled multi-step path == eager path."""
+    from spikingjelly_b200.ops import counters
+    torch.manual_seed(0)
+    x = torch.rand(6, 4, 256, device="cuda") * 2
+    before = counters.by_name().get("flexsn_forward", 0)
+    for make in (lambda b: neuron.IzhikevichNode(step_mode="m", backend=b, a=0.2, b=0.05),
+                 lambda b: neuron.ILIFNode(step_mode="m", backend=b)):
+        a, e = make("cuda"), make("torch")
+        xa, xe = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+        ya, ye = a(xa), e(xe)
+        assert torch.equal(ya, ye), type(a).__name__
+        g = torch.randn_like(ya)
+        ya.backward(g)
+        ye.backward(g)
+        assert torch.allclose(xa.grad, xe.grad, atol=1e-5, rtol=1e-4), type(a).__name__
+        assert torch.allclose(a.v, e.v, atol=1e-6)
+    st = neuron.STBIFNeuron(0.25, level=8, step_mode="m").cuda()
+    ref = neuron.STBIFNeuron(0.25, level=8, step_mode="m")
+    xs = torch.randn(5, 3, 64, device="cuda")
+    with torch.no_grad():
+        out = st(xs)
+        want = ref(xs.cpu())
+    assert torch.allclose(out.cpu(), want) and torch.allclose(st.acc_q.cpu(), ref.acc_q)
+    assert counters.by_name().get("flexsn_forward", 0) >= before + 3
