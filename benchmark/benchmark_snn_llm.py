@@ -1,0 +1,100 @@
+#!/usr/bin/env python
+"""SNN-LLM (24 layers, d 2048, 16 heads, FFN 5504, vocabulary 32000, T = 4) training step: sequence length 2048,
+micro-batch 4 per tensor-parallel group, random token ids, bf16 autocast, AdamW.  Tensor parallel over all ranks
+(Megatron-style on NCCL); tokens/s counts the tokens of the micro-batch once (not per time step).
+
+    python benchmark/benchmark_snn_llm.py [--layers 24 --steps 5 --warmup 2]
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 benchmark/benchmark_snn_llm.py
+
+CUDA-event timing with a 256 MB L2 flush per step, max over ranks, one JSON line on rank 0 with the model FLOPs per
+second against the measured bf16 peak.
+"""
+import argparse
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+from spikingjelly_b200 import ops  # noqa: E402
+from spikingjelly_b200.models import snn_llm  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--micro-batch", type=int, default=4)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--out", default="")
+    a = ap.parse_args()
+    world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    ops.require()
+    torch.manual_seed(0)                                   # identical replicated parameters on every rank
+    model = snn_llm.snn_llm_1b(n_layers=a.layers, backend="cuda", max_seq_len=a.seq)
+    if world > 1:
+        model = snn_llm.parallelize_snn_llm(model)
+    model.to(device)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
+    tok = torch.randint(0, model.cfg.vocab_size, (a.micro_batch, a.seq), device=device, generator=torch.Generator(device).manual_seed(1))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def step():
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            _, loss = model(tok, labels=tok)
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        flush.zero_()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(a.warmup):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        loss = step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms = t.item() / a.steps
+        tokens = a.micro_batch * a.seq
+        fwd_flops = tokens * model.flops_per_token(a.seq)
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+        peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        tflops = 3.0 * fwd_flops / (ms / 1e3) / 1e12 / world
+        rec = {"config": f"SNN-LLM {a.layers}L d2048 ffn5504 T4 seq{a.seq} mb{a.micro_batch} bf16 tp{world}", "n_gpus": world,
+               "ms_per_step": round(ms, 2), "tokens_per_s": round(tokens / ms * 1e3, 1), "model_tflops_per_gpu": round(tflops, 1),
+               "of_measured_sustained_bf16_peak": round(tflops / peak, 3), "peak_source": "measured" if peaks else "fallback",
+               "last_loss": round(float(loss), 4), "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+               "parameters": sum(p.numel() for p in model.parameters())}
+        line = json.dumps(rec)
+        print(line)
+        if a.out:
+            with open(a.out, "a") as f:
+                f.write(line + "\n")
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

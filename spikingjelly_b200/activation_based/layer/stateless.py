@@ -115,6 +115,33 @@ class Linear(nn.Linear, base.StepModule):
         super().__init__(in_features, out_features, bias, **kw)
         self.step_mode = step_mode
 
+    def forward(self, x: Tensor) -> Tensor:
+        dtype = _native_linear_dtype(x, self.weight)
+        if dtype is None:
+            return F.linear(x, self.weight, self.bias)
+        from ...ops import gemm
+        y = gemm.linear(x.to(dtype), self.weight.to(dtype))
+        return y if self.bias is None else y + self.bias.to(dtype)
+
+
+def _native_linear_dtype(x: Tensor, weight: Tensor) -> Optional[torch.dtype]:
+    """The 16-bit dtype in which the tensor-core kernel should compute this product, or ``None`` for the library path."""
+    from ... import configure
+    if not (configure.native_linear and x.is_cuda and weight.is_cuda) or x.dim() < 2:
+        return None
+    if weight.shape[0] % 8 or weight.shape[1] % 8 or x.numel() == 0:
+        return None
+    if torch.is_autocast_enabled("cuda"):
+        dtype = torch.get_autocast_dtype("cuda")
+    elif x.dtype == weight.dtype:
+        dtype = x.dtype
+    else:
+        return None
+    if dtype not in (torch.bfloat16, torch.float16):
+        return None
+    from ... import ops
+    return dtype if ops.available() else None
+
 
 def _standardize(weight: Tensor, gain: Optional[Tensor], eps: float) -> Tensor:
     """Zero-mean, ``1/sqrt(fan_in)``-scaled weights per output unit, times ``gain``."""

@@ -32,3 +32,8 @@ triton_neuron_kernel_static_range_max_T = 64
 # Name used when a user asks for one of the reference's GPU backends
 # ("cupy", "triton", "inductor"): all of them resolve to the native kernels.
 native_backend_name = "cuda"
+
+# ``layer.Linear`` (and everything built on it) runs forward, dgrad and wgrad on the tcgen05 GEMM kernel when its input
+# is a CUDA tensor computed in bf16 / fp16 (under autocast, or with 16-bit parameters) and the feature sizes are multiples
+# of 8.  False: always ``torch.nn.functional.linear`` (cuBLAS).
+native_linear = True

@@ -40,6 +40,8 @@ def load(build_if_needed: bool = True) -> None:
             torch.ops.load_library(str(_build.LIB))
             _loaded = True
             _error = None
+            from . import _fake
+            _fake.register()
         except Exception as exc:
             _error = exc
             raise
