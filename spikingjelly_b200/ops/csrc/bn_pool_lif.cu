@@ -235,15 +235,13 @@ __global__ void __launch_bounds__(kThreads)
 bn_pool_backward2_kernel(PoolGeom g, int NB, const T* __restrict__ y, const uint8_t* __restrict__ idx,
                          const T* __restrict__ Gin, const float* __restrict__ coefA, const float* __restrict__ coefB,
                          const float* __restrict__ coefD, T* __restrict__ dy) {
+    // blockIdx.x = image row (img * H + h); blockIdx.y, threadIdx.x = position inside the row (w, channel group):
+    // all index arithmetic is 32-bit, one division per thread
     const int G = g.C / V;
-    const long long vec = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long n_vec = (long long)NB * g.H * g.W * G;
-    if (vec >= n_vec) return;
-    const int c0 = (int)(vec % G) * V;
-    long long pix = vec / G;
-    const int w = (int)(pix % g.W); pix /= g.W;
-    const int h = (int)(pix % g.H);
-    const int img = (int)(pix / g.H);
+    const int wc = (int)(blockIdx.y * blockDim.x + threadIdx.x);
+    if (wc >= g.W * G) return;
+    const int w = wc / G, c0 = (wc - w * G) * V;
+    const int img = (int)blockIdx.x / g.H, h = (int)blockIdx.x - img * g.H;
     float acc[V];
 #pragma unroll
     for (int j = 0; j < V; ++j) acc[j] = 0.0f;
@@ -397,8 +395,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> bn_pool_lif_backward(
                                 mean.data_ptr<float>(), invstd.data_ptr<float>(), grad_gamma.data_ptr<float>(),
                                 grad_beta.data_ptr<float>(), coef.data_ptr<float>(), coef.data_ptr<float>() + g.C,
                                 coef.data_ptr<float>() + 2 * g.C, stream);
-    const long long n_in = (long long)NB * g.H * g.W * G;
-    const unsigned grid2 = (unsigned)((n_in + kThreads - 1) / kThreads);
+    const dim3 grid2((unsigned)(NB * g.H), (unsigned)((g.W * G + kThreads - 1) / kThreads));
     SJ_POOL_DISPATCH(y.scalar_type(), {
         bn_pool_backward2_kernel<scalar_t><<<grid2, kThreads, 0, stream>>>(
             g, NB, reinterpret_cast<const scalar_t*>(y.data_ptr()), idx.data_ptr<uint8_t>(),

@@ -4,6 +4,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
+#include <cuda_fp8.h>
+
 #include "neuron_scan_launch.cuh"
 
 namespace sjb200 {
@@ -42,13 +44,17 @@ ScanParams make_params(const Dims& d, int64_t kind, double tau, double q0, doubl
     return p;
 }
 
-#define SJ_DISPATCH_FLOATING(DTYPE, ...)                                                   \
-    switch (DTYPE) {                                                                        \
-    case at::kFloat: { using scalar_t = float; __VA_ARGS__; break; }                        \
-    case at::kHalf: { using scalar_t = __half; __VA_ARGS__; break; }                        \
-    case at::kBFloat16: { using scalar_t = __nv_bfloat16; __VA_ARGS__; break; }             \
-    default: TORCH_CHECK(false, "neuron scan: unsupported dtype ", DTYPE);                  \
+// scalar_t: storage type of x_seq; state_t: type of spikes, potentials and gradients (bf16 when x is fp8-e4m3)
+#define SJ_DISPATCH_FLOATING(DTYPE, ...)                                                                      \
+    switch (DTYPE) {                                                                                           \
+    case at::kFloat: { using scalar_t = float; using state_t = float; __VA_ARGS__; break; }                    \
+    case at::kHalf: { using scalar_t = __half; using state_t = __half; __VA_ARGS__; break; }                   \
+    case at::kBFloat16: { using scalar_t = __nv_bfloat16; using state_t = __nv_bfloat16; __VA_ARGS__; break; } \
+    case at::kFloat8_e4m3fn: { using scalar_t = __nv_fp8_e4m3; using state_t = __nv_bfloat16; __VA_ARGS__; break; } \
+    default: TORCH_CHECK(false, "neuron scan: unsupported dtype ", DTYPE);                                     \
     }
+
+at::ScalarType state_dtype(at::ScalarType x) { return x == at::kFloat8_e4m3fn ? at::kBFloat16 : x; }
 
 int chunk_for(int T) { return T <= 4 ? 4 : 8; }
 
@@ -68,17 +74,18 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> scan_forw
     c10::optional<at::Tensor> vi;
     if (v_init.has_value() && v_init->defined() && v_init->numel() > 0) {
         TORCH_CHECK(v_init->numel() == d.N, "v_init must have one value per neuron");
-        vi = v_init->to(x.scalar_type()).contiguous();
+        vi = v_init->to(state_dtype(x.scalar_type())).contiguous();
     }
     const ScanParams p = make_params(d, kind, tau, q0, q1, q2, r, v_th, v_reset, soft_reset, vi, v_init_scalar);
 
-    at::Tensor spike = at::empty_like(x);
+    const auto sopt = x.options().dtype(state_dtype(x.scalar_type()));
+    at::Tensor spike = at::empty(x.sizes(), sopt);
     std::vector<int64_t> state_shape(x.sizes().begin() + 1, x.sizes().end());
-    at::Tensor v_last = at::empty(state_shape, x.options());
+    at::Tensor v_last = at::empty(state_shape, sopt);
     // a zero-element tensor stands for an absent optional output (each output gets its own)
     auto none = [&]() { return at::empty({0}, x.options()); };
     c10::optional<at::Tensor> v_seq, packed, ckpt;
-    if (store_v_seq) v_seq = at::empty_like(x);
+    if (store_v_seq) v_seq = at::empty(x.sizes(), sopt);
     if (pack_bits) packed = at::empty({d.T, (d.N + 31) / 32}, x.options().dtype(at::kInt));
     const int TC = chunk_for(d.T);
     const int n_ckpt = (d.T + TC - 1) / TC - 1;
@@ -88,10 +95,10 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> scan_forw
     }
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
     SJ_DISPATCH_FLOATING(x.scalar_type(), {
-        constexpr int VV = 16 / sizeof(scalar_t);
-        const bool vec = (d.N % VV == 0) && aligned<scalar_t>(x.data_ptr(), VV) && aligned<scalar_t>(spike.data_ptr(), VV) &&
-                         aligned<scalar_t>(v_last.data_ptr(), VV) && aligned<scalar_t>(p.v_init, VV) &&
-                         (!v_seq.has_value() || aligned<scalar_t>(v_seq->data_ptr(), VV)) &&
+        constexpr int VV = 16 / sizeof(state_t);
+        const bool vec = (d.N % VV == 0) && aligned<scalar_t>(x.data_ptr(), VV) && aligned<state_t>(spike.data_ptr(), VV) &&
+                         aligned<state_t>(v_last.data_ptr(), VV) && aligned<state_t>(p.v_init, VV) &&
+                         (!v_seq.has_value() || aligned<state_t>(v_seq->data_ptr(), VV)) &&
                          (!ckpt.has_value() || aligned<float>(ckpt->data_ptr(), VV));
         const int V = vec ? (TC == 8 ? 4 : VV) : 1;
         const long long threads_needed = (d.N + V - 1) / V;
@@ -100,7 +107,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> scan_forw
                        v_seq.has_value() ? v_seq->data_ptr() : nullptr,
                        packed.has_value() ? reinterpret_cast<uint32_t*>(packed->data_ptr()) : nullptr,
                        ckpt.has_value() ? ckpt->data_ptr<float>() : nullptr};
-        scan_forward_launch<scalar_t>(p, io, vec, TC, grid, stream);
+        scan_forward_launch<scalar_t, state_t>(p, io, vec, TC, grid, stream);
     });
     C10_CUDA_KERNEL_LAUNCH_CHECK();
     return {spike, v_last, v_seq.has_value() ? *v_seq : none(), packed.has_value() ? *packed : none(), ckpt.has_value() ? *ckpt : none()};
@@ -119,14 +126,15 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> scan_backward(
     const c10::cuda::CUDAGuard guard(x_seq.device());
     at::Tensor x = x_seq.contiguous();
     const Dims d = seq_dims(x);
-    at::Tensor gs = grad_spike_seq.to(x.scalar_type()).contiguous();
+    const at::ScalarType sdt = state_dtype(x.scalar_type());
+    at::Tensor gs = grad_spike_seq.to(sdt).contiguous();
     TORCH_CHECK(gs.numel() == x.numel(), "grad_spike_seq must match x_seq");
     c10::optional<at::Tensor> vi, gvl, gvs;
-    if (v_init.has_value() && v_init->defined() && v_init->numel() > 0) vi = v_init->to(x.scalar_type()).contiguous();
+    if (v_init.has_value() && v_init->defined() && v_init->numel() > 0) vi = v_init->to(sdt).contiguous();
     if (grad_v_last.has_value() && grad_v_last->defined() && grad_v_last->numel() > 0)
-        gvl = grad_v_last->to(x.scalar_type()).contiguous();
+        gvl = grad_v_last->to(sdt).contiguous();
     if (grad_v_seq.has_value() && grad_v_seq->defined() && grad_v_seq->numel() > 0)
-        gvs = grad_v_seq->to(x.scalar_type()).contiguous();
+        gvs = grad_v_seq->to(sdt).contiguous();
     ScanParams p = make_params(d, kind, tau, q0, q1, q2, r, v_th, v_reset, soft_reset, vi, v_init_scalar);
     p.sg_id = (int)sg_id; p.sg_p0 = (float)sg_p0; p.sg_p1 = (float)sg_p1; p.detach_reset = detach_reset ? 1 : 0;
 
@@ -138,21 +146,22 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> scan_backward(
                     "scan_backward: T > chunk needs the forward checkpoints");
         ckpt_ptr = ckpt->data_ptr<float>();
     }
-    at::Tensor gx = at::empty_like(x);
+    const auto sopt = x.options().dtype(sdt);
+    at::Tensor gx = at::empty(x.sizes(), sopt);
     std::vector<int64_t> state_shape(x.sizes().begin() + 1, x.sizes().end());
-    at::Tensor gvi = need_grad_v_init ? at::empty(state_shape, x.options()) : at::empty({0}, x.options());
+    at::Tensor gvi = need_grad_v_init ? at::empty(state_shape, sopt) : at::empty({0}, sopt);
     const bool plif = (kind == NK_PLIF_DI || kind == NK_PLIF_NDI);
     at::Tensor grad_r = plif ? at::zeros({1}, x.options().dtype(at::kFloat)) : at::empty({0}, x.options());
     if (d.N == 0 || d.T == 0) return {gx, gvi, grad_r};
 
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
     SJ_DISPATCH_FLOATING(x.scalar_type(), {
-        constexpr int VV = 16 / sizeof(scalar_t);
-        const bool vec = (d.N % VV == 0) && aligned<scalar_t>(x.data_ptr(), VV) && aligned<scalar_t>(gs.data_ptr(), VV) &&
-                         aligned<scalar_t>(gx.data_ptr(), VV) && aligned<scalar_t>(p.v_init, VV) &&
-                         (!gvl.has_value() || aligned<scalar_t>(gvl->data_ptr(), VV)) &&
-                         (!gvs.has_value() || aligned<scalar_t>(gvs->data_ptr(), VV)) &&
-                         (!need_grad_v_init || aligned<scalar_t>(gvi.data_ptr(), VV)) && aligned<float>(ckpt_ptr, VV);
+        constexpr int VV = 16 / sizeof(state_t);
+        const bool vec = (d.N % VV == 0) && aligned<scalar_t>(x.data_ptr(), VV) && aligned<state_t>(gs.data_ptr(), VV) &&
+                         aligned<state_t>(gx.data_ptr(), VV) && aligned<state_t>(p.v_init, VV) &&
+                         (!gvl.has_value() || aligned<state_t>(gvl->data_ptr(), VV)) &&
+                         (!gvs.has_value() || aligned<state_t>(gvs->data_ptr(), VV)) &&
+                         (!need_grad_v_init || aligned<state_t>(gvi.data_ptr(), VV)) && aligned<float>(ckpt_ptr, VV);
         const int V = vec ? (TC == 8 ? 4 : VV) : 1;
         const long long threads_needed = (d.N + V - 1) / V;
         const unsigned grid = (unsigned)((threads_needed + kThreads - 1) / kThreads);
@@ -169,7 +178,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> scan_backward(
         void* gvi_p = need_grad_v_init ? gvi.data_ptr() : nullptr;
         float* gr_p = plif ? grad_r.data_ptr<float>() : nullptr;
         ScanBwdPtrs io{x.data_ptr(), gs.data_ptr(), gvl_p, gvs_p, ckpt_ptr, gx.data_ptr(), gvi_p, gr_p, partial, ticket};
-        scan_backward_launch<scalar_t>(p, io, vec, TC, grid, stream);
+        scan_backward_launch<scalar_t, state_t>(p, io, vec, TC, grid, stream);
     });
     C10_CUDA_KERNEL_LAUNCH_CHECK();
     return {gx, gvi, grad_r};

@@ -99,7 +99,7 @@ struct Neuron {
 };
 
 // ------------------------------------------------------------------- forward
-// spike_seq [T,N] (TO), v_last [N] (TIN), optional v_seq [T,N] (TIN),
+// x_seq [T,N] (TIN: may be narrower than the rest, e.g. fp8-e4m3); spike_seq [T,N], v_last [N], optional v_seq [T,N] (TO),
 // optional packed [T, ceil(N/32)] (bit i of word j = neuron 32 j + i),
 // optional ckpt [ceil(T/TC)-1, N] fp32 (membrane potential after step (j+1)*TC-1).
 // LEAN: the common training call, with everything optional compiled out: T is a multiple of TC (no
@@ -107,7 +107,7 @@ struct Neuron {
 template <typename TIN, typename TO, int V, int TC, int KIND, bool LEAN = false>
 __global__ void __launch_bounds__(256, 3)
 scan_forward_kernel(ScanParams p, const TIN* __restrict__ x_seq, TO* __restrict__ spike_seq,
-                    TIN* __restrict__ v_last, TIN* __restrict__ v_seq, uint32_t* __restrict__ packed,
+                    TO* __restrict__ v_last, TO* __restrict__ v_seq, uint32_t* __restrict__ packed,
                     float* __restrict__ ckpt) {
     const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long n0 = gtid * V;
@@ -121,7 +121,7 @@ scan_forward_kernel(ScanParams p, const TIN* __restrict__ x_seq, TO* __restrict_
 
     float v[V];
     if (active && p.v_init != nullptr) {
-        load_vec<TIN, V>(reinterpret_cast<const TIN*>(p.v_init) + n0, v);
+        load_vec<TO, V>(reinterpret_cast<const TO*>(p.v_init) + n0, v);
     } else {
 #pragma unroll
         for (int j = 0; j < V; ++j) v[j] = p.v_init_scalar;
@@ -150,7 +150,7 @@ scan_forward_kernel(ScanParams p, const TIN* __restrict__ x_seq, TO* __restrict_
                 const long long off = (long long)(t0 + i) * p.N + n0;
                 if (active) {
                     store_vec<TO, V>(spike_seq + off, s);
-                    if (v_seq != nullptr) store_vec<TIN, V>(v_seq + off, v);
+                    if (v_seq != nullptr) store_vec<TO, V>(v_seq + off, v);
                 }
                 if (packed != nullptr) {  // uniform branch: every lane of the warp takes part
                     if (!active) bits = 0;
@@ -166,19 +166,19 @@ scan_forward_kernel(ScanParams p, const TIN* __restrict__ x_seq, TO* __restrict_
             store_vec<float, V>(ckpt + (long long)(t0 / TC) * p.N + n0, v);
         }
     }
-    if (active && v_last != nullptr) store_vec<TIN, V>(v_last + n0, v);
+    if (active && v_last != nullptr) store_vec<TO, V>(v_last + n0, v);
 }
 
 // ------------------------------------------------------------------ backward
-// grad_x_seq [T,N] (TIN); optional grad_v_init [N] (TIN); PLIF: block partial sums of
+// x_seq (TIN); every gradient, the initial potential and grad_x_seq [T,N], grad_v_init [N] in TG; PLIF: block partial sums of
 // dL/dr go to partial[gridDim.x], the last block to finish (ticket counter) adds them
 // in index order into grad_r[0] — a deterministic single-launch reduction.
 // LEAN: T is a multiple of TC, scalar initial potential, no gradient flowing in through v_last or v_seq.
 template <typename TIN, typename TG, int V, int TC, int KIND, bool LEAN = false>
 __global__ void __launch_bounds__(256, 2)
 scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __restrict__ grad_spike_seq,
-                     const TIN* __restrict__ grad_v_last, const TIN* __restrict__ grad_v_seq,
-                     const float* __restrict__ ckpt, TIN* __restrict__ grad_x_seq, TIN* __restrict__ grad_v_init,
+                     const TG* __restrict__ grad_v_last, const TG* __restrict__ grad_v_seq,
+                     const float* __restrict__ ckpt, TG* __restrict__ grad_x_seq, TG* __restrict__ grad_v_init,
                      float* __restrict__ grad_r, float* __restrict__ partial, unsigned int* __restrict__ ticket) {
     const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long n0 = gtid * V;
@@ -200,7 +200,7 @@ scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __re
     float c[V];     // dL/dv_t flowing in from step t+1
     float gr = 0.0f;
     if (active && grad_v_last != nullptr) {
-        load_vec<TIN, V>(grad_v_last + n0, c);
+        load_vec<TG, V>(grad_v_last + n0, c);
     } else {
 #pragma unroll
         for (int j = 0; j < V; ++j) c[j] = 0.0f;
@@ -216,7 +216,7 @@ scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __re
         } else if (ck > 0) {
             load_vec<float, V>(ckpt + (long long)(ck - 1) * p.N + n0, v0);
         } else if (p.v_init != nullptr) {
-            load_vec<TIN, V>(reinterpret_cast<const TIN*>(p.v_init) + n0, v0);
+            load_vec<TG, V>(reinterpret_cast<const TG*>(p.v_init) + n0, v0);
         } else {
 #pragma unroll
             for (int j = 0; j < V; ++j) v0[j] = p.v_init_scalar;
@@ -261,7 +261,7 @@ scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __re
                 float gs[V], gv[V], gx[V], sg[V];
                 if (active) {
                     unpack<TG, V>(gr_raw[i], gs);
-                    if (grad_v_seq != nullptr) load_vec_stream<TIN, V>(grad_v_seq + off, gv);
+                    if (grad_v_seq != nullptr) load_vec_stream<TG, V>(grad_v_seq + off, gv);
                 } else {
 #pragma unroll
                     for (int j = 0; j < V; ++j) gs[j] = 0.0f;
@@ -287,11 +287,11 @@ scan_backward_kernel(ScanParams p, const TIN* __restrict__ x_seq, const TG* __re
                     }
                     gx[j] = gh * dhdx;
                 }
-                if (active) store_vec<TIN, V>(grad_x_seq + off, gx);
+                if (active) store_vec<TG, V>(grad_x_seq + off, gx);
             }
         }
     }
-    if (active && grad_v_init != nullptr) store_vec<TIN, V>(grad_v_init + n0, c);
+    if (active && grad_v_init != nullptr) store_vec<TG, V>(grad_v_init + n0, c);
 
     if constexpr (plif) {
         __shared__ float warp_part[8];

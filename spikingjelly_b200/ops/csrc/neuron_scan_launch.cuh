@@ -17,8 +17,8 @@ struct ScanBwdPtrs {
 // `vec`: use vector accesses (caller checked divisibility and alignment for 16 bytes); TC: chunk
 // (4 or 8 steps).  Chunks of 8 steps use 4 elements per thread whatever the dtype, so that the
 // recomputed trajectory (TC x V floats) stays in registers.
-template <typename T> void scan_forward_launch(const ScanParams& p, const ScanFwdPtrs& io, bool vec, int TC, unsigned grid, cudaStream_t s);
-template <typename T> void scan_backward_launch(const ScanParams& p, const ScanBwdPtrs& io, bool vec, int TC, unsigned grid, cudaStream_t s);
+template <typename T, typename TO = T> void scan_forward_launch(const ScanParams& p, const ScanFwdPtrs& io, bool vec, int TC, unsigned grid, cudaStream_t s);
+template <typename T, typename TO = T> void scan_backward_launch(const ScanParams& p, const ScanBwdPtrs& io, bool vec, int TC, unsigned grid, cudaStream_t s);
 
 // (the instantiation macro below names its type parameter T, so p.T cannot be spelled inside it)
 inline int scan_steps(const ScanParams& p) { return p.T; }
@@ -75,5 +75,48 @@ inline int scan_steps(const ScanParams& p) { return p.T; }
             else scan_backward_kernel<T, T, 1, 8, KIND><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket);                 \
         });                                                                                                         \
     }
+
+#define SJ_SCAN_INSTANTIATE2(T, TO)                                                                                      \
+    template <>                                                                                                     \
+    void scan_forward_launch<T, TO>(const ScanParams& p, const ScanFwdPtrs& io, bool vec, int TC, unsigned grid,       \
+                                cudaStream_t s) {                                                                   \
+        constexpr int VV = 16 / sizeof(TO);                                                                          \
+        constexpr int V8 = 4;                                                                                       \
+        auto x = reinterpret_cast<const T*>(io.x_seq);                                                              \
+        auto sp = reinterpret_cast<TO*>(io.spike_seq);                                                               \
+        auto vl = reinterpret_cast<TO*>(io.v_last);                                                                  \
+        auto vs = reinterpret_cast<TO*>(io.v_seq);                                                                   \
+        const bool lean = vec && scan_steps(p) % TC == 0 && p.v_init == nullptr && io.v_seq == nullptr && io.packed == nullptr;   \
+        SJ_SCAN_KIND_SWITCH(p.kind, {                                                                               \
+            if (lean && TC == 4) scan_forward_kernel<T, TO, VV, 4, KIND, true><<<grid, 256, 0, s>>>(p, x, sp, vl, vs, io.packed, io.ckpt); \
+            else if (lean) scan_forward_kernel<T, TO, V8, 8, KIND, true><<<grid, 256, 0, s>>>(p, x, sp, vl, vs, io.packed, io.ckpt);       \
+            else if (vec && TC == 4) scan_forward_kernel<T, TO, VV, 4, KIND><<<grid, 256, 0, s>>>(p, x, sp, vl, vs, io.packed, io.ckpt); \
+            else if (vec) scan_forward_kernel<T, TO, V8, 8, KIND><<<grid, 256, 0, s>>>(p, x, sp, vl, vs, io.packed, io.ckpt);       \
+            else if (TC == 4) scan_forward_kernel<T, TO, 1, 4, KIND><<<grid, 256, 0, s>>>(p, x, sp, vl, vs, io.packed, io.ckpt);    \
+            else scan_forward_kernel<T, TO, 1, 8, KIND><<<grid, 256, 0, s>>>(p, x, sp, vl, vs, io.packed, io.ckpt);                 \
+        });                                                                                                         \
+    }                                                                                                               \
+    template <>                                                                                                     \
+    void scan_backward_launch<T, TO>(const ScanParams& p, const ScanBwdPtrs& io, bool vec, int TC, unsigned grid,      \
+                                 cudaStream_t s) {                                                                  \
+        constexpr int VV = 16 / sizeof(TO);                                                                          \
+        constexpr int V8 = 4;                                                                                       \
+        auto x = reinterpret_cast<const T*>(io.x_seq);                                                              \
+        auto gs = reinterpret_cast<const TO*>(io.grad_spike_seq);                                                    \
+        auto gvl = reinterpret_cast<const TO*>(io.grad_v_last);                                                      \
+        auto gvs = reinterpret_cast<const TO*>(io.grad_v_seq);                                                       \
+        auto gx = reinterpret_cast<TO*>(io.grad_x_seq);                                                              \
+        auto gvi = reinterpret_cast<TO*>(io.grad_v_init);                                                            \
+        const bool lean = vec && scan_steps(p) % TC == 0 && p.v_init == nullptr && io.grad_v_last == nullptr && io.grad_v_seq == nullptr; \
+        SJ_SCAN_KIND_SWITCH(p.kind, {                                                                               \
+            if (lean && TC == 4) scan_backward_kernel<T, TO, VV, 4, KIND, true><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket); \
+            else if (lean) scan_backward_kernel<T, TO, V8, 8, KIND, true><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket);       \
+            else if (vec && TC == 4) scan_backward_kernel<T, TO, VV, 4, KIND><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket); \
+            else if (vec) scan_backward_kernel<T, TO, V8, 8, KIND><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket);       \
+            else if (TC == 4) scan_backward_kernel<T, TO, 1, 4, KIND><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket);    \
+            else scan_backward_kernel<T, TO, 1, 8, KIND><<<grid, 256, 0, s>>>(p, x, gs, gvl, gvs, io.ckpt, gx, gvi, io.grad_r, io.partial, io.ticket);                 \
+        });                                                                                                         \
+    }
+
 
 }  // namespace sjb200

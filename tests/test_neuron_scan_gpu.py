@@ -151,3 +151,30 @@ def test_deterministic_twice():
         outs.append((g, b.w.grad.clone()))
     assert torch.equal(outs[0][0], outs[1][0])
     assert torch.equal(outs[0][1], outs[1][1])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,N", [(4, 4096), (8, 4096), (16, 1000), (5, 777)])
+@pytest.mark.parametrize("kind", ["if", "lif_di", "lif_ndi"])
+def test_fp8_e4m3_input_equals_bf16_kernel_on_the_same_values(T, N, kind):
+    """x stored as one byte per element: every e4m3 value is exact in bf16, so spikes, final potential and the input
+    gradient must be bit-identical to the bf16 kernel fed with the widened tensor."""
+    from spikingjelly_b200 import ops
+    from spikingjelly_b200.ops.neuron_scan import KIND
+    ops.require()
+    torch.manual_seed(0)
+    x8 = (torch.randn(T, N, device="cuda") + 0.5).to(torch.float8_e4m3fn)
+    x16 = x8.to(torch.bfloat16)
+    g = torch.randn(T, N, device="cuda").to(torch.bfloat16)
+    k = KIND[kind]
+
+    def run(x):
+        s, v, _, _, ck = torch.ops.sjb200.scan_forward(x, None, 0.0, None, k, 2.0, 0.0, 0.0, 0.0, 1.0, 0.0, False, False, False, True)
+        gx, _, _ = torch.ops.sjb200.scan_backward(g, None, None, x, None, 0.0, None, ck if ck.numel() else None, k, 2.0, 0.0, 0.0, 0.0,
+                                                  1.0, 0.0, False, 1, 2.0, 0.0, False, False)
+        return s, v, gx
+
+    a, b = run(x8), run(x16)
+    assert a[0].dtype == torch.bfloat16 and a[2].dtype == torch.bfloat16
+    for u, w in zip(a, b):
+        assert torch.equal(u, w)
