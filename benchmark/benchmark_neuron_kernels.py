@@ -78,7 +78,9 @@ def main():
         except Exception as exc:
             print("reference unavailable:", exc, file=sys.stderr)
     dts = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16, "fp8": torch.bfloat16}
+    from spikingjelly_b200 import ops
     from spikingjelly_b200.ops.neuron_scan import KIND
+    ops.require()
     kind_id = {"if": KIND["if"], "lif": KIND["lif_di"], "lif_ndi": KIND["lif_ndi"]}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     rows = []

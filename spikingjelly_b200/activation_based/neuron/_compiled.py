@@ -71,5 +71,5 @@ def scalar_signature(module, extra: Tuple = ()) -> tuple:
     """Every int / float / bool / None attribute of ``module``, its surrogate's description and the training flag."""
     items = tuple(sorted((k, v) for k, v in vars(module).items() if isinstance(v, (int, float, bool)) or v is None))
     sg = getattr(module, "surrogate_function", None)
-    return (type(module).__name__, items, repr(sg), tuple(sorted(vars(sg).items(), key=str)) if hasattr(sg, "__dict__") else (),
-            bool(module.training), *extra)
+    sg_items = tuple(sorted((k, v) for k, v in vars(sg).items() if isinstance(v, (int, float, bool, str)))) if hasattr(sg, "__dict__") else ()
+    return (type(module).__name__, items, type(sg).__name__, sg_items, bool(module.training), *extra)

@@ -194,6 +194,10 @@ class ResidualSNN(nn.Module):
         return self.fc(x)
 
     def forward(self, x):
+        if x.is_cuda and x.ndim == 5:
+            from . import _resnet_fused
+            if _resnet_fused.eligible(self, x):
+                return _resnet_fused.forward(self, x)
         return self._forward_impl(x)
 
 

@@ -140,3 +140,39 @@ def test_ottt_vgg_family_builds_and_trains_online():
     full = O.ottt_spiking_vgg11_ws(num_classes=7)        # three-layer classifier with weight-standardised linears
     assert full(torch.rand(1, 3, 32, 32)).shape == (1, 7)
     assert [k for k in O.ottt_spiking_vgg16(num_classes=3).state_dict()][:2] == ["features.0.weight", "features.0.bias"]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cnf", ["ADD", "AND"])
+def test_sew_resnet_fused_channels_last_schedule_matches_module_path(cnf):
+    from spikingjelly_b200.activation_based import functional, neuron, surrogate
+    from spikingjelly_b200.models import _resnet_fused, sew_resnet
+    from spikingjelly_b200.ops import counters
+    torch.manual_seed(0)
+    net = sew_resnet.sew_resnet18(num_classes=11, cnf=cnf, spiking_neuron=neuron.LIFNode, tau=2.0, detach_reset=True,
+                                  surrogate_function=surrogate.ATan(), in_channels=2).cuda()
+    functional.set_step_mode(net, "m")
+    functional.set_backend(net, "cuda", instance=neuron.LIFNode)
+    x = (torch.rand(4, 4, 2, 64, 64, device="cuda") < 0.3).float()
+    res = {}
+    for name in ("fused", "module"):
+        net.zero_grad(set_to_none=True)
+        functional.reset_net(net)
+        before = counters.by_name().get("bn_lif_forward", 0)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            assert _resnet_fused.eligible(net, x)
+            out = net(x) if name == "fused" else net._forward_impl(x)
+        used = counters.by_name().get("bn_lif_forward", 0) - before
+        assert (used == 20) if name == "fused" else (used == 0)          # 17 conv stages + 3 down-sampling shortcuts
+        out.float().mean(0).square().sum().backward()
+        res[name] = (out.detach().float(), net.fc.weight.grad.clone(), net.layer1[0].conv1.weight.grad.clone(), net.conv1.weight.grad.clone())
+    functional.reset_net(net)
+    rel = lambda a, b: ((a - b).norm() / (b.norm() + 1e-12)).item()
+    assert rel(res["fused"][0], res["module"][0]) < 0.08
+    assert rel(res["fused"][1], res["module"][1]) < 0.15 and rel(res["fused"][2], res["module"][2]) < 0.3
+    net.eval()
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        a = net(x)
+        functional.reset_net(net)
+        b = net._forward_impl(x)
+    assert rel(a.float(), b.float()) < 0.08
