@@ -58,9 +58,17 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """fp32 statistics; the result is returned in the autocast compute dtype when autocast is on (the neuron that
+        follows then reads and writes 16-bit tensors), else in ``x``'s dtype."""
+        out_dtype = x.dtype
+        if x.is_cuda and torch.is_autocast_enabled("cuda"):
+            out_dtype = torch.get_autocast_dtype("cuda")
+        if x.is_cuda:
+            with torch.autocast("cuda", enabled=False):
+                return F.rms_norm(x.float() if x.dtype != torch.float32 else x, (x.shape[-1],), self.weight.float(), self.eps).to(out_dtype)
         xf = x.float()
         y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)
-        return (y * self.weight.float()).to(x.dtype)
+        return (y * self.weight.float()).to(out_dtype)
 
 
 class RotaryEmbedding(nn.Module):
