@@ -72,10 +72,9 @@ def _init_v(n) -> float:
 
 
 def _conv(conv: nn.Conv2d, h: torch.Tensor) -> torch.Tensor:
-    w = conv.weight
-    if w.dim() == 4 and not w.is_contiguous(memory_format=torch.channels_last):
-        # one-time, value-preserving relayout of the parameter so that cuDNN's NHWC kernels take it as it is
-        w.data = w.data.contiguous(memory_format=torch.channels_last)
+    # the cast to the compute dtype also lays the filter out channels-last, so cuDNN's NHWC kernels take it as it is
+    # (the parameter itself keeps its layout: optimizers and gradient buckets rely on it)
+    w = conv.weight.to(dtype=h.dtype, memory_format=torch.channels_last)
     return F.conv2d(h, w, None, conv.stride, conv.padding, conv.dilation, conv.groups)
 
 

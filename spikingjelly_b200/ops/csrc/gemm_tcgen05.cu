@@ -7,7 +7,8 @@
 // * warp 0: TMA producer (one thread) filling a STAGES-deep ring of 128B-swizzled
 //   A/B tiles; warp 1: tcgen05.mma issuer (one thread), accumulator double-buffered in
 //   TMEM (2 x BN columns) so the epilogue of tile i overlaps the main loop of tile
-//   i+1; warps 2-5: epilogue (tcgen05.ld -> convert -> global);
+//   i+1; warps 2-9: epilogue (tcgen05.ld -> convert -> shared -> TMA store), two warps per TMEM lane quarter,
+//   each draining half of the tile's columns;
 // * either operand may be stored "MN-major" (memory is [K, M] or [K, N] with the
 //   non-contracted index contiguous), which is what dgrad/wgrad of a linear layer
 //   need, so no transposes are ever materialised;
@@ -33,7 +34,7 @@ using namespace tc;
 constexpr int BM = 128;
 constexpr int BK = 64;          // 64 x 2 B = one 128 B swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 192;   // 6 warps: producer, mma, 4 x epilogue
+constexpr int kThreads = 320;   // 10 warps: producer, mma, 2 x 4 epilogue (each group of four drains half of the columns)
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -41,9 +42,9 @@ struct SmemLayout {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int OUT_OFFSET = BAR_OFFSET + 1024;    // epilogue staging: 2 x [128 rows][32 cols] 16-bit
+    static constexpr int OUT_OFFSET = BAR_OFFSET + 1024;    // epilogue staging: 2 groups x 2 x [128 rows][32 cols] 16-bit
     static constexpr int OUT_BYTES = BM * 32 * 2;
-    static constexpr int TOTAL = OUT_OFFSET + 2 * OUT_BYTES + 1024;   // + slack for 1024 B alignment
+    static constexpr int TOTAL = OUT_OFFSET + 4 * OUT_BYTES + 1024;   // + slack for 1024 B alignment
 };
 
 struct GemmArgs {
@@ -84,7 +85,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar + a, 1); mbar_init(tempty_bar + a, 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar + a, 1); mbar_init(tempty_bar + a, 8); }
         *abort_flag = 0;
         mbar_init_fence();
         tma_prefetch_desc(&tmA);
@@ -170,6 +171,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     } else {
         // ---------------------------------------------------------------- epilogue
         const int quarter = warp & 3;              // TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;          // which half of the tile's columns this group of four warps drains
+        const int issuer = 64 + half * 128;        // the thread of the group that talks to the TMA unit
         uint32_t tl = 0, oc = 0;                   // tiles / output chunks handled so far
         for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tl) {
             const int split = tile / tiles_mn, mn = tile % tiles_mn;
@@ -183,7 +186,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + c * 32, r);
                 tmem_ld_wait();
@@ -208,10 +211,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     // 16-bit output: stage the 128 x 32 chunk in shared memory (64-byte rows, 16-byte
                     // chunks XOR-swizzled by (row >> 1) & 3 = the TMA 64B swizzle) and let TMA write it:
                     // full-sector, clipped at the matrix edges, asynchronous.
-                    uint8_t* stage_buf = smem + L::OUT_OFFSET + (oc & 1) * L::OUT_BYTES;
-                    if (oc >= 2 && threadIdx.x == 64) tma_store_wait_read<1>();  // the store that last read this buffer is done
+                    uint8_t* stage_buf = smem + L::OUT_OFFSET + (half * 2 + (oc & 1)) * L::OUT_BYTES;
+                    if (oc >= 2 && (int)threadIdx.x == issuer) tma_store_wait_read<1>();  // the store that last read this buffer is done
                     ++oc;
-                    named_barrier(1, 128);
+                    named_barrier(1 + half, 128);
                     const int r_in_tile = quarter * 32 + lane;
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
@@ -226,8 +229,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         *reinterpret_cast<uint4*>(stage_buf + r_in_tile * 64 + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                     fence_async_smem();
-                    named_barrier(1, 128);
-                    if (threadIdx.x == 64) {
+                    named_barrier(1 + half, 128);
+                    if ((int)threadIdx.x == issuer) {
                         tma_store_2d(&tmD, stage_buf, n0 + c * 32, m0);
                         tma_store_commit();
                     }
@@ -237,7 +240,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar + acc);
         }
-        if (threadIdx.x == 64) tma_store_wait_all<0>();   // all output boxes written before the CTA retires
+        if ((int)threadIdx.x == issuer) tma_store_wait_all<0>();   // all output boxes written before the CTA retires
     }
 
     // -------------------------------------------------------------------- teardown
