@@ -119,25 +119,32 @@ def _ssa(S: torch.Tensor, T: int, B: int, L: int, heads: int, scale: float) -> t
     return out.reshape(T, B * L, C)
 
 
+def _linear_bn(x2d: torch.Tensor, w: torch.Tensor, bn):
+    """The token GEMM; in training mode its epilogue also emits the per-channel sums the batch norm needs."""
+    if bn.training or bn.running_mean is None:
+        return G.linear_with_stats(x2d, w)
+    return G.linear(x2d, w), None
+
+
 def _block(blk, X: torch.Tensor, T: int, B: int, L: int, dt) -> torch.Tensor:
     """``X``: ``[T, B*L, C]`` contiguous tokens."""
     C = X.shape[-1]
     M = T * B * L
     attn, mlp = blk.attn, blk.mlp
     w_qkv = attn.qkv_conv_bn[0].weight.squeeze(-1).to(dt)
-    y = G.linear(X.view(M, C), w_qkv).view(T, B * L, 3 * C)
-    S = bn_lif(y, attn.qkv_conv_bn[1], _spec(attn.qkv_lif), v_init=_init_v(attn.qkv_lif))
+    y, st = _linear_bn(X.view(M, C), w_qkv, attn.qkv_conv_bn[1])
+    S = bn_lif(y.view(T, B * L, 3 * C), attn.qkv_conv_bn[1], _spec(attn.qkv_lif), v_init=_init_v(attn.qkv_lif), stats=st)
     a = _ssa(S, T, B, L, attn.num_heads, attn.scale)
     A, _, _, _ = multistep_neuron(a.reshape(T, -1), _init_v(attn.attn_lif), _spec(attn.attn_lif))
     w_proj = attn.proj_conv_bn[0].weight.squeeze(-1).to(dt)
-    y = G.linear(A.view(M, C), w_proj).view(T, B * L, C)
-    X1 = bn_lif(y, attn.proj_conv_bn[1], _spec(attn.proj_lif), residual=X, v_init=_init_v(attn.proj_lif))
+    y, st = _linear_bn(A.view(M, C), w_proj, attn.proj_conv_bn[1])
+    X1 = bn_lif(y.view(T, B * L, C), attn.proj_conv_bn[1], _spec(attn.proj_lif), residual=X, v_init=_init_v(attn.proj_lif), stats=st)
     w1 = mlp.fc1[0].weight.squeeze(-1).to(dt)
-    y = G.linear(X1.view(M, C), w1).view(T, B * L, -1)
-    F1 = bn_lif(y, mlp.fc1[1], _spec(mlp.neuron1), v_init=_init_v(mlp.neuron1))
+    y, st = _linear_bn(X1.view(M, C), w1, mlp.fc1[1])
+    F1 = bn_lif(y.view(T, B * L, -1), mlp.fc1[1], _spec(mlp.neuron1), v_init=_init_v(mlp.neuron1), stats=st)
     w2 = mlp.fc2[0].weight.squeeze(-1).to(dt)
-    y = G.linear(F1.view(M, F1.shape[-1]), w2).view(T, B * L, C)
-    return bn_lif(y, mlp.fc2[1], _spec(mlp.neuron2), residual=X1, v_init=_init_v(mlp.neuron2))
+    y, st = _linear_bn(F1.view(M, F1.shape[-1]), w2, mlp.fc2[1])
+    return bn_lif(y.view(T, B * L, C), mlp.fc2[1], _spec(mlp.neuron2), residual=X1, v_init=_init_v(mlp.neuron2), stats=st)
 
 
 def forward(model, x: torch.Tensor) -> torch.Tensor:

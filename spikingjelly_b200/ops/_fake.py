@@ -22,6 +22,12 @@ def register() -> None:
         N = b.shape[1] if b_mn else b.shape[0]
         return a.new_empty((M, N), dtype=torch.float32 if out_f32 else a.dtype)
 
+    @reg("sjb200::gemm_16bit_stats")
+    def _(a, b, a_mn, b_mn):
+        M = a.shape[1] if a_mn else a.shape[0]
+        N = b.shape[1] if b_mn else b.shape[0]
+        return a.new_empty((M, N)), a.new_empty(((M + 127) // 128 * 4, 2, N), dtype=torch.float32)
+
     @reg("sjb200::gemm_fp8")
     def _(a, b, alpha, out_f32, split_k):
         return a.new_empty((a.shape[0], b.shape[0]), dtype=torch.float32 if out_f32 else torch.bfloat16)

@@ -20,11 +20,17 @@ __all__ = ["bn_lif", "BNLIFFunction"]
 class BNLIFFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y, gamma, beta, running_mean, running_var, residual, training: bool, momentum: float,
-                eps: float, spec: NeuronSpec, v_init: float, need_grad: bool):
+                eps: float, spec: NeuronSpec, v_init: float, need_grad: bool, stats=None):
         vr = 0.0 if spec.soft else float(spec.v_reset)
-        counters.bump("bn_stats", 2 if training else 1)
-        mean, invstd, scale, shift = torch.ops.sjb200.bn_coefficients(
-            y, gamma, beta, running_mean, running_var, training, momentum, eps)
+        if training and stats is not None:
+            # the producer (GEMM epilogue) already summed y and y^2 per channel: only the finalisation runs
+            counters.bump("bn_stats", 1)
+            mean, invstd, scale, shift = torch.ops.sjb200.bn_coefficients_partial(
+                stats, y.numel() // y.shape[-1], gamma, beta, running_mean, running_var, momentum, eps)
+        else:
+            counters.bump("bn_stats", 2 if training else 1)
+            mean, invstd, scale, shift = torch.ops.sjb200.bn_coefficients(
+                y, gamma, beta, running_mean, running_var, training, momentum, eps)
         counters.bump("bn_lif_forward")
         out, ckpt = torch.ops.sjb200.bn_lif_forward(y, scale, shift, residual, spec.kind, spec.tau, spec.v_threshold,
                                                     vr, spec.soft, v_init, need_grad)
@@ -46,12 +52,14 @@ class BNLIFFunction(torch.autograd.Function):
             ckpt if ckpt.numel() > 0 else None, ctx.training, spec.kind, spec.tau, spec.v_threshold, vr, spec.soft,
             ctx.v_init, spec.sg[0], spec.sg[1], spec.sg[2], spec.detach_reset)
         return (dy, g_gamma if ctx.has_affine else None, g_beta if ctx.has_affine else None, None, None,
-                g_out if ctx.has_residual else None, None, None, None, None, None, None)
+                g_out if ctx.has_residual else None, None, None, None, None, None, None, None)
 
 
 def bn_lif(y: torch.Tensor, bn: torch.nn.modules.batchnorm._BatchNorm, spec: NeuronSpec,
-           residual: Optional[torch.Tensor] = None, v_init: float = 0.0) -> torch.Tensor:
-    """``y``: contiguous ``[T, ..., C]`` with ``C == bn.num_features`` (channels last)."""
+           residual: Optional[torch.Tensor] = None, v_init: float = 0.0,
+           stats: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y``: contiguous ``[T, ..., C]`` with ``C == bn.num_features`` (channels last).  ``stats``: optional
+    ``[blocks, 2, C]`` fp32 partial sums of ``y`` and ``y^2`` per channel (``ops.gemm.linear_with_stats``)."""
     require()
     training = bn.training or bn.running_mean is None
     momentum = 0.0 if bn.momentum is None else float(bn.momentum)
@@ -63,7 +71,7 @@ def bn_lif(y: torch.Tensor, bn: torch.nn.modules.batchnorm._BatchNorm, spec: Neu
     rv = bn.running_var if (bn.track_running_stats and bn.training) or not training else None
     need_grad = torch.is_grad_enabled() and (y.requires_grad or (bn.weight is not None and bn.weight.requires_grad))
     return BNLIFFunction.apply(y.contiguous(), bn.weight, bn.bias, rm, rv, residual, training, momentum, float(bn.eps),
-                               spec, float(v_init), need_grad)
+                               spec, float(v_init), need_grad, stats)
 
 
 class BNPoolLIFFunction(torch.autograd.Function):

@@ -80,7 +80,19 @@ __device__ __forceinline__ void reduce_partials(const float* __restrict__ partia
     const int lane_c = threadIdx.x % kFinCh, slice = threadIdx.x / kFinCh;
     double a1 = 0.0, a2 = 0.0;
     if (c < C) {
-        for (int b = slice; b < nblk; b += kFinSlices) {
+        // sixteen independent loads per round: the serial chain is nblk / 256 memory latencies, not nblk / 32
+        int b = slice;
+        for (; b + 7 * kFinSlices < nblk; b += 8 * kFinSlices) {
+            float p1[8], p2[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                p1[u] = partial[(size_t)(b + u * kFinSlices) * 2 * C + c];
+                p2[u] = partial[(size_t)(b + u * kFinSlices) * 2 * C + C + c];
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) { a1 += (double)p1[u]; a2 += (double)p2[u]; }
+        }
+        for (; b < nblk; b += kFinSlices) {
             a1 += (double)partial[(size_t)b * 2 * C + c];
             a2 += (double)partial[(size_t)b * 2 * C + C + c];
         }
@@ -392,6 +404,31 @@ void launch_bn_finalize_backward(const float* partial, int nblk, int C, double c
 
 // Training-mode or frozen BN coefficients of a channels-last tensor y [*, C].
 // returns (mean, invstd, scale, shift) fp32 [C]; updates running stats in place when training.
+// mean / invstd / scale / shift from partial sums [nblk, 2, C] that some other kernel produced (the tensor-core GEMM's
+// epilogue emits this layout); `rows` is the number of values per channel behind them.
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> bn_coefficients_partial(
+    const at::Tensor& partial, int64_t rows, const c10::optional<at::Tensor>& gamma, const c10::optional<at::Tensor>& beta,
+    const c10::optional<at::Tensor>& running_mean, const c10::optional<at::Tensor>& running_var, double momentum, double eps) {
+    TORCH_CHECK(partial.is_cuda() && partial.is_contiguous() && partial.dim() == 3 && partial.size(1) == 2 &&
+                partial.scalar_type() == at::kFloat, "bn_coefficients_partial: contiguous fp32 CUDA [blocks, 2, C] required");
+    const c10::cuda::CUDAGuard guard(partial.device());
+    const int C = (int)partial.size(2), nblk = (int)partial.size(0);
+    auto fopt = partial.options();
+    at::Tensor mean = at::empty({C}, fopt), invstd = at::empty({C}, fopt), scale = at::empty({C}, fopt), shift = at::empty({C}, fopt);
+    auto fptr = [](const c10::optional<at::Tensor>& t) -> float* {
+        if (!t.has_value() || !t->defined()) return nullptr;
+        TORCH_CHECK(t->scalar_type() == at::kFloat && t->is_contiguous(), "BN parameters and buffers must be contiguous fp32");
+        return t->data_ptr<float>();
+    };
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    bn_finalize_forward_kernel<<<(C + kFinCh - 1) / kFinCh, kFinCh * kFinSlices, 0, stream>>>(
+        partial.data_ptr<float>(), nblk, C, (double)rows, (float)eps, (float)momentum, fptr(gamma), fptr(beta),
+        fptr(running_mean), fptr(running_var), mean.data_ptr<float>(), invstd.data_ptr<float>(), scale.data_ptr<float>(),
+        shift.data_ptr<float>());
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    return {mean, invstd, scale, shift};
+}
+
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> bn_coefficients(
     const at::Tensor& y, const c10::optional<at::Tensor>& gamma, const c10::optional<at::Tensor>& beta,
     const c10::optional<at::Tensor>& running_mean, const c10::optional<at::Tensor>& running_var, bool training,
@@ -550,6 +587,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> bn_lif_backward(
 TORCH_LIBRARY_FRAGMENT(sjb200, m) {
     m.def("bn_coefficients(Tensor y, Tensor? gamma, Tensor? beta, Tensor(a!)? running_mean, Tensor(b!)? running_var, "
           "bool training, float momentum, float eps) -> (Tensor, Tensor, Tensor, Tensor)");
+    m.def("bn_coefficients_partial(Tensor partial, int rows, Tensor? gamma, Tensor? beta, Tensor(a!)? running_mean, "
+          "Tensor(b!)? running_var, float momentum, float eps) -> (Tensor, Tensor, Tensor, Tensor)");
     m.def("bn_lif_forward(Tensor y, Tensor scale, Tensor shift, Tensor? residual, int kind, float tau, float v_th, "
           "float v_reset, bool soft_reset, float v_init, bool save_ckpt) -> (Tensor, Tensor)");
     m.def("bn_lif_backward(Tensor g_out, Tensor y, Tensor scale, Tensor shift, Tensor mean, Tensor invstd, Tensor? gamma, "
@@ -558,6 +597,7 @@ TORCH_LIBRARY_FRAGMENT(sjb200, m) {
 }
 TORCH_LIBRARY_IMPL(sjb200, CUDA, m) {
     m.impl("bn_coefficients", &sjb200::bn_coefficients);
+    m.impl("bn_coefficients_partial", &sjb200::bn_coefficients_partial);
     m.impl("bn_lif_forward", &sjb200::bn_lif_forward);
     m.impl("bn_lif_backward", &sjb200::bn_lif_backward);
 }

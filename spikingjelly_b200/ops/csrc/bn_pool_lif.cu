@@ -230,49 +230,79 @@ bn_pool_lif_backward1_kernel(ScanParams p, PoolGeom g_in, const T* __restrict__ 
     }
 }
 
+// One thread owns a 2 x 2 patch of input pixels (rows 2a, 2a + 1; columns 2b, 2b + 1) and 8 channels.  The patch is
+// covered by exactly the four windows (a .. a + 1) x (b .. b + 1), so four (argmax, gradient) loads serve four pixels,
+// and every load of the thread (4 windows, 4 y vectors, 3 coefficient vectors) is issued before the first use:
+// one memory round trip per thread instead of one per window.
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 bn_pool_backward2_kernel(PoolGeom g, int NB, const T* __restrict__ y, const uint8_t* __restrict__ idx,
                          const T* __restrict__ Gin, const float* __restrict__ coefA, const float* __restrict__ coefB,
                          const float* __restrict__ coefD, T* __restrict__ dy) {
-    // blockIdx.x = image row (img * H + h); blockIdx.y, threadIdx.x = position inside the row (w, channel group):
-    // all index arithmetic is 32-bit, one division per thread
+    // blockIdx.x = img * PH + a;  (blockIdx.y, threadIdx.x) = (b, channel group): 32-bit index arithmetic throughout
     const int G = g.C / V;
-    const int wc = (int)(blockIdx.y * blockDim.x + threadIdx.x);
-    if (wc >= g.W * G) return;
-    const int w = wc / G, c0 = (wc - w * G) * V;
-    const int img = (int)blockIdx.x / g.H, h = (int)blockIdx.x - img * g.H;
-    float acc[V];
+    const int PH = (g.H + 1) / 2, PW = (g.W + 1) / 2;
+    const int bc = (int)(blockIdx.y * blockDim.x + threadIdx.x);
+    if (bc >= PW * G) return;
+    const int pb = bc / G, c0 = (bc - pb * G) * V;
+    const int img = (int)blockIdx.x / PH, pa = (int)blockIdx.x - img * PH;
+    const int h0 = 2 * pa, w0 = 2 * pb;
+    const bool row1 = h0 + 1 < g.H, col1 = w0 + 1 < g.W;
+
+    // windows: k = 2 * dh + dw -> (pa + dh, pb + dw)
+    uint2 code[4];
+    Pack<T, V> graw[4];
 #pragma unroll
-    for (int j = 0; j < V; ++j) acc[j] = 0.0f;
-    // windows (oh, ow) with 2 oh - 1 <= h <= 2 oh + 1
-    const int oh_lo = h / 2, oh_hi = (h + 1) / 2, ow_lo = w / 2, ow_hi = (w + 1) / 2;
-    for (int oh = oh_lo; oh <= oh_hi; ++oh) {
-        if (oh >= g.OH) continue;
-        const uint32_t kh = (uint32_t)(h - (2 * oh - 1));
-        for (int ow = ow_lo; ow <= ow_hi; ++ow) {
-            if (ow >= g.OW) continue;
-            const uint32_t code = kh * 3 + (uint32_t)(w - (2 * ow - 1));
+    for (int k = 0; k < 4; ++k) {
+        const int oh = pa + (k >> 1), ow = pb + (k & 1);
+        code[k] = make_uint2(0xFFFFFFFFu, 0xFFFFFFFFu);       // no argmax code is 0xFF: an absent window matches nothing
+        if (oh < g.OH && ow < g.OW) {
             const long long o = (((long long)img * g.OH + oh) * g.OW + ow) * g.C + c0;
-            const uint2 packed = *reinterpret_cast<const uint2*>(idx + o);
-            float gv[V];
-            load_vec<T, V>(Gin + o, gv);
-#pragma unroll
-            for (int j = 0; j < V; ++j) {
-                const uint32_t cj = ((j < 4 ? packed.x : packed.y) >> (8 * (j & 3))) & 0xFF;
-                acc[j] += (cj == code) ? gv[j] : 0.0f;
-            }
+            code[k] = *reinterpret_cast<const uint2*>(idx + o);
+            graw[k] = *reinterpret_cast<const Pack<T, V>*>(Gin + o);
         }
     }
-    float a[V], b[V], d[V], yy[V], o[V];
+    const long long off00 = (((long long)img * g.H + h0) * g.W + w0) * g.C + c0;
+    const long long rstride = (long long)g.W * g.C;
+    Pack<T, V> yraw[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (((k >> 1) == 0 || row1) && ((k & 1) == 0 || col1))
+            yraw[k] = load_raw_stream<T, V>(y + off00 + (k >> 1) * rstride + (k & 1) * g.C);
+    }
+    float a[V], b[V], d[V];
     load_vec<float, V>(coefA + c0, a);
     load_vec<float, V>(coefB + c0, b);
     load_vec<float, V>(coefD + c0, d);
-    const long long off = (((long long)img * g.H + h) * g.W + w) * g.C + c0;
-    load_vec_stream<T, V>(y + off, yy);
+
+    float gw[4][V];
 #pragma unroll
-    for (int j = 0; j < V; ++j) o[j] = fmaf(a[j], acc[j], fmaf(b[j], yy[j], d[j]));
-    store_vec<T, V>(dy + off, o);
+    for (int k = 0; k < 4; ++k) unpack<T, V>(graw[k], gw[k]);
+    // pixel (dh, dw) of the patch lies at (kh, kw) = (1 + dh - 2 eh, 1 + dw - 2 ew) of window (eh, ew), eh <= dh, ew <= dw
+#pragma unroll
+    for (int px = 0; px < 4; ++px) {
+        const int dh = px >> 1, dw = px & 1;
+        if ((dh == 1 && !row1) || (dw == 1 && !col1)) continue;
+        float acc[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int eh = k >> 1, ew = k & 1;
+            if (eh > dh || ew > dw) continue;
+            const uint32_t want = (uint32_t)((1 + dh - 2 * eh) * 3 + (1 + dw - 2 * ew));
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                const uint32_t cj = ((j < 4 ? code[k].x : code[k].y) >> (8 * (j & 3))) & 0xFF;
+                acc[j] += (cj == want) ? gw[k][j] : 0.0f;
+            }
+        }
+        float yy[V], o[V];
+        unpack<T, V>(yraw[px], yy);
+#pragma unroll
+        for (int j = 0; j < V; ++j) o[j] = fmaf(a[j], acc[j], fmaf(b[j], yy[j], d[j]));
+        store_vec<T, V>(dy + off00 + dh * rstride + dw * g.C, o);
+    }
 }
 
 #define SJ_POOL_DISPATCH(DTYPE, ...)                                                        \
@@ -395,7 +425,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> bn_pool_lif_backward(
                                 mean.data_ptr<float>(), invstd.data_ptr<float>(), grad_gamma.data_ptr<float>(),
                                 grad_beta.data_ptr<float>(), coef.data_ptr<float>(), coef.data_ptr<float>() + g.C,
                                 coef.data_ptr<float>() + 2 * g.C, stream);
-    const dim3 grid2((unsigned)(NB * g.H), (unsigned)((g.W * G + kThreads - 1) / kThreads));
+    const dim3 grid2((unsigned)(NB * ((g.H + 1) / 2)), (unsigned)((((g.W + 1) / 2) * G + kThreads - 1) / kThreads));
     SJ_POOL_DISPATCH(y.scalar_type(), {
         bn_pool_backward2_kernel<scalar_t><<<grid2, kThreads, 0, stream>>>(
             g, NB, reinterpret_cast<const scalar_t*>(y.data_ptr()), idx.data_ptr<uint8_t>(),

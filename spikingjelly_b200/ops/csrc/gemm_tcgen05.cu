@@ -56,6 +56,8 @@ struct GemmArgs {
     int ab_format;          // kind::f16: 0 = fp16, 1 = bf16;  kind::f8f6f4: 0 = e4m3, 1 = e5m2 (A and B alike)
     int out_bf16;           // 16-bit results are bf16 (else fp16)
     const float* alpha;     // optional device scalar multiplied into the result (product of the fp8 scales)
+    float* stats;           // optional [ceil(M / 128) * 4][2][N]: per-column sum and sum of squares of the rounded
+                            // 16-bit result over each 32-row slice (batch-norm statistics without re-reading D)
 };
 
 // ES: operand element size in bytes (2: fp16 / bf16, 1: fp8).  A k-block is always one 128-byte
@@ -234,6 +236,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         tma_store_2d(&tmD, stage_buf, n0 + c * 32, m0);
                         tma_store_commit();
                     }
+                    if (g.stats != nullptr) {
+                        // Column sums over this warp's own 32 staged rows (the rounded values BN will read).
+                        // Lane = (column pair, row half); the upper half walks its rows one step ahead so that the
+                        // two halves hit different 64-byte halves of a bank line.
+                        const int cp = lane & 15, hi = lane >> 4;
+                        float s1a = 0.f, s1b = 0.f, s2a = 0.f, s2b = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int rr = quarter * 32 + hi * 16 + ((i + hi) & 15);
+                            const int chunk = (cp >> 2) ^ ((rr >> 1) & 3);
+                            const uint32_t w = *reinterpret_cast<const uint32_t*>(stage_buf + rr * 64 + chunk * 16 + (cp & 3) * 4);
+                            float lo, up;
+                            if (g.out_bf16) { lo = __uint_as_float(w << 16); up = __uint_as_float(w & 0xffff0000u); }
+                            else { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w)); lo = f.x; up = f.y; }
+                            s1a += lo; s1b += up; s2a = fmaf(lo, lo, s2a); s2b = fmaf(up, up, s2b);
+                        }
+                        s1a += __shfl_xor_sync(0xffffffffu, s1a, 16); s1b += __shfl_xor_sync(0xffffffffu, s1b, 16);
+                        s2a += __shfl_xor_sync(0xffffffffu, s2a, 16); s2b += __shfl_xor_sync(0xffffffffu, s2b, 16);
+                        const int col = n0 + c * 32 + cp * 2;
+                        if (hi == 0 && col < g.N) {
+                            float* dst = g.stats + ((size_t)((m0 / BM) * 4 + quarter) * 2) * g.N + col;
+                            *reinterpret_cast<float2*>(dst) = make_float2(s1a, s1b);
+                            *reinterpret_cast<float2*>(dst + g.N) = make_float2(s2a, s2b);
+                        }
+                    }
                 }
             }
             fence_before_sync();
@@ -296,7 +323,8 @@ void launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
 //   a_mn == false: `a` is [M, K] (K contiguous);  a_mn == true: `a` is [K, M] (M contiguous)
 //   b_mn == false: `b` is [N, K] (K contiguous);  b_mn == true: `b` is [K, N] (N contiguous)
 //   out_f32: result dtype fp32 instead of the input dtype;  split_k: 0 = choose, else forced
-at::Tensor gemm_16bit(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, bool out_f32, int64_t split_k) {
+static at::Tensor gemm_16bit_impl(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, bool out_f32, int64_t split_k,
+                                  at::Tensor* stats) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda(), "gemm_16bit: CUDA tensors required");
     TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm_16bit: 2-D operands required");
     TORCH_CHECK(a.scalar_type() == b.scalar_type() && (a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf),
@@ -322,6 +350,7 @@ at::Tensor gemm_16bit(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool 
         splits = 1;
         if (tiles * 2 <= sms && kb_total >= 16) splits = std::min(std::max(1, sms / tiles), kb_total / 4);
     }
+    if (stats != nullptr) splits = 1;                      // the statistics come from complete 16-bit tiles
     splits = std::max(1, std::min(splits, kb_total));
     int kb_per = (kb_total + splits - 1) / splits;
     splits = (kb_total + kb_per - 1) / kb_per;
@@ -333,6 +362,12 @@ at::Tensor gemm_16bit(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool 
     g.ab_format = bf16 ? 1 : 0;
     g.out_bf16 = bf16 ? 1 : 0;
     g.alpha = nullptr;
+    g.stats = nullptr;
+    if (stats != nullptr) {
+        TORCH_CHECK(!out_f32, "gemm_16bit: column statistics need a 16-bit result");
+        *stats = at::empty({(M + BM - 1) / BM * 4, 2, N}, a.options().dtype(at::kFloat));
+        g.stats = stats->data_ptr<float>();
+    }
 
     const CUtensorMap ta = a_mn ? make_map(A.data_ptr(), K, M, A.stride(0), BK, bf16)
                                 : make_map(A.data_ptr(), M, K, A.stride(0), BM, bf16);
@@ -375,6 +410,18 @@ at::Tensor gemm_16bit(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool 
         C10_CUDA_KERNEL_LAUNCH_CHECK();
     }
     return out;
+}
+
+at::Tensor gemm_16bit(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, bool out_f32, int64_t split_k) {
+    return gemm_16bit_impl(a, b, a_mn, b_mn, out_f32, split_k, nullptr);
+}
+
+// The same product plus partial[blk][0 | 1][n] = sum | sum of squares of D[32 * blk .. 32 * blk + 31][n] (rows past M
+// count as zero), taken from the rounded 16-bit values inside the epilogue: a following batch norm needs no pass over D.
+std::tuple<at::Tensor, at::Tensor> gemm_16bit_stats(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn) {
+    at::Tensor stats;
+    at::Tensor out = gemm_16bit_impl(a, b, a_mn, b_mn, false, 1, &stats);
+    return {out, stats};
 }
 
 // D[M, N] (bf16) = alpha * A[M, K] (.) B[N, K]^T with fp8 operands (both e4m3 or both e5m2, K contiguous) and fp32
@@ -458,11 +505,13 @@ std::vector<int64_t> gemm_status(const at::Tensor& like) {
 
 TORCH_LIBRARY_FRAGMENT(sjb200, m) {
     m.def("gemm_16bit(Tensor a, Tensor b, bool a_mn, bool b_mn, bool out_f32, int split_k) -> Tensor");
+    m.def("gemm_16bit_stats(Tensor a, Tensor b, bool a_mn, bool b_mn) -> (Tensor, Tensor)");
     m.def("gemm_fp8(Tensor a, Tensor b, Tensor? alpha, bool out_f32, int split_k) -> Tensor");
     m.def("gemm_status(Tensor like) -> int[]");
 }
 TORCH_LIBRARY_IMPL(sjb200, CUDA, m) {
     m.impl("gemm_16bit", &sjb200::gemm_16bit);
+    m.impl("gemm_16bit_stats", &sjb200::gemm_16bit_stats);
     m.impl("gemm_fp8", &sjb200::gemm_fp8);
     m.impl("gemm_status", &sjb200::gemm_status);
 }

@@ -57,16 +57,23 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
     __half2 v = __floats2half2_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Stage `rows` rows of D contiguous elements (row stride `gstride` in global) into a padded tile and
-// zero rows [rows, rows_pad).
+// Stage `rows` rows of D contiguous elements (row stride `gstride` in global) into a padded tile with
+// asynchronous 16-byte copies (no register round trip: every copy of the tile is in flight at once, which is
+// what hides the DRAM latency with a single resident CTA per SM) and zero rows [rows, rows_pad).
+// The caller commits the group and waits for it.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+
 template <typename T, int D>
 __device__ __forceinline__ void stage(const T* __restrict__ g, long long gstride, int rows, int rows_pad, T* __restrict__ s) {
     constexpr int CH = D / 8, LD = Geo<D>::LD;
     for (int i = threadIdx.x; i < rows_pad * CH; i += blockDim.x) {
         const int l = i / CH, c = i % CH;
-        int4 v = make_int4(0, 0, 0, 0);
-        if (l < rows) v = *reinterpret_cast<const int4*>(g + (long long)l * gstride + c * 8);
-        *reinterpret_cast<int4*>(s + l * LD + c * 8) = v;
+        if (l < rows) cp_async16(s_addr(s + l * LD + c * 8), g + (long long)l * gstride + c * 8);
+        else *reinterpret_cast<int4*>(s + l * LD + c * 8) = make_int4(0, 0, 0, 0);
     }
 }
 
@@ -105,9 +112,9 @@ __device__ __forceinline__ void gram(const T* __restrict__ X, const T* __restric
 }
 
 // dst[l][j] = alpha * sum_c X[l][c] * M[c][j]  (TRANS = false)   or   alpha * sum_c X[l][c] * M[j][c]  (TRANS = true)
-// X: padded tile (Lp rows), M: padded [D][LD] tile; dst: global, row stride `dstride`, rows l < L.
+// X: padded tile (Lp rows; overwritten with the result), M: padded [D][LD] tile; dst: global, row stride `dstride`, rows l < L.
 template <typename T, int D, bool TRANS>
-__device__ __forceinline__ void apply(const T* __restrict__ X, const T* __restrict__ M, int L, int Lp, float alpha,
+__device__ __forceinline__ void apply(T* __restrict__ X, const T* __restrict__ M, int L, int Lp, float alpha,
                                       T* __restrict__ dst, long long dstride) {
     constexpr int LD = Geo<D>::LD, NT = D / 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -127,11 +134,21 @@ __device__ __forceinline__ void apply(const T* __restrict__ X, const T* __restri
                 mma16816<T>(acc[nt + 1], a, b[2], b[3]);
             }
         }
+        // Rows [m0, m0 + 16) of X are read by this warp only and are dead now: the result goes back into them, and
+        // leaves as 16-byte stores of whole 2 * D-byte rows instead of 4-byte fragments.
+        __syncwarp();
         const int row = m0 + (lane >> 2), col = (lane & 3) * 2;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            if (row < L) *reinterpret_cast<uint32_t*>(dst + (long long)row * dstride + nt * 8 + col) = pack2<T>(alpha * acc[nt][0], alpha * acc[nt][1]);
-            if (row + 8 < L) *reinterpret_cast<uint32_t*>(dst + (long long)(row + 8) * dstride + nt * 8 + col) = pack2<T>(alpha * acc[nt][2], alpha * acc[nt][3]);
+            *reinterpret_cast<uint32_t*>(X + row * LD + nt * 8 + col) = pack2<T>(alpha * acc[nt][0], alpha * acc[nt][1]);
+            *reinterpret_cast<uint32_t*>(X + (row + 8) * LD + nt * 8 + col) = pack2<T>(alpha * acc[nt][2], alpha * acc[nt][3]);
+        }
+        __syncwarp();
+        constexpr int CH = D / 8;
+#pragma unroll
+        for (int i = lane; i < 16 * CH; i += 32) {
+            const int l = m0 + i / CH, c = i % CH;
+            if (l < L) *reinterpret_cast<int4*>(dst + (long long)l * dstride + c * 8) = *reinterpret_cast<const int4*>(X + l * LD + c * 8);
         }
     }
 }
@@ -149,11 +166,15 @@ ssa_forward_kernel(const T* __restrict__ S, T* __restrict__ O, int L, int Lp, in
     const int head = blockIdx.x % H;
     const long long tb = blockIdx.x / H;
     const T* base = S + tb * L * 3 * C + head * D;
-    stage<T, D>(base, 3LL * C, L, Lp, Qs);
     stage<T, D>(base + C, 3LL * C, L, Lp, Ks);
     stage<T, D>(base + 2 * C, 3LL * C, L, Lp, Vs);
+    cp_async_commit();
+    stage<T, D>(base, 3LL * C, L, Lp, Qs);
+    cp_async_commit();
+    cp_async_wait<1>();                       // K and V have landed; Q is still in flight under the gram
     __syncthreads();
     gram<T, D>(Ks, Vs, Lp, 1.0f, KV);
+    cp_async_wait<0>();
     __syncthreads();
     apply<T, D, false>(Qs, KV, L, Lp, scale, O + tb * L * C + head * D, C);
 }
@@ -173,12 +194,17 @@ ssa_backward_kernel(const T* __restrict__ S, const T* __restrict__ dO, T* __rest
     const int head = blockIdx.x % H;
     const long long tb = blockIdx.x / H;
     const T* base = S + tb * L * 3 * C + head * D;
-    stage<T, D>(base, 3LL * C, L, Lp, Qs);
     stage<T, D>(base + C, 3LL * C, L, Lp, Ks);
     stage<T, D>(base + 2 * C, 3LL * C, L, Lp, Vs);
+    cp_async_commit();
+    stage<T, D>(base, 3LL * C, L, Lp, Qs);
     stage<T, D>(dO + tb * L * C + head * D, C, L, Lp, Gs);
+    cp_async_commit();
+    cp_async_wait<1>();                       // K and V have landed; Q and dO are still in flight under the first gram
     __syncthreads();
     gram<T, D>(Ks, Vs, Lp, 1.0f, KV);         // K^T V
+    cp_async_wait<0>();
+    __syncthreads();
     gram<T, D>(Qs, Gs, Lp, scale, dKV);       // scale Q^T dO
     __syncthreads();
     T* dbase = dS + tb * L * 3 * C + head * D;

@@ -9,7 +9,7 @@ import torch
 
 from . import counters, require
 
-__all__ = ["gemm", "linear", "check_status"]
+__all__ = ["gemm", "linear", "linear_with_stats", "check_status"]
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = False, out_f32: bool = False,
@@ -49,6 +49,28 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             gw = gemm(gy, x2d, True, True, out_f32=False)      # [M, N]^T x [M, K] -> [N, K]
         return gx, gw
+
+
+class _LinearStats(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x2d, weight):
+        ctx.save_for_backward(x2d, weight)
+        require()
+        counters.bump("gemm_tcgen05")
+        y, stats = torch.ops.sjb200.gemm_16bit_stats(x2d, weight, False, False)
+        ctx.mark_non_differentiable(stats)
+        return y, stats
+
+    @staticmethod
+    def backward(ctx, gy, _gstats):
+        return _Linear.backward(ctx, gy)
+
+
+def linear_with_stats(x2d: torch.Tensor, weight: torch.Tensor):
+    """``(x2d @ weight.T, partial)`` where ``partial[b, 0 | 1, n]`` is the sum | sum of squares of rows
+    ``32 b .. 32 b + 31`` of the (rounded) result: the batch-norm statistics come out of the GEMM's epilogue
+    instead of a second pass over the output.  Pass ``partial`` to ``ops.bn_lif.bn_lif(..., stats=partial)``."""
+    return _LinearStats.apply(x2d, weight)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -65,3 +65,31 @@ def test_linear_autograd():
     torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=5e-2)
     torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=5e-2)
     torch.testing.assert_close(w.grad.float(), wr.grad, rtol=2e-2, atol=2e-1)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1000, 264, 200), (392, 128, 512), (6272, 1536, 512)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_epilogue_column_statistics(M, N, K, dtype):
+    """Per-channel sum and sum of squares from the GEMM epilogue equal those of the stored 16-bit result, and the
+    batch-norm coefficients built from them equal the ones of the stand-alone statistics kernel."""
+    torch.manual_seed(1)
+    x = torch.randn(M, K, device=DEV).to(dtype).requires_grad_(True)
+    w = (torch.randn(N, K, device=DEV) * 0.1).to(dtype).requires_grad_(True)
+    y, part = G.linear_with_stats(x, w)
+    G.check_status(y)
+    assert part.shape == ((M + 127) // 128 * 4, 2, N) and not part.requires_grad
+    torch.testing.assert_close(y.float(), G.gemm(x.detach(), w.detach()).float(), rtol=0, atol=0)
+    yd = y.detach().double()
+    torch.testing.assert_close(part[:, 0].double().sum(0), yd.sum(0), rtol=1e-5, atol=1e-3)
+    torch.testing.assert_close(part[:, 1].double().sum(0), (yd * yd).sum(0), rtol=1e-5, atol=1e-3)
+    if N % 8 == 0 and N <= 4096:
+        a = torch.ops.sjb200.bn_coefficients_partial(part, M, None, None, None, None, 0.1, 1e-5)
+        b = torch.ops.sjb200.bn_coefficients(y.detach(), None, None, None, None, True, 0.1, 1e-5)
+        for u, v in zip(a, b):
+            torch.testing.assert_close(u, v, rtol=1e-5, atol=1e-6)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    (xr @ wr.t()).backward(g.float())
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=5e-2)
+    torch.testing.assert_close(w.grad.float(), wr.grad, rtol=2e-2, atol=3e-1)
