@@ -45,7 +45,8 @@ struct Smem {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BAR_OFFSET + 1024 + 1024;            // + slack for 1024 B alignment
+    static constexpr int OUT_OFFSET = BAR_OFFSET + 1024;              // epilogue staging: 4 warps x [32 rows][64 cols] bf16
+    static constexpr int TOTAL = OUT_OFFSET + 4 * 4096 + 1024;        // + slack for 1024 B alignment
 };
 
 struct SpikeGemmArgs {
@@ -215,14 +216,18 @@ spike_gemm_kernel(const __grid_constant__ CUtensorMap tmB, const SpikeGemmArgs g
             if (!ok) { if (lane == 0) { report(status, WAIT_TMEM_FULL, tile); *abort_flag = 1; } break; }
             fence_after_sync();
             const int row = m0 + quarter * 32 + lane;
-            __nv_bfloat16* drow;
+            // rows of one tile share their owner (row blocks of a source rank are multiples of BM)
+            __nv_bfloat16* dtile;                        // row `m0 + quarter * 32` of the destination
             if (EPI == 0) {
-                drow = g.d_local + (size_t)row * g.ldd;
+                dtile = g.d_local + (size_t)(m0 + quarter * 32) * g.ldd;
             } else {
                 int owner; long long local_row;
                 locate(g, true, m0, owner, local_row);
-                drow = g.d_dst[owner] + (size_t)g.rank * g.slot_elems + (size_t)(local_row + quarter * 32 + lane) * g.N;
+                dtile = g.d_dst[owner] + (size_t)g.rank * g.slot_elems + (size_t)(local_row + quarter * 32) * g.N;
             }
+            const size_t dld = EPI == 0 ? (size_t)g.ldd : (size_t)g.N;
+            __nv_bfloat16* drow = dtile + (size_t)lane * dld;
+            uint8_t* stg = smem + L::OUT_OFFSET + quarter * 4096;      // this warp's [32][64] bf16, 16-byte chunks XOR (row & 7)
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
@@ -230,19 +235,42 @@ spike_gemm_kernel(const __grid_constant__ CUtensorMap tmB, const SpikeGemmArgs g
                 tmem_ld_32x32(taddr + c * 32, rr);
                 tmem_ld_wait();
                 const int col0 = n0 + c * 32;
-                if (row < g.M && col0 < g.N) {
-                    uint32_t w[16];
+                uint32_t w[16];
 #pragma unroll
-                    for (int q = 0; q < 16; ++q) {
-                        __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(rr[2 * q]), __uint_as_float(rr[2 * q + 1]));
-                        w[q] = *reinterpret_cast<uint32_t*>(&v);
+                for (int q = 0; q < 16; ++q) {
+                    __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(rr[2 * q]), __uint_as_float(rr[2 * q + 1]));
+                    w[q] = *reinterpret_cast<uint32_t*>(&v);
+                }
+                const int pair0 = n0 + (c & ~1) * 32;    // first column of the 64-column pair this chunk belongs to
+                if (pair0 + 64 <= g.N) {
+                    // Stage two 32-column chunks, then leave as 128-byte row segments: eight lanes per row, four rows per
+                    // store instruction.  A lane-per-row store would put 32 separate 16-byte pieces on the wire, which is
+                    // what made the peer push slow over NVLink.
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        *reinterpret_cast<uint4*>(stg + lane * 128 + ((((c & 1) * 4 + q) ^ (lane & 7)) << 4)) =
+                            make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+                    if (c & 1) {
+                        __syncwarp();
+                        const int ch = lane & 7;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = i * 4 + (lane >> 3);
+                            const uint4 v = *reinterpret_cast<const uint4*>(stg + r * 128 + ((ch ^ (r & 7)) << 4));
+                            if (m0 + quarter * 32 + r < g.M)
+                                *reinterpret_cast<uint4*>(dtile + (size_t)r * dld + pair0 + ch * 8) = v;
+                        }
+                        __syncwarp();
                     }
+                } else if (row < g.M && col0 < g.N) {
                     if (col0 + 32 <= g.N) {
 #pragma unroll
                         for (int q = 0; q < 4; ++q)
                             reinterpret_cast<uint4*>(drow + col0)[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
                     } else {
-                        for (int q = 0; q < 16 && col0 + 2 * q < g.N; ++q) *reinterpret_cast<uint32_t*>(drow + col0 + 2 * q) = w[q];
+#pragma unroll
+                        for (int q = 0; q < 16; ++q)
+                            if (col0 + 2 * q < g.N) *reinterpret_cast<uint32_t*>(drow + col0 + 2 * q) = w[q];
                     }
                 }
             }
@@ -299,9 +327,14 @@ lif_pack_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ out, 
 
 // RMSNorm over C, then the same LIF, then bit-pack.  h: [T, rows, C] (fp32 or bf16); one block per row;
 // blockDim.x * 8 == C.
+struct PackDst {
+    uint8_t* p[comm::kMaxWorld];   // where this rank's packed rows go: one buffer per rank of the group (its own included)
+    int n;
+};
+
 template <typename HT>
 __global__ void __launch_bounds__(512)
-rmsnorm_lif_pack_kernel(const HT* __restrict__ h, const float* __restrict__ weight, uint8_t* __restrict__ out, int T, long long rows,
+rmsnorm_lif_pack_kernel(const HT* __restrict__ h, const float* __restrict__ weight, PackDst dst, int T, long long rows,
                         int C, long long pitch, float eps, float inv_tau, float v_th) {
     __shared__ float red[16];
     const long long row = blockIdx.x;
@@ -341,7 +374,17 @@ rmsnorm_lif_pack_kernel(const HT* __restrict__ h, const float* __restrict__ weig
             bits |= (s ? 1u : 0u) << q;
             v[q] = s ? 0.f : hh;
         }
-        out[((size_t)t * rows + row) * pitch + threadIdx.x] = (uint8_t)bits;
+        // sixteen lanes' bytes travel as one 16-byte store per destination (a peer store of single bytes would
+        // put one NVLink packet on the wire per byte)
+        const uint32_t full = 0xffffffffu;
+        const uint32_t w32 = bits | (__shfl_down_sync(full, bits, 1) << 8) | (__shfl_down_sync(full, bits, 2) << 16) |
+                             (__shfl_down_sync(full, bits, 3) << 24);
+        uint4 q;
+        q.x = w32; q.y = __shfl_down_sync(full, w32, 4); q.z = __shfl_down_sync(full, w32, 8); q.w = __shfl_down_sync(full, w32, 12);
+        if ((threadIdx.x & 15) == 0) {
+            const size_t off = ((size_t)t * rows + row) * pitch + threadIdx.x;
+            for (int d = 0; d < dst.n; ++d) *reinterpret_cast<uint4*>(dst.p[d] + off) = q;
+        }
     }
 }
 
@@ -460,7 +503,9 @@ void lif_pack(const at::Tensor& x, int64_t out_ptr, int64_t pitch, double tau, d
     C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
-void rmsnorm_lif_pack(const at::Tensor& h, const at::Tensor& weight, int64_t out_ptr, int64_t pitch, double eps, double tau, double v_th) {
+// Packed spikes of LIF_T(RMSNorm(h)) are written to every pointer of `out_ptrs` (the same bytes to each): with the peers'
+// gather buffers in the list the all-gather of the spikes happens as stores out of the producing kernel.
+void rmsnorm_lif_pack(const at::Tensor& h, const at::Tensor& weight, std::vector<int64_t> out_ptrs, int64_t pitch, double eps, double tau, double v_th) {
     TORCH_CHECK(h.is_cuda() && h.dim() == 3 && h.is_contiguous(), "rmsnorm_lif_pack: contiguous [T, rows, C]");
     TORCH_CHECK(weight.scalar_type() == at::kFloat && weight.is_contiguous() && weight.numel() == h.size(2), "rmsnorm_lif_pack: fp32 weight [C]");
     const int T = (int)h.size(0), C = (int)h.size(2);
@@ -468,7 +513,13 @@ void rmsnorm_lif_pack(const at::Tensor& h, const at::Tensor& weight, int64_t out
     TORCH_CHECK(C % 256 == 0 && C <= 4096 && pitch * 8 >= C, "rmsnorm_lif_pack: C must be a multiple of 256, at most 4096");
     const c10::cuda::CUDAGuard guard(h.device());
     cudaStream_t st = at::cuda::getCurrentCUDAStream();
-    uint8_t* out = reinterpret_cast<uint8_t*>(out_ptr);
+    TORCH_CHECK(!out_ptrs.empty() && (int)out_ptrs.size() <= comm::kMaxWorld && pitch % 16 == 0, "rmsnorm_lif_pack: 1..16 destinations, pitch a multiple of 16");
+    PackDst out{};
+    out.n = (int)out_ptrs.size();
+    for (int d = 0; d < out.n; ++d) {
+        TORCH_CHECK(out_ptrs[d] % 16 == 0, "rmsnorm_lif_pack: destinations must be 16-byte aligned");
+        out.p[d] = reinterpret_cast<uint8_t*>(out_ptrs[d]);
+    }
     if (h.scalar_type() == at::kFloat)
         rmsnorm_lif_pack_kernel<float><<<(unsigned)rows, C / 8, 0, st>>>(h.data_ptr<float>(), weight.data_ptr<float>(), out, T, rows, C, pitch, (float)eps, (float)(1.0 / tau), (float)v_th);
     else if (h.scalar_type() == at::kBFloat16)
@@ -508,7 +559,7 @@ void tp_barrier(std::vector<int64_t> sig_ptrs, int64_t rank, int64_t epoch, at::
 TORCH_LIBRARY_FRAGMENT(sjb200, m) {
     m.def("spike_gemm(int[] a_ptrs, int a_pitch, int M, int K, Tensor w, int rows_per_t, int rows_per_src, int rank, int[] push_ptrs, int slot_elems) -> Tensor");
     m.def("lif_pack(Tensor x, int out_ptr, int pitch, float tau, float v_th) -> ()");
-    m.def("rmsnorm_lif_pack(Tensor h, Tensor weight, int out_ptr, int pitch, float eps, float tau, float v_th) -> ()");
+    m.def("rmsnorm_lif_pack(Tensor h, Tensor weight, int[] out_ptrs, int pitch, float eps, float tau, float v_th) -> ()");
     m.def("tp_reduce_residual(Tensor(a!) h, int stage_ptr, int slot_elems, int world) -> ()");
     m.def("tp_barrier(int[] sig_ptrs, int rank, int epoch, Tensor(a!) status, float timeout_s) -> ()");
 }

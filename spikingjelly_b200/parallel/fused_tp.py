@@ -3,10 +3,13 @@
 The residual stream ``h`` is split by tokens over the group (rank ``r`` holds ``h[:, r * n : (r + 1) * n]``).
 One fused sub-layer ``h += W2 . LIF(W1 . LIF(RMSNorm(h)))`` with ``W1`` split by rows and ``W2`` by columns runs as
 
-1. ``rmsnorm_lif_pack``: norm + LIF over T on the local tokens, spikes written as bits into symmetric memory;
+1. ``rmsnorm_lif_pack``: norm + LIF over T on the local tokens; the spikes leave the kernel as bits, stored into
+   the gather buffer of EVERY rank (16-byte peer stores: the all-gather is the producer's epilogue and moves 1/16
+   of the bf16 payload, once per peer);
 2. barrier; ``spike_gemm`` (gather): every rank multiplies ALL tokens by its rows of ``W1`` — the A-operand producer
-   of the GEMM reads the 1-bit rows straight from the peers' buffers (all-gather inside the operand fetch,
-   1/16 of the bf16 payload);
+   of the GEMM expands the 1-bit rows of all source ranks from its local gather buffer (the kernel takes one
+   pointer per source rank, so it can also read the peers' buffers in place; measured on two GPUs that costs
+   the NVLink latency once per n-tile and is slower than the push);
 3. ``lif_pack``: LIF over T on the local columns, bits stay local;
 4. ``spike_gemm`` (push): partial products of ``W2`` leave the epilogue as peer stores into the owner's staging slot
    (reduce-scatter inside the epilogue);
@@ -60,13 +63,16 @@ class FusedTPWorkspace:
         ops.require()
         if self.world > 1:
             import torch.distributed._symmetric_memory as symm
-            self.bits_x = symm.empty(self.rows * self.x_pitch, dtype=torch.uint8, device=self.device)
+            self.bits_x = symm.empty(self.world * self.rows * self.x_pitch, dtype=torch.uint8, device=self.device)
             self.stage = symm.empty(self.world * self.slot_elems, dtype=torch.bfloat16, device=self.device)
             self._signal = symm.empty(self.world, dtype=torch.int32, device=self.device)
             for t in (self.bits_x, self.stage, self._signal):
                 t.zero_()
             hb, hs, hg = (symm.rendezvous(t, self.group) for t in (self.bits_x, self.stage, self._signal))
-            self.bits_ptrs: List[int] = [int(p) for p in hb.buffer_ptrs]
+            slot = self.rows * self.x_pitch                      # one source rank's packed rows
+            # the GEMM reads source s from the local slot s; this rank's pack kernel writes slot `rank` everywhere
+            self.bits_ptrs: List[int] = [self.bits_x.data_ptr() + s * slot for s in range(self.world)]
+            self.bits_push_ptrs: List[int] = [int(p) + self.rank * slot for p in hb.buffer_ptrs]
             self.stage_ptrs: List[int] = [int(p) for p in hs.buffer_ptrs]
             self.sig_ptrs: List[int] = [int(p) for p in hg.buffer_ptrs]
             self._handles = (hb, hs, hg)
@@ -77,6 +83,7 @@ class FusedTPWorkspace:
             self.stage = torch.zeros(self.slot_elems, dtype=torch.bfloat16, device=self.device)
             self._signal = torch.zeros(1, dtype=torch.int32, device=self.device)
             self.bits_ptrs, self.stage_ptrs, self.sig_ptrs = [self.bits_x.data_ptr()], [self.stage.data_ptr()], [self._signal.data_ptr()]
+            self.bits_push_ptrs = [self.bits_x.data_ptr()]
         self._status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._local_bits: dict = {}
 
@@ -141,7 +148,7 @@ class FusedSpikingSubLayer(nn.Module):
         ops = torch.ops.sjb200
         tokens = ws.tokens_per_rank * ws.world
         M = ws.T * tokens
-        ops.rmsnorm_lif_pack(h, self.norm_weight, ws.bits_x.data_ptr(), ws.x_pitch, self.eps, self.tau, self.v_threshold)
+        ops.rmsnorm_lif_pack(h, self.norm_weight, ws.bits_push_ptrs, ws.x_pitch, self.eps, self.tau, self.v_threshold)
         ws.barrier()                                             # everybody's spikes are in place
         u = ops.spike_gemm(ws.bits_ptrs, ws.x_pitch, M, ws.d_model, self.w1, tokens, ws.tokens_per_rank, ws.rank, [], 0)
         bits_u = ws.local_bits(self.f_pad)

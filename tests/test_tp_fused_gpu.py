@@ -69,7 +69,7 @@ def test_lif_and_rmsnorm_packers_match_reference():
         w = torch.rand(C, device=dev) + 0.5
         pitch = pack_pitch(C)
         out = torch.zeros(T * rows, pitch, dtype=torch.uint8, device=dev)
-        torch.ops.sjb200.rmsnorm_lif_pack(h, w, out.data_ptr(), pitch, 1e-6, 2.0, 1.0)
+        torch.ops.sjb200.rmsnorm_lif_pack(h, w, [out.data_ptr()], pitch, 1e-6, 2.0, 1.0)
         hf = h.float()
         xn = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6) * w
         ref = _lif_seq(xn, 2.0, 1.0).reshape(T * rows, C)
