@@ -20,6 +20,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..activation_based import layer, neuron, surrogate
+from ..ops import pool as pool_ops
 from ..ops.bn_lif import bn_lif
 from ..ops.neuron_scan import KIND, NeuronSpec
 
@@ -116,7 +117,10 @@ def forward(model, x: torch.Tensor) -> torch.Tensor:
     h = x.flatten(0, 1).to(dt).contiguous(memory_format=torch.channels_last)
     h = _stage(model.conv1, model.bn1, model.sn1, h, T)
     mp = model.maxpool
-    h = F.max_pool2d(h, mp.kernel_size, mp.stride, mp.padding, mp.dilation, mp.ceil_mode)
+    if pool_ops.supports(mp, h):
+        h = pool_ops.max_pool_3x3s2_channels_last(h)
+    else:
+        h = F.max_pool2d(h, mp.kernel_size, mp.stride, mp.padding, mp.dilation, mp.ceil_mode)
     for stage in (model.layer1, model.layer2, model.layer3, model.layer4):
         for blk in stage:
             h = _block(blk, h, T)

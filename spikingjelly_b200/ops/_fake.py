@@ -28,6 +28,16 @@ def register() -> None:
         N = b.shape[1] if b_mn else b.shape[0]
         return a.new_empty((M, N)), a.new_empty(((M + 127) // 128 * 4, 2, N), dtype=torch.float32)
 
+    @reg("sjb200::maxpool3x3s2_nhwc_forward")
+    def _(x):
+        n, h, w, c = x.shape
+        shape = (n, (h - 1) // 2 + 1, (w - 1) // 2 + 1, c)
+        return x.new_empty(shape), x.new_empty(shape, dtype=torch.uint8)
+
+    @reg("sjb200::maxpool3x3s2_nhwc_backward")
+    def _(g_out, idx, H, W):
+        return g_out.new_empty((g_out.shape[0], H, W, g_out.shape[3]))
+
     @reg("sjb200::gemm_fp8")
     def _(a, b, alpha, out_f32, split_k):
         return a.new_empty((a.shape[0], b.shape[0]), dtype=torch.float32 if out_f32 else torch.bfloat16)
