@@ -20,6 +20,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..activation_based import layer, neuron, surrogate
+from ..ops import conv_stem as stem_ops
 from ..ops import pool as pool_ops
 from ..ops.bn_lif import bn_lif
 from ..ops.neuron_scan import KIND, NeuronSpec
@@ -88,6 +89,13 @@ def _rows(t: torch.Tensor, T: int) -> torch.Tensor:
 
 
 def _stage(conv, bn, sn, h: torch.Tensor, T: int, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if residual is None and stem_ops.supports(conv, h):
+        # few input channels (the network input): patch matrix + tensor-core GEMM whose epilogue also sums the BN statistics
+        training = bn.training or bn.running_mean is None
+        rows, stats, (H, W) = stem_ops.conv2d_few_channels(h, conv.weight, conv.stride, conv.padding, want_stats=training)
+        C = rows.shape[1]
+        out = bn_lif(rows.view(T, -1, C), bn, _spec(sn), v_init=_init_v(sn), stats=stats)
+        return out.view(h.shape[0], H, W, C).permute(0, 3, 1, 2)
     y = _conv(conv, h)
     TB, C, H, W = y.shape
     out = bn_lif(_rows(y, T), bn, _spec(sn), residual=None if residual is None else _rows(residual, T), v_init=_init_v(sn))

@@ -24,6 +24,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..activation_based import neuron, surrogate
+from ..ops import conv_stem as stem_ops
 from ..ops import gemm as G
 from ..ops.bn_lif import bn_lif, bn_pool_lif
 from ..ops.ssa import ssa as ssa_op
@@ -75,7 +76,12 @@ def _stem_stage(stage, h: torch.Tensor, T: int, static: bool, dt) -> torch.Tenso
     """``h``: NHWC-in-memory ``[T*B (or B when static), C, H, W]`` -> spikes ``[T*B, C', H', W']``."""
     conv, bn = stage.conv_bn.block[0], stage.conv_bn.block[1]
     pool = stage.conv_bn.block[2] if len(stage.conv_bn.block) > 2 else None
-    y = F.conv2d(h, conv.weight.to(dt), None, conv.stride, conv.padding, conv.dilation, conv.groups)
+    if stem_ops.supports(conv, h):
+        # the image itself (3 channels): patch matrix + tensor-core GEMM instead of cuDNN's padded-channel kernel
+        rows, _, (oh, ow) = stem_ops.conv2d_few_channels(h, conv.weight, conv.stride, conv.padding, want_stats=False)
+        y = rows.view(h.shape[0], oh, ow, rows.shape[1]).permute(0, 3, 1, 2)
+    else:
+        y = F.conv2d(h, conv.weight.to(dt), None, conv.stride, conv.padding, conv.dilation, conv.groups)
     lif = stage.neuron
     spec = _spec(lif)
     if pool is None:

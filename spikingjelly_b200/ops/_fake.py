@@ -38,6 +38,12 @@ def register() -> None:
     def _(g_out, idx, H, W):
         return g_out.new_empty((g_out.shape[0], H, W, g_out.shape[3]))
 
+    @reg("sjb200::im2col_nhwc")
+    def _(x, KH, KW, sh, sw, ph, pw):
+        n, h, w, c = x.shape
+        oh, ow = (h + 2 * ph - KH) // sh + 1, (w + 2 * pw - KW) // sw + 1
+        return x.new_empty((n * oh * ow, (KH * KW * c + 7) // 8 * 8))
+
     @reg("sjb200::gemm_fp8")
     def _(a, b, alpha, out_f32, split_k):
         return a.new_empty((a.shape[0], b.shape[0]), dtype=torch.float32 if out_f32 else torch.bfloat16)

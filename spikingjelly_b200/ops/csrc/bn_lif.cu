@@ -404,6 +404,25 @@ void launch_bn_finalize_backward(const float* partial, int nblk, int C, double c
 
 // Training-mode or frozen BN coefficients of a channels-last tensor y [*, C].
 // returns (mean, invstd, scale, shift) fp32 [C]; updates running stats in place when training.
+// partial [nblk, 2, C] -> out [gridDim.x, 2, C]: block b sums rows [b * per, (b + 1) * per) in order (deterministic).  Used
+// when a producer emits so many partial rows that the per-channel finalisation (C / 8 blocks) would be the slow part.
+__global__ void __launch_bounds__(256)
+bn_partial_fold_kernel(const float* __restrict__ partial, int nblk, int width, int per, float* __restrict__ out) {
+    const int r0 = blockIdx.x * per, r1 = min(nblk, r0 + per);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        int r = r0;
+        for (; r + 3 < r1; r += 4) {
+            a0 += partial[(size_t)r * width + i];
+            a1 += partial[(size_t)(r + 1) * width + i];
+            a2 += partial[(size_t)(r + 2) * width + i];
+            a3 += partial[(size_t)(r + 3) * width + i];
+        }
+        for (; r < r1; ++r) a0 += partial[(size_t)r * width + i];
+        out[(size_t)blockIdx.x * width + i] = (a0 + a1) + (a2 + a3);
+    }
+}
+
 // mean / invstd / scale / shift from partial sums [nblk, 2, C] that some other kernel produced (the tensor-core GEMM's
 // epilogue emits this layout); `rows` is the number of values per channel behind them.
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> bn_coefficients_partial(
@@ -412,8 +431,21 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> bn_coefficients_parti
     TORCH_CHECK(partial.is_cuda() && partial.is_contiguous() && partial.dim() == 3 && partial.size(1) == 2 &&
                 partial.scalar_type() == at::kFloat, "bn_coefficients_partial: contiguous fp32 CUDA [blocks, 2, C] required");
     const c10::cuda::CUDAGuard guard(partial.device());
-    const int C = (int)partial.size(2), nblk = (int)partial.size(0);
+    const int C = (int)partial.size(2);
+    int nblk = (int)partial.size(0);
     auto fopt = partial.options();
+    cudaStream_t stream0 = at::cuda::getCurrentCUDAStream();
+    at::Tensor folded;
+    const float* pptr = partial.data_ptr<float>();
+    if (nblk > 2048) {
+        const int rows_out = 512, per = (nblk + rows_out - 1) / rows_out;
+        const int used = (nblk + per - 1) / per;
+        folded = at::empty({used, 2, C}, fopt);
+        bn_partial_fold_kernel<<<used, 256, 0, stream0>>>(pptr, nblk, 2 * C, per, folded.data_ptr<float>());
+        C10_CUDA_KERNEL_LAUNCH_CHECK();
+        pptr = folded.data_ptr<float>();
+        nblk = used;
+    }
     at::Tensor mean = at::empty({C}, fopt), invstd = at::empty({C}, fopt), scale = at::empty({C}, fopt), shift = at::empty({C}, fopt);
     auto fptr = [](const c10::optional<at::Tensor>& t) -> float* {
         if (!t.has_value() || !t->defined()) return nullptr;
@@ -422,7 +454,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> bn_coefficients_parti
     };
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
     bn_finalize_forward_kernel<<<(C + kFinCh - 1) / kFinCh, kFinCh * kFinSlices, 0, stream>>>(
-        partial.data_ptr<float>(), nblk, C, (double)rows, (float)eps, (float)momentum, fptr(gamma), fptr(beta),
+        pptr, nblk, C, (double)rows, (float)eps, (float)momentum, fptr(gamma), fptr(beta),
         fptr(running_mean), fptr(running_var), mean.data_ptr<float>(), invstd.data_ptr<float>(), scale.data_ptr<float>(),
         shift.data_ptr<float>());
     C10_CUDA_KERNEL_LAUNCH_CHECK();
