@@ -7,3 +7,5 @@ from .neuron_state import *  # noqa: F401,F403
 from .lemaire_addressing import *  # noqa: F401,F403
 from .analytical_energy import *  # noqa: F401,F403
 from .memory_residency import *  # noqa: F401,F403
+from . import spikesim  # noqa: F401
+from .spikesim import *  # noqa: F401,F403

@@ -139,3 +139,48 @@ def test_memory_residency_hierarchy():
     assert "aten.addmm" in next(iter(k for k in c.get_op_level_bits() if "addmm" in k))
     c.reset()
     assert c.get_level_bits() == {}
+
+
+def _spikesim_net(ab):
+    torch.manual_seed(0)
+    return torch.nn.Sequential(
+        ab.layer.Conv2d(3, 70, 3, padding=1, bias=False), ab.neuron.IFNode(),
+        ab.layer.Conv2d(70, 130, 3, stride=2, padding=1, bias=False), ab.neuron.LIFNode(),
+        ab.layer.Conv2d(130, 20, 1, bias=False)).eval()
+
+
+@pytest.mark.parametrize("mode", ["dense", "event"])
+def test_spikesim_energy_equals_reference(mode):
+    import importlib, sys
+    from pathlib import Path
+    import spikingjelly_b200.activation_based as ours_ab
+    from spikingjelly_b200.activation_based.op_counter import spikesim as ours
+    net = _spikesim_net(ours_ab)
+    x = torch.rand(2, 3, 12, 12)
+    cfg = ours.SpikeSimEnergyConfig(activity_mode=mode, xbar_size=64)
+    rep = ours.estimate_spikesim_event_energy(net, x, config=cfg)
+    assert rep.counts["stage_count"] == 3 and rep.energy_total_pj > 0
+    # dense PE cycles by hand: ceil(Cin/64) * ceil(Cout/64) * sites
+    assert rep.counts["dense_pe_cycle_count"] == 1 * 2 * 2 * 144 + 2 * 3 * 2 * 36 + 3 * 1 * 2 * 36
+    if mode == "event":
+        st = rep.event_stats_by_stage["1" if "1" in rep.event_stats_by_stage else list(rep.event_stats_by_stage)[1]]
+        assert st["active_row_count"] <= st["dense_row_count"]
+    ref_dir = Path(__file__).resolve().parents[1] / "baseline" / "_ref"
+    if not (ref_dir / "spikingjelly").exists():
+        pytest.skip("reference package not installed under baseline/_ref")
+    sys.path.insert(0, str(ref_dir))
+    try:
+        ref_ab = importlib.import_module("spikingjelly.activation_based")
+        ref = importlib.import_module("spikingjelly.activation_based.op_counter.spikesim")
+        importlib.import_module("spikingjelly.activation_based.layer"); importlib.import_module("spikingjelly.activation_based.neuron")
+    finally:
+        sys.path.remove(str(ref_dir))
+    net_r = _spikesim_net(ref_ab)
+    net_r.load_state_dict(net.state_dict())
+    rep_r = ref.estimate_spikesim_event_energy(net_r, x, config=ref.SpikeSimEnergyConfig(activity_mode=mode, xbar_size=64))
+    assert rep.energy_total_pj == pytest.approx(rep_r.energy_total_pj, rel=1e-9)
+    assert rep.counts == rep_r.counts
+    for stage, e in rep_r.energy_by_stage.items():
+        assert rep.energy_by_stage[stage] == pytest.approx(e, rel=1e-9)
+    for k, v in rep_r.breakdown_pj.items():
+        assert rep.breakdown_pj[k] == pytest.approx(v, rel=1e-9)
