@@ -22,3 +22,40 @@ def test_flexsn_and_distributed_examples_run(capsys):
     assert len(rates) == 2 and rates[0] == rates[1]
     train_distributed.main(["--synthetic", "--max-steps", "1", "--T", "2", "--batch-size", "2", "--resolution", "32"])
     assert "mode none" in capsys.readouterr().out
+
+
+def test_stdp_examples_run_and_match_closed_form():
+    from spikingjelly_b200.activation_based.examples import mstdp, mstdpet, stdp_trace
+    s = stdp_trace.main(["-T", "120"])
+    assert s["post_spikes"] > 0 and abs(s["w_final"] - s["w_expected"]) < 1e-5
+    s = mstdp.main(["-T", "120"])
+    assert s["target_dw"] != 0.0 and s["other_dw"] < 1e-6
+    s = mstdpet.main(["-T", "60"])
+    assert s["other_dw"] < 1e-6
+
+
+def test_recurrent_examples_run():
+    from spikingjelly_b200.activation_based.examples import rsnn_sequential_fmnist, spiking_lstm_sequential_mnist
+    for model in ("plain", "feedback"):
+        s = rsnn_sequential_fmnist.main(["--model", model, "--synthetic", "--device", "cpu", "--max-steps", "3", "--hidden", "16", "-b", "16"])
+        assert s["train_loss"] > 0
+    s = spiking_lstm_sequential_mnist.main(["--synthetic", "--device", "cpu", "--max-steps", "2", "--hidden", "8", "-b", "8"])
+    assert s["test_loss"] > 0
+
+
+def test_dqn_examples_run_on_builtin_cartpole():
+    from spikingjelly_b200.activation_based.examples import DQN_state, Spiking_DQN_state, _cartpole
+    env = _cartpole.CartPole(0)
+    s = _cartpole.reset_env(env)
+    assert len(s) == 4
+    steps = 0
+    while True:                                  # always pushing one way tips the pole over well before the step cap
+        s, r, over, fell = _cartpole.step_env(env, 1)
+        steps += 1
+        if over:
+            break
+    assert fell and 5 < steps < 100
+    out = Spiking_DQN_state.main(["--episodes", "3", "--hidden", "16", "-T", "4", "--batch-size", "8", "--builtin-env"])
+    assert out["best"] >= 1
+    out = DQN_state.main(["--episodes", "3", "--hidden", "16", "--batch-size", "8", "--builtin-env"])
+    assert out["best"] >= 1
