@@ -38,8 +38,12 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--iters", type=int, default=11)
     ap.add_argument("--only", default="")
+    ap.add_argument("--pair", type=int, default=-1, help="1 / 0: force the two-CTA (cta_group::2) kernel on / off; -1: library default")
     a = ap.parse_args()
     dev = "cuda"
+    G.require()
+    if a.pair >= 0:
+        torch.ops.sjb200.gemm_set_pair_mode(a.pair)
     M = 4 * 32 * 196
     shapes = [("qkv_fwd", M, 1536, 512), ("proj_fwd", M, 512, 512), ("fc1_fwd", M, 2048, 512), ("fc2_fwd", M, 512, 2048),
               ("n128", M, 128, 2048), ("square8k", 8192, 8192, 8192)]
@@ -60,7 +64,7 @@ def main():
         for cname, (ours, ref) in cases.items():
             t_o = timeit(ours, flush, a.iters)
             t_r = timeit(ref, flush, a.iters)
-            row = {"shape": name, "op": cname, "M": m, "N": n, "K": k, "ours_us": round(t_o, 1), "cublas_us": round(t_r, 1),
+            row = {"pair": a.pair, "shape": name, "op": cname, "M": m, "N": n, "K": k, "ours_us": round(t_o, 1), "cublas_us": round(t_r, 1),
                    "ours_tflops": round(flops / t_o / 1e6, 1), "cublas_tflops": round(flops / t_r / 1e6, 1)}
             print(json.dumps(row), flush=True)
             rows.append(row)

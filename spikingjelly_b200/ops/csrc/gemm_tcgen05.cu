@@ -21,6 +21,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cstdlib>
 #include <torch/library.h>
 
 #include "tc_common.cuh"
@@ -46,6 +47,19 @@ struct SmemLayout {
     static constexpr int OUT_BYTES = BM * 32 * 2;
     static constexpr int TOTAL = OUT_OFFSET + 4 * OUT_BYTES + 1024;   // + slack for 1024 B alignment
 };
+
+// Output tiles are visited in column groups of kGroupN tiles: within a group all row tiles are visited (n fastest), so
+// the CTAs that run together share kGroupN column tiles of B (they stay in L2 for the whole group) and a few row
+// tiles of A.  With plain n-fastest order a wide B (N * K * 2 B beyond the L2 size) is re-read from DRAM once per
+// row of tiles.
+constexpr int kGroupN = 8;
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int per_group = tiles_m * kGroupN;
+    const int grp = t / per_group, in = t - grp * per_group;
+    const int gw = min(kGroupN, tiles_n - grp * kGroupN);
+    tm = in / gw;
+    tn = grp * kGroupN + (in - tm * gw);
+}
 
 struct GemmArgs {
     int M, N, K;            // logical sizes (K = contraction)
@@ -108,7 +122,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
                 const int split = tile / tiles_mn, mn = tile % tiles_mn;
-                const int m0 = (mn / tiles_n) * BM, n0 = (mn % tiles_n) * BN;
+                int tm, tn;
+                tile_coords(mn, tiles_m, tiles_n, tm, tn);
+                const int m0 = tm * BM, n0 = tn * BN;
                 const int kb0 = split * g.kb_per_split;
                 const int kb1 = min(kb_total, kb0 + g.kb_per_split);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -178,7 +194,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         uint32_t tl = 0, oc = 0;                   // tiles / output chunks handled so far
         for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tl) {
             const int split = tile / tiles_mn, mn = tile % tiles_mn;
-            const int m0 = (mn / tiles_n) * BM, n0 = (mn % tiles_n) * BN;
+            int tm, tn;
+            tile_coords(mn, tiles_m, tiles_n, tm, tn);
+            const int m0 = tm * BM, n0 = tn * BN;
             const uint32_t acc = tl & 1, acc_ph = (tl >> 1) & 1;
             bool ok = true;
             if (lane == 0) ok = mbar_wait_bounded(tfull_bar + acc, acc_ph);
@@ -281,6 +299,227 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
 }
 
+// ---- CTA-pair variant -----------------------------------------------------------------------------------
+// Two CTAs of a cluster (two SMs) work on one 256 x 256 output tile.  Each CTA loads 128 rows of A and 128 of the 256
+// columns' worth of B per k-block (32 KB instead of the 48 KB a 128 x 256 single-CTA tile needs for half the
+// output), one thread of the pair's first CTA issues `tcgen05.mma.cta_group::2` (M = 256, N = 256), and each CTA ends
+// up with its 128 rows x 256 columns of the accumulator in its own TMEM, which its own epilogue warps drain.
+// Barrier protocol:
+//   full[s]   (first CTA only)  expect 2 x 32 KB: both producers' TMA loads credit it
+//   empty[s]  (each CTA)        one arrival per round: the MMA thread commits to the local and to the peer's barrier
+//   tfull[a]  (each CTA)        likewise, after the last k-block of a tile
+//   tempty[a] (first CTA only)  16 arrivals: the 8 epilogue warps of both CTAs
+// Cluster barriers bracket the kernel: nobody signals into a CTA whose barriers are not initialised yet, and no CTA
+// retires (or frees tensor memory) while its partner may still read its shared memory or write its TMEM.
+constexpr int kPairStages = 5;
+constexpr int kPairBN = 256;
+struct PairSmem {
+    static constexpr int A_BYTES = BM * BK * 2;                 // this CTA's 128 rows of A
+    static constexpr int B_BYTES = (kPairBN / 2) * BK * 2;      // this CTA's 128 of the 256 columns of B
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_OFFSET = kPairStages * STAGE_BYTES;
+    static constexpr int OUT_OFFSET = BAR_OFFSET + 1024;
+    static constexpr int OUT_BYTES = BM * 32 * 2;
+    static constexpr int TOTAL = OUT_OFFSET + 4 * OUT_BYTES + 1024;
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmD, GemmArgs g, KernelStatus* __restrict__ status) {
+    using L = PairSmem;
+    constexpr int STAGES = kPairStages, BN = kPairBN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tfull_bar = empty_bar + STAGES;
+    uint64_t* tempty_bar = tfull_bar + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                 // 0: issues the MMAs; 1: partner
+    const bool first = rank == 0;
+    const int tiles_m = (g.M + 2 * BM - 1) / (2 * BM), tiles_n = (g.N + BN - 1) / BN;
+    const int total_tiles = tiles_m * tiles_n;
+    const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
+    const int kb_total = (g.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar + a, 1); mbar_init(tempty_bar + a, 16); }
+        *abort_flag = 0;
+        mbar_init_fence();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    __syncthreads();
+    cluster_sync_all();                                      // both CTAs' barriers exist before anyone signals them
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 2 * BN);
+        tmem_relinquish_pair();
+    }
+    fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                                      // both halves of the accumulator are allocated
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (one thread in each CTA)
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs) {
+                int tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                const int m0 = tm * (2 * BM) + (int)rank * BM;
+                const int nb0 = tn * BN + (int)rank * (BN / 2);                    // this CTA's half of the B columns
+                for (int kb = 0; kb < kb_total; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait_bounded(empty_bar + s, ph ^ 1)) { report(status, WAIT_EMPTY, s); *abort_flag = 1; break; }
+                    uint8_t* sa = smem + s * L::STAGE_BYTES;
+                    uint8_t* sb = sa + L::A_BYTES;
+                    if (first) mbar_expect_tx(full_bar + s, 2 * L::STAGE_BYTES);
+                    const uint32_t bar = map_to_cta(smem_u32(full_bar + s), 0);
+                    const int k0 = kb * BK;
+                    if (A_MN) {
+#pragma unroll
+                        for (int c = 0; c < BM / 64; ++c) tma_load_2d_pair(sa + c * (BK * 128), &tmA, m0 + c * 64, k0, bar);
+                    } else {
+                        tma_load_2d_pair(sa, &tmA, k0, m0, bar);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int c = 0; c < (BN / 2) / 64; ++c) tma_load_2d_pair(sb + c * (BK * 128), &tmB, nb0 + c * 64, k0, bar);
+                    } else {
+                        tma_load_2d_pair(sb, &tmB, k0, nb0, bar);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- MMA issuer (first CTA only)
+        if (lane == 0 && first) {
+            const uint32_t idesc = make_idesc_f16(g.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, 2 * BM, BN);
+            uint32_t it = 0, tl = 0;
+            for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs, ++tl) {
+                const uint32_t acc = tl & 1, acc_ph = (tl >> 1) & 1;
+                if (!mbar_wait_bounded(tempty_bar + acc, acc_ph ^ 1)) { report(status, WAIT_TMEM_EMPTY, tile); *abort_flag = 1; break; }
+                fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < kb_total; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait_bounded(full_bar + s, ph)) { report(status, WAIT_FULL, s); *abort_flag = 1; break; }
+                    fence_after_sync();
+                    const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+                    const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+                    for (int j = 0; j < BK / UMMA_K; ++j) {
+                        const uint64_t da = A_MN ? make_smem_desc(sa + j * (UMMA_K * 128), BK * 128, 1024)
+                                                 : make_smem_desc(sa + j * (UMMA_K * 2), 16, 1024);
+                        const uint64_t db = B_MN ? make_smem_desc(sb + j * (UMMA_K * 128), BK * 128, 1024)
+                                                 : make_smem_desc(sb + j * (UMMA_K * 2), 16, 1024);
+                        mma_f16_ss_pair(d_tmem, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                    }
+                    const uint32_t eb = smem_u32(empty_bar + s);
+                    mma_commit_pair(eb);                       // this CTA's stage is reusable ...
+                    mma_commit_pair(map_to_cta(eb, 1));        // ... and the partner's
+                }
+                const uint32_t tb = smem_u32(tfull_bar + acc);
+                mma_commit_pair(tb);
+                mma_commit_pair(map_to_cta(tb, 1));
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (both CTAs: own 128 rows)
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int issuer = 64 + half * 128;
+        const uint32_t tempty_first = map_to_cta(smem_u32(tempty_bar), 0);
+        uint32_t tl = 0, oc = 0;
+        for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs, ++tl) {
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int m0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * BN;
+            const uint32_t acc = tl & 1, acc_ph = (tl >> 1) & 1;
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait_bounded(tfull_bar + acc, acc_ph);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { if (lane == 0) { report(status, WAIT_TMEM_FULL, tile); *abort_flag = 1; } break; }
+            fence_after_sync();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + c * 32, r);
+                tmem_ld_wait();
+                uint8_t* stage_buf = smem + L::OUT_OFFSET + (half * 2 + (oc & 1)) * L::OUT_BYTES;
+                if (oc >= 2 && (int)threadIdx.x == issuer) tma_store_wait_read<1>();
+                ++oc;
+                named_barrier(1 + half, 128);
+                const int r_in_tile = quarter * 32 + lane;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float lo = __uint_as_float(r[8 * q + 2 * e]), hi = __uint_as_float(r[8 * q + 2 * e + 1]);
+                        if (g.out_bf16) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
+                        else { __half2 v = __floats2half2_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
+                    }
+                    const int chunk = q ^ ((r_in_tile >> 1) & 3);
+                    *reinterpret_cast<uint4*>(stage_buf + r_in_tile * 64 + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                fence_async_smem();
+                named_barrier(1 + half, 128);
+                if ((int)threadIdx.x == issuer) {
+                    tma_store_2d(&tmD, stage_buf, n0 + c * 32, m0);
+                    tma_store_commit();
+                }
+                if (g.stats != nullptr) {
+                    const int cp = lane & 15, hi = lane >> 4;
+                    float s1a = 0.f, s1b = 0.f, s2a = 0.f, s2b = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int rr = quarter * 32 + hi * 16 + ((i + hi) & 15);
+                        const int chunk = (cp >> 2) ^ ((rr >> 1) & 3);
+                        const uint32_t w = *reinterpret_cast<const uint32_t*>(stage_buf + rr * 64 + chunk * 16 + (cp & 3) * 4);
+                        float lo, up;
+                        if (g.out_bf16) { lo = __uint_as_float(w << 16); up = __uint_as_float(w & 0xffff0000u); }
+                        else { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w)); lo = f.x; up = f.y; }
+                        s1a += lo; s1b += up; s2a = fmaf(lo, lo, s2a); s2b = fmaf(up, up, s2b);
+                    }
+                    s1a += __shfl_xor_sync(0xffffffffu, s1a, 16); s1b += __shfl_xor_sync(0xffffffffu, s1b, 16);
+                    s2a += __shfl_xor_sync(0xffffffffu, s2a, 16); s2b += __shfl_xor_sync(0xffffffffu, s2b, 16);
+                    const int col = n0 + c * 32 + cp * 2;
+                    if (hi == 0 && col < g.N) {
+                        float* dst = g.stats + ((size_t)((m0 / BM) * 4 + quarter) * 2) * g.N + col;
+                        *reinterpret_cast<float2*>(dst) = make_float2(s1a, s1b);
+                        *reinterpret_cast<float2*>(dst + g.N) = make_float2(s2a, s2b);
+                    }
+                }
+            }
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_first + acc * 8);      // the MMA thread lives in the first CTA
+        }
+        if ((int)threadIdx.x == issuer) tma_store_wait_all<0>();
+    }
+
+    // -------------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                                      // the partner is done with this CTA's shared memory and TMEM
+    fence_after_sync();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, 2 * BN);
+}
+
 // out[m, n] = sum_s partial[s, m, n]   (fixed order), cast to OUT
 template <typename OUT>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, OUT* __restrict__ out, long long mn, int splits,
@@ -315,6 +554,27 @@ void launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
         configured = true;
     }
     kern<<<grid, kThreads, L::TOTAL, stream>>>(ta, tb, td, d, g, st);
+}
+
+template <bool A_MN, bool B_MN>
+void launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmArgs& g, KernelStatus* st,
+                 int grid, cudaStream_t stream) {
+    auto kern = gemm_pair_kernel<A_MN, B_MN>;
+    static bool configured = false;
+    if (!configured) {
+        C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL));
+        configured = true;
+    }
+    kern<<<grid, kThreads, PairSmem::TOTAL, stream>>>(ta, tb, td, g, st);
+}
+
+// 0: never use CTA pairs; 1: use them where the shape allows (16-bit result, no split-K, M and N >= 256)
+int& pair_mode() {
+    static int mode = []() {
+        const char* e = std::getenv("SJB200_GEMM_PAIR");
+        return e != nullptr ? std::atoi(e) : 1;
+    }();
+    return mode;
 }
 
 }  // namespace
@@ -363,10 +623,32 @@ static at::Tensor gemm_16bit_impl(const at::Tensor& a, const at::Tensor& b, bool
     g.out_bf16 = bf16 ? 1 : 0;
     g.alpha = nullptr;
     g.stats = nullptr;
+    const bool use_pair = pair_mode() != 0 && !g.out_f32 && splits == 1 && M >= 2 * BM && N >= kPairBN && sms >= 2;
     if (stats != nullptr) {
         TORCH_CHECK(!out_f32, "gemm_16bit: column statistics need a 16-bit result");
-        *stats = at::empty({(M + BM - 1) / BM * 4, 2, N}, a.options().dtype(at::kFloat));
+        // the pair kernel works on 256-row tiles: its last tile may cover one more (all-zero) 128-row slice
+        const int64_t slices = use_pair ? (M + 2 * BM - 1) / (2 * BM) * 2 : (M + BM - 1) / BM;
+        *stats = at::empty({slices * 4, 2, N}, a.options().dtype(at::kFloat));
         g.stats = stats->data_ptr<float>();
+    }
+    if (use_pair) {
+        const CUtensorMap pa = a_mn ? make_map(A.data_ptr(), K, M, A.stride(0), BK, bf16)
+                                    : make_map(A.data_ptr(), M, K, A.stride(0), BM, bf16);
+        const CUtensorMap pb = b_mn ? make_map(B.data_ptr(), K, N, B.stride(0), BK, bf16)
+                                    : make_map(B.data_ptr(), N, K, B.stride(0), kPairBN / 2, bf16);
+        at::Tensor out = at::empty({M, N}, a.options());
+        const CUtensorMap pd = make_map(out.data_ptr(), M, N, N, BM, bf16, 32);
+        at::Tensor& stw = status_word(a.device());
+        KernelStatus* stp = reinterpret_cast<KernelStatus*>(stw.data_ptr<int>());
+        const int ptiles = (int)(((M + 2 * BM - 1) / (2 * BM)) * ((N + kPairBN - 1) / kPairBN));
+        const int grid = 2 * std::min(ptiles, sms / 2);
+        cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+        if (a_mn && b_mn) launch_pair<true, true>(pa, pb, pd, g, stp, grid, stream);
+        else if (a_mn) launch_pair<true, false>(pa, pb, pd, g, stp, grid, stream);
+        else if (b_mn) launch_pair<false, true>(pa, pb, pd, g, stp, grid, stream);
+        else launch_pair<false, false>(pa, pb, pd, g, stp, grid, stream);
+        C10_CUDA_KERNEL_LAUNCH_CHECK();
+        return out;
     }
 
     const CUtensorMap ta = a_mn ? make_map(A.data_ptr(), K, M, A.stride(0), BK, bf16)
@@ -492,6 +774,13 @@ at::Tensor gemm_fp8(const at::Tensor& a, const at::Tensor& b, const c10::optiona
     return out;
 }
 
+// Switches the CTA-pair kernel on (1) or off (0) for the shapes it supports; returns the previous setting.
+int64_t gemm_set_pair_mode(int64_t mode) {
+    const int prev = pair_mode();
+    pair_mode() = (int)mode;
+    return prev;
+}
+
 // (code, block, detail) of the first bounded wait that gave up since the last call; resets it.
 std::vector<int64_t> gemm_status(const at::Tensor& like) {
     at::Tensor& st = status_word(like.device());
@@ -508,6 +797,10 @@ TORCH_LIBRARY_FRAGMENT(sjb200, m) {
     m.def("gemm_16bit_stats(Tensor a, Tensor b, bool a_mn, bool b_mn) -> (Tensor, Tensor)");
     m.def("gemm_fp8(Tensor a, Tensor b, Tensor? alpha, bool out_f32, int split_k) -> Tensor");
     m.def("gemm_status(Tensor like) -> int[]");
+    m.def("gemm_set_pair_mode(int mode) -> int");
+}
+TORCH_LIBRARY_IMPL(sjb200, CompositeExplicitAutograd, m) {
+    m.impl("gemm_set_pair_mode", &sjb200::gemm_set_pair_mode);
 }
 TORCH_LIBRARY_IMPL(sjb200, CUDA, m) {
     m.impl("gemm_16bit", &sjb200::gemm_16bit);

@@ -77,7 +77,8 @@ def test_epilogue_column_statistics(M, N, K, dtype):
     w = (torch.randn(N, K, device=DEV) * 0.1).to(dtype).requires_grad_(True)
     y, part = G.linear_with_stats(x, w)
     G.check_status(y)
-    assert part.shape == ((M + 127) // 128 * 4, 2, N) and not part.requires_grad
+    # 32-row slices; the two-CTA kernel rounds M up to 256-row tiles (the extra slices hold zeros)
+    assert part.shape[0] in ((M + 127) // 128 * 4, (M + 255) // 256 * 8) and part.shape[1:] == (2, N) and not part.requires_grad
     torch.testing.assert_close(y.float(), G.gemm(x.detach(), w.detach()).float(), rtol=0, atol=0)
     yd = y.detach().double()
     torch.testing.assert_close(part[:, 0].double().sum(0), yd.sum(0), rtol=1e-5, atol=1e-3)
@@ -93,3 +94,37 @@ def test_epilogue_column_statistics(M, N, K, dtype):
     (xr @ wr.t()).backward(g.float())
     torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=5e-2)
     torch.testing.assert_close(w.grad.float(), wr.grad, rtol=2e-2, atol=3e-1)
+
+
+@pytest.fixture
+def pair_mode():
+    G.require()
+    prev = torch.ops.sjb200.gemm_set_pair_mode(1)
+    yield
+    torch.ops.sjb200.gemm_set_pair_mode(prev)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 512), (1000, 264, 200), (6272, 1536, 512)])
+def test_cta_pair_kernel_layouts(pair_mode, a_mn, b_mn, M, N, K):
+    """The two-CTA (cta_group::2) kernel against fp32 matmul, every operand layout, ragged edges in M, N and K."""
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV).to(torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV).to(torch.bfloat16)
+    out = G.gemm(a, b, a_mn, b_mn)
+    G.check_status(out)
+    torch.testing.assert_close(out.float(), _ref(a, b, a_mn, b_mn), rtol=2e-2, atol=2e-2 * K ** 0.5)
+
+
+def test_cta_pair_kernel_statistics_and_determinism(pair_mode):
+    torch.manual_seed(2)
+    x = torch.randn(1500, 512, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(520, 512, device=DEV) * 0.1).to(torch.bfloat16)
+    y, part = G.linear_with_stats(x, w)
+    G.check_status(y)
+    yd = y.double()
+    torch.testing.assert_close(part[:, 0].double().sum(0), yd.sum(0), rtol=1e-5, atol=1e-3)
+    torch.testing.assert_close(part[:, 1].double().sum(0), (yd * yd).sum(0), rtol=1e-5, atol=1e-3)
+    torch.ops.sjb200.gemm_set_pair_mode(0)
+    y1 = G.gemm(x, w)
+    assert torch.equal(y, y1)            # same k order and rounding as the single-CTA kernel
