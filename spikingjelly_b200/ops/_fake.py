@@ -26,7 +26,9 @@ def register() -> None:
     def _(a, b, a_mn, b_mn):
         M = a.shape[1] if a_mn else a.shape[0]
         N = b.shape[1] if b_mn else b.shape[0]
-        rows = (M + 255) // 256 * 8 if (M >= 256 and N >= 256) else (M + 127) // 128 * 4     # 256-row tiles on the two-CTA kernel
+        K = a.shape[0] if a_mn else a.shape[1]
+        pair = M >= 256 and N >= 256 and (K + 63) // 64 >= 16       # the shapes that run on the two-CTA kernel (256-row tiles)
+        rows = (M + 255) // 256 * 8 if pair else (M + 127) // 128 * 4
         return a.new_empty((M, N)), a.new_empty((rows, 2, N), dtype=torch.float32)
 
     @reg("sjb200::maxpool3x3s2_nhwc_forward")

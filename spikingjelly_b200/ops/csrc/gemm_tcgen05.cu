@@ -223,7 +223,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             for (int q = 0; q < 8; ++q)
                                 reinterpret_cast<uint4*>(dst)[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
                         } else {
-                            for (int q = 0; q < 32 && col0 + q < g.N; ++q) dst[q] = __uint_as_float(r[q]);
+#pragma unroll
+                            for (int q = 0; q < 32; ++q)
+                                if (col0 + q < g.N) dst[q] = __uint_as_float(r[q]);
                         }
                     }
                 }
@@ -311,7 +313,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 //   tempty[a] (first CTA only)  16 arrivals: the 8 epilogue warps of both CTAs
 // Cluster barriers bracket the kernel: nobody signals into a CTA whose barriers are not initialised yet, and no CTA
 // retires (or frees tensor memory) while its partner may still read its shared memory or write its TMEM.
-constexpr int kPairStages = 5;
+constexpr int kPairStages = 6;
 constexpr int kPairBN = 256;
 struct PairSmem {
     static constexpr int A_BYTES = BM * BK * 2;                 // this CTA's 128 rows of A
@@ -323,10 +325,12 @@ struct PairSmem {
     static constexpr int TOTAL = OUT_OFFSET + 4 * OUT_BYTES + 1024;
 };
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int ES = 2>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmD, GemmArgs g, KernelStatus* __restrict__ status) {
+                 const __grid_constant__ CUtensorMap tmD, void* __restrict__ Dptr, GemmArgs g, KernelStatus* __restrict__ status) {
+    static_assert(ES == 2 || (!A_MN && !B_MN), "8-bit operands are K-major only");
+    constexpr int BKE = 128 / ES;                            // elements per k-block (one 128-byte swizzle row)
     using L = PairSmem;
     constexpr int STAGES = kPairStages, BN = kPairBN;
     extern __shared__ uint8_t smem_raw[];
@@ -342,9 +346,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t rank = cluster_ctarank();                 // 0: issues the MMAs; 1: partner
     const bool first = rank == 0;
     const int tiles_m = (g.M + 2 * BM - 1) / (2 * BM), tiles_n = (g.N + BN - 1) / BN;
-    const int total_tiles = tiles_m * tiles_n;
+    const int tiles_mn = tiles_m * tiles_n;
+    const int total_tiles = tiles_mn * g.split_k;
     const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
-    const int kb_total = (g.K + BK - 1) / BK;
+    const int kb_total = (g.K + BKE - 1) / BKE;
+    const float alpha = g.alpha != nullptr ? __ldg(g.alpha) : 1.0f;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
@@ -371,11 +377,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) {
             uint32_t it = 0;
             for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs) {
+                const int split = tile / tiles_mn;
                 int tm, tn;
-                tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                tile_coords(tile - split * tiles_mn, tiles_m, tiles_n, tm, tn);
                 const int m0 = tm * (2 * BM) + (int)rank * BM;
                 const int nb0 = tn * BN + (int)rank * (BN / 2);                    // this CTA's half of the B columns
-                for (int kb = 0; kb < kb_total; ++kb, ++it) {
+                const int kb0 = split * g.kb_per_split, kb1 = min(kb_total, kb0 + g.kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait_bounded(empty_bar + s, ph ^ 1)) { report(status, WAIT_EMPTY, s); *abort_flag = 1; break; }
@@ -383,7 +391,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     uint8_t* sb = sa + L::A_BYTES;
                     if (first) mbar_expect_tx(full_bar + s, 2 * L::STAGE_BYTES);
                     const uint32_t bar = map_to_cta(smem_u32(full_bar + s), 0);
-                    const int k0 = kb * BK;
+                    const int k0 = kb * BKE;
                     if (A_MN) {
 #pragma unroll
                         for (int c = 0; c < BM / 64; ++c) tma_load_2d_pair(sa + c * (BK * 128), &tmA, m0 + c * 64, k0, bar);
@@ -405,11 +413,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint32_t idesc = make_idesc_f16(g.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, 2 * BM, BN);
             uint32_t it = 0, tl = 0;
             for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs, ++tl) {
+                const int split = tile / tiles_mn;
+                const int kb0 = split * g.kb_per_split, kb1 = min(kb_total, kb0 + g.kb_per_split);
                 const uint32_t acc = tl & 1, acc_ph = (tl >> 1) & 1;
                 if (!mbar_wait_bounded(tempty_bar + acc, acc_ph ^ 1)) { report(status, WAIT_TMEM_EMPTY, tile); *abort_flag = 1; break; }
                 fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < kb_total; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait_bounded(full_bar + s, ph)) { report(status, WAIT_FULL, s); *abort_flag = 1; break; }
@@ -422,7 +432,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                                  : make_smem_desc(sa + j * (UMMA_K * 2), 16, 1024);
                         const uint64_t db = B_MN ? make_smem_desc(sb + j * (UMMA_K * 128), BK * 128, 1024)
                                                  : make_smem_desc(sb + j * (UMMA_K * 2), 16, 1024);
-                        mma_f16_ss_pair(d_tmem, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                        if constexpr (ES == 2) mma_f16_ss_pair(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+                        else mma_f8_ss_pair(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
                     }
                     const uint32_t eb = smem_u32(empty_bar + s);
                     mma_commit_pair(eb);                       // this CTA's stage is reusable ...
@@ -441,9 +452,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t tempty_first = map_to_cta(smem_u32(tempty_bar), 0);
         uint32_t tl = 0, oc = 0;
         for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs, ++tl) {
+            const int split = tile / tiles_mn;
             int tm, tn;
-            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            tile_coords(tile - split * tiles_mn, tiles_m, tiles_n, tm, tn);
             const int m0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * BN;
+            const int row = m0 + quarter * 32 + lane;
             const uint32_t acc = tl & 1, acc_ph = (tl >> 1) & 1;
             bool ok = true;
             if (lane == 0) ok = mbar_wait_bounded(tfull_bar + acc, acc_ph);
@@ -456,6 +469,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + c * 32, r);
                 tmem_ld_wait();
+                if (g.alpha != nullptr) {
+#pragma unroll
+                    for (int q = 0; q < 32; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) * alpha);
+                }
+                if (g.out_f32) {
+                    // split-K partial sums / fp32 results: straight from registers, one 128-byte run per row
+                    const int col0 = n0 + c * 32;
+                    if (row < g.M && col0 < g.N) {
+                        float* dst = reinterpret_cast<float*>(Dptr) + ((size_t)split * g.M + row) * g.ldd + col0;
+                        if (col0 + 32 <= g.N) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                reinterpret_cast<uint4*>(dst)[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < 32; ++q)
+                                if (col0 + q < g.N) dst[q] = __uint_as_float(r[q]);
+                        }
+                    }
+                    continue;
+                }
                 uint8_t* stage_buf = smem + L::OUT_OFFSET + (half * 2 + (oc & 1)) * L::OUT_BYTES;
                 if (oc >= 2 && (int)threadIdx.x == issuer) tma_store_wait_read<1>();
                 ++oc;
@@ -556,19 +590,19 @@ void launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
     kern<<<grid, kThreads, L::TOTAL, stream>>>(ta, tb, td, d, g, st);
 }
 
-template <bool A_MN, bool B_MN>
-void launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmArgs& g, KernelStatus* st,
+template <bool A_MN, bool B_MN, int ES = 2>
+void launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, void* d, const GemmArgs& g, KernelStatus* st,
                  int grid, cudaStream_t stream) {
-    auto kern = gemm_pair_kernel<A_MN, B_MN>;
+    auto kern = gemm_pair_kernel<A_MN, B_MN, ES>;
     static bool configured = false;
     if (!configured) {
         C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL));
         configured = true;
     }
-    kern<<<grid, kThreads, PairSmem::TOTAL, stream>>>(ta, tb, td, g, st);
+    kern<<<grid, kThreads, PairSmem::TOTAL, stream>>>(ta, tb, td, d, g, st);
 }
 
-// 0: never use CTA pairs; 1: use them where the shape allows (16-bit result, no split-K, M and N >= 256)
+// 0: never use CTA pairs; 1: use them where they measured faster (M, N >= 256 and >= 16 k-blocks); 2: wherever possible
 int& pair_mode() {
     static int mode = []() {
         const char* e = std::getenv("SJB200_GEMM_PAIR");
@@ -601,14 +635,21 @@ static at::Tensor gemm_16bit_impl(const at::Tensor& a, const at::Tensor& b, bool
     TORCH_CHECK(N % 8 == 0, "gemm_16bit: N must be a multiple of 8");
     const bool bf16 = a.scalar_type() == at::kBFloat16;
 
-    const int BN = N > 128 ? 256 : 128;
-    const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
-    const int kb_total = (int)((K + BK - 1) / BK);
     const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    // Two SMs per 256 x 256 tile where the output is large enough and the contraction long enough (>= 16 k-blocks:
+    // measured, shorter main loops are bound by the epilogue, where the pair's cross-CTA hand-shakes only cost);
+    // else one SM per 128 x BN tile.  Mode 2 forces the pair kernel wherever the shape allows it.
+    const bool use_pair = pair_mode() != 0 && M >= 2 * BM && N >= kPairBN && sms >= 2 &&
+                          (pair_mode() == 2 || (K + BK - 1) / BK >= 16);
+    const int BN = use_pair ? kPairBN : (N > 128 ? 256 : 128);
+    const int TM = use_pair ? 2 * BM : BM;
+    const int units = use_pair ? sms / 2 : sms;            // tiles that run at the same time
+    const int tiles = (int)(((M + TM - 1) / TM) * ((N + BN - 1) / BN));
+    const int kb_total = (int)((K + BK - 1) / BK);
     int splits = (int)split_k;
     if (splits <= 0) {
         splits = 1;
-        if (tiles * 2 <= sms && kb_total >= 16) splits = std::min(std::max(1, sms / tiles), kb_total / 4);
+        if (tiles * 2 <= units && kb_total >= 16) splits = std::min(std::max(1, units / tiles), kb_total / 4);
     }
     if (stats != nullptr) splits = 1;                      // the statistics come from complete 16-bit tiles
     splits = std::max(1, std::min(splits, kb_total));
@@ -623,38 +664,17 @@ static at::Tensor gemm_16bit_impl(const at::Tensor& a, const at::Tensor& b, bool
     g.out_bf16 = bf16 ? 1 : 0;
     g.alpha = nullptr;
     g.stats = nullptr;
-    const bool use_pair = pair_mode() != 0 && !g.out_f32 && splits == 1 && M >= 2 * BM && N >= kPairBN && sms >= 2;
     if (stats != nullptr) {
         TORCH_CHECK(!out_f32, "gemm_16bit: column statistics need a 16-bit result");
         // the pair kernel works on 256-row tiles: its last tile may cover one more (all-zero) 128-row slice
-        const int64_t slices = use_pair ? (M + 2 * BM - 1) / (2 * BM) * 2 : (M + BM - 1) / BM;
-        *stats = at::empty({slices * 4, 2, N}, a.options().dtype(at::kFloat));
+        *stats = at::empty({(M + TM - 1) / TM * (TM / BM) * 4, 2, N}, a.options().dtype(at::kFloat));
         g.stats = stats->data_ptr<float>();
-    }
-    if (use_pair) {
-        const CUtensorMap pa = a_mn ? make_map(A.data_ptr(), K, M, A.stride(0), BK, bf16)
-                                    : make_map(A.data_ptr(), M, K, A.stride(0), BM, bf16);
-        const CUtensorMap pb = b_mn ? make_map(B.data_ptr(), K, N, B.stride(0), BK, bf16)
-                                    : make_map(B.data_ptr(), N, K, B.stride(0), kPairBN / 2, bf16);
-        at::Tensor out = at::empty({M, N}, a.options());
-        const CUtensorMap pd = make_map(out.data_ptr(), M, N, N, BM, bf16, 32);
-        at::Tensor& stw = status_word(a.device());
-        KernelStatus* stp = reinterpret_cast<KernelStatus*>(stw.data_ptr<int>());
-        const int ptiles = (int)(((M + 2 * BM - 1) / (2 * BM)) * ((N + kPairBN - 1) / kPairBN));
-        const int grid = 2 * std::min(ptiles, sms / 2);
-        cudaStream_t stream = at::cuda::getCurrentCUDAStream();
-        if (a_mn && b_mn) launch_pair<true, true>(pa, pb, pd, g, stp, grid, stream);
-        else if (a_mn) launch_pair<true, false>(pa, pb, pd, g, stp, grid, stream);
-        else if (b_mn) launch_pair<false, true>(pa, pb, pd, g, stp, grid, stream);
-        else launch_pair<false, false>(pa, pb, pd, g, stp, grid, stream);
-        C10_CUDA_KERNEL_LAUNCH_CHECK();
-        return out;
     }
 
     const CUtensorMap ta = a_mn ? make_map(A.data_ptr(), K, M, A.stride(0), BK, bf16)
                                 : make_map(A.data_ptr(), M, K, A.stride(0), BM, bf16);
     const CUtensorMap tb = b_mn ? make_map(B.data_ptr(), K, N, B.stride(0), BK, bf16)
-                                : make_map(B.data_ptr(), N, K, B.stride(0), BN, bf16);
+                                : make_map(B.data_ptr(), N, K, B.stride(0), use_pair ? kPairBN / 2 : BN, bf16);
 
     auto opts = a.options();
     at::Tensor out = at::empty({M, N}, out_f32 ? opts.dtype(at::kFloat) : opts);
@@ -668,9 +688,16 @@ static at::Tensor gemm_16bit_impl(const at::Tensor& a, const at::Tensor& b, bool
     const CUtensorMap td = g.out_f32 ? ta : make_map(out.data_ptr(), M, N, N, BM, bf16, 32);
     at::Tensor& st = status_word(a.device());
     KernelStatus* stp = reinterpret_cast<KernelStatus*>(st.data_ptr<int>());
-    const int grid = std::min(tiles * splits, sms);
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
 
+    if (use_pair) {
+        const int grid = 2 * std::min(tiles * splits, units);
+        if (a_mn && b_mn) launch_pair<true, true>(ta, tb, td, dptr, g, stp, grid, stream);
+        else if (a_mn) launch_pair<true, false>(ta, tb, td, dptr, g, stp, grid, stream);
+        else if (b_mn) launch_pair<false, true>(ta, tb, td, dptr, g, stp, grid, stream);
+        else launch_pair<false, false>(ta, tb, td, dptr, g, stp, grid, stream);
+    } else {
+        const int grid = std::min(tiles * splits, sms);
 #define SJ_LAUNCH(BN_, ST_)                                                                          \
     do {                                                                                             \
         if (a_mn && b_mn) launch<BN_, ST_, true, true>(ta, tb, td, dptr, g, stp, grid, stream);          \
@@ -678,8 +705,9 @@ static at::Tensor gemm_16bit_impl(const at::Tensor& a, const at::Tensor& b, bool
         else if (b_mn) launch<BN_, ST_, false, true>(ta, tb, td, dptr, g, stp, grid, stream);            \
         else launch<BN_, ST_, false, false>(ta, tb, td, dptr, g, stp, grid, stream);                     \
     } while (0)
-    if (BN == 256) SJ_LAUNCH(256, 4); else SJ_LAUNCH(128, 6);
+        if (BN == 256) SJ_LAUNCH(256, 4); else SJ_LAUNCH(128, 6);
 #undef SJ_LAUNCH
+    }
     C10_CUDA_KERNEL_LAUNCH_CHECK();
 
     if (splits > 1) {
@@ -722,14 +750,18 @@ at::Tensor gemm_fp8(const at::Tensor& a, const at::Tensor& b, const c10::optiona
     TORCH_CHECK(B.size(1) == K, "gemm_fp8: contraction sizes differ (", K, " vs ", B.size(1), ")");
     TORCH_CHECK(N % 8 == 0 && K % 16 == 0, "gemm_fp8: N must be a multiple of 8 and K a multiple of 16");
     constexpr int BKE = 128;
-    const int BN = N > 128 ? 256 : 128;
-    const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
-    const int kb_total = (int)((K + BKE - 1) / BKE);
     const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    const bool use_pair = pair_mode() != 0 && M >= 2 * BM && N >= kPairBN && sms >= 2 &&
+                          (pair_mode() == 2 || (K + BKE - 1) / BKE >= 16);
+    const int BN = use_pair ? kPairBN : (N > 128 ? 256 : 128);
+    const int TM = use_pair ? 2 * BM : BM;
+    const int units = use_pair ? sms / 2 : sms;
+    const int tiles = (int)(((M + TM - 1) / TM) * ((N + BN - 1) / BN));
+    const int kb_total = (int)((K + BKE - 1) / BKE);
     int splits = (int)split_k;
     if (splits <= 0) {
         splits = 1;
-        if (tiles * 2 <= sms && kb_total >= 16) splits = std::min(std::max(1, sms / tiles), kb_total / 4);
+        if (tiles * 2 <= units && kb_total >= 16) splits = std::min(std::max(1, units / tiles), kb_total / 4);
     }
     splits = std::max(1, std::min(splits, kb_total));
     const int kb_per = (kb_total + splits - 1) / splits;
@@ -747,7 +779,7 @@ at::Tensor gemm_fp8(const at::Tensor& a, const at::Tensor& b, const c10::optiona
         g.alpha = alpha->data_ptr<float>();
     }
     const CUtensorMap ta = make_map_u8(A.data_ptr(), M, K, A.stride(0), BM);
-    const CUtensorMap tb = make_map_u8(B.data_ptr(), N, K, B.stride(0), BN);
+    const CUtensorMap tb = make_map_u8(B.data_ptr(), N, K, B.stride(0), use_pair ? kPairBN / 2 : BN);
     auto opts = a.options();
     at::Tensor out = at::empty({M, N}, opts.dtype(out_f32 ? at::kFloat : at::kBFloat16));
     at::Tensor scratch;
@@ -759,10 +791,10 @@ at::Tensor gemm_fp8(const at::Tensor& a, const at::Tensor& b, const c10::optiona
     const CUtensorMap td = g.out_f32 ? ta : make_map(out.data_ptr(), M, N, N, BM, true, 32);
     at::Tensor& st = status_word(a.device());
     KernelStatus* stp = reinterpret_cast<KernelStatus*>(st.data_ptr<int>());
-    const int grid = std::min(tiles * splits, sms);
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
-    if (BN == 256) launch<256, 4, false, false, 1>(ta, tb, td, dptr, g, stp, grid, stream);
-    else launch<128, 6, false, false, 1>(ta, tb, td, dptr, g, stp, grid, stream);
+    if (use_pair) launch_pair<false, false, 1>(ta, tb, td, dptr, g, stp, 2 * std::min(tiles * splits, units), stream);
+    else if (BN == 256) launch<256, 4, false, false, 1>(ta, tb, td, dptr, g, stp, std::min(tiles * splits, sms), stream);
+    else launch<128, 6, false, false, 1>(ta, tb, td, dptr, g, stp, std::min(tiles * splits, sms), stream);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
     if (splits > 1) {
         const long long mn = (long long)M * N;

@@ -99,7 +99,7 @@ def test_epilogue_column_statistics(M, N, K, dtype):
 @pytest.fixture
 def pair_mode():
     G.require()
-    prev = torch.ops.sjb200.gemm_set_pair_mode(1)
+    prev = torch.ops.sjb200.gemm_set_pair_mode(2)          # force the two-CTA kernel on every shape it supports
     yield
     torch.ops.sjb200.gemm_set_pair_mode(prev)
 
@@ -128,3 +128,15 @@ def test_cta_pair_kernel_statistics_and_determinism(pair_mode):
     torch.ops.sjb200.gemm_set_pair_mode(0)
     y1 = G.gemm(x, w)
     assert torch.equal(y, y1)            # same k order and rounding as the single-CTA kernel
+
+
+@pytest.mark.parametrize("split", [0, 3])
+def test_cta_pair_kernel_split_k_and_fp32_output(pair_mode, split):
+    a = torch.randn(4096, 512, device=DEV).to(torch.bfloat16)      # [K, M]
+    b = torch.randn(4096, 264, device=DEV).to(torch.bfloat16)      # [K, N]
+    out = G.gemm(a, b, True, True, out_f32=True, split_k=split)
+    G.check_status(out)
+    torch.testing.assert_close(out, a.float().t() @ b.float(), rtol=1e-3, atol=5e-2)
+    assert torch.equal(out, G.gemm(a, b, True, True, out_f32=True, split_k=split))
+    out16 = G.gemm(a, b, True, True, split_k=split)
+    torch.testing.assert_close(out16.float(), a.float().t() @ b.float(), rtol=2e-2, atol=1.5)
