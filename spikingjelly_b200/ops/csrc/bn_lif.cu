@@ -204,7 +204,7 @@ bn_lif_forward_kernel(ScanParams p_in, int C, const T* __restrict__ y, const flo
 // g_out: dL/d(out) [T, N];  writes gx = dL/d(BN output) [T, N];
 // partial[blk][0][c] = sum gx, partial[blk][1][c] = sum gx * y   (the finalize kernel turns the latter
 // into sum gx * xhat = invstd * (sum gx y - mean * sum gx))
-template <typename T, int V, int KIND, int TFIX = 0, int OCC = (V <= 4 ? 3 : 2)>
+template <typename T, int V, int KIND, int TFIX = 0, int OCC = 2>
 __global__ void __launch_bounds__(kThreads, OCC)
 bn_lif_backward1_kernel(ScanParams p_in, int C, const T* __restrict__ y, const T* __restrict__ g_out,
                         const float* __restrict__ scale, const float* __restrict__ shift,
