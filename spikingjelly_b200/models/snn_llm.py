@@ -26,6 +26,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..activation_based import functional, layer, neuron, surrogate
+from ..ops import rope as rope_ops
 
 __all__ = ["SNNLLMConfig", "RMSNorm", "RotaryEmbedding", "SpikingCausalSelfAttention", "SpikingFFN", "SNNLLMBlock",
            "SNNLLM", "snn_llm_1b", "snn_llm_tiny", "parallelize_snn_llm"]
@@ -109,8 +110,14 @@ class SpikingCausalSelfAttention(nn.Module):
         T, B, S, _ = s.shape
         H, D = self.n_local_heads, self.cfg.head_dim
         qkv = self.qkv(s).reshape(T * B, S, H, 3, D)                     # head-major so that TP shards whole heads
-        q, k, v = (qkv[:, :, :, i].transpose(1, 2) for i in range(3))    # [T*B, H, S, D]
-        a = F.scaled_dot_product_attention(self.rope(q), self.rope(k), v, is_causal=True)
+        if rope_ops.supports(qkv, D):
+            # one kernel: rotate q and k, split; the results are [T*B, S, H, D] in memory, which is also the order the
+            # attention output comes back in, so neither side needs a layout copy
+            q, k, v = (t.transpose(1, 2) for t in rope_ops.rope_qkv(qkv, self.rope.cos, self.rope.sin))
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        else:
+            q, k, v = (qkv[:, :, :, i].transpose(1, 2) for i in range(3))    # [T*B, H, S, D]
+            a = F.scaled_dot_product_attention(self.rope(q), self.rope(k), v, is_causal=True)
         a = a.transpose(1, 2).reshape(T, B, S, H * D)
         return self.proj(self.attn_lif(a))
 

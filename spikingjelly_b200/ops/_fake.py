@@ -47,6 +47,16 @@ def register() -> None:
         oh, ow = (h + 2 * ph - KH) // sh + 1, (w + 2 * pw - KW) // sw + 1
         return x.new_empty((n * oh * ow, (KH * KW * c + 7) // 8 * 8))
 
+    @reg("sjb200::rope_qkv_forward")
+    def _(qkv, cos, sin, offset):
+        n, s_, h, _, d = qkv.shape
+        return tuple(qkv.new_empty((n, s_, h, d)) for _ in range(3))
+
+    @reg("sjb200::rope_qkv_backward")
+    def _(gq, gk, gv, cos, sin, offset):
+        n, s_, h, d = gq.shape
+        return gq.new_empty((n, s_, h, 3, d))
+
     @reg("sjb200::gemm_fp8")
     def _(a, b, alpha, out_f32, split_k):
         return a.new_empty((a.shape[0], b.shape[0]), dtype=torch.float32 if out_f32 else torch.bfloat16)

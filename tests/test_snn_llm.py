@@ -95,3 +95,28 @@ def test_native_backend_bf16_step_on_gpu():
         _, loss = net(tok, labels=tok)
     loss.backward()
     assert torch.isfinite(loss) and all(torch.isfinite(p.grad).all() for p in net.parameters())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fused_rope_qkv_matches_eager(dtype):
+    from spikingjelly_b200 import ops
+    from spikingjelly_b200.models.snn_llm import RotaryEmbedding
+    from spikingjelly_b200.ops import rope as rope_ops
+    ops.require()
+    torch.manual_seed(0)
+    N, S, H, D = 3, 37, 4, 64
+    rope = RotaryEmbedding(D, 64).cuda()
+    qkv = torch.randn(N, S, H, 3, D, device="cuda").to(dtype).requires_grad_(True)
+    q, k, v = rope_ops.rope_qkv(qkv, rope.cos, rope.sin)
+    ref = qkv.detach().float().requires_grad_(True)
+    qr, kr, vr = (ref[:, :, :, i].transpose(1, 2) for i in range(3))            # [N, H, S, D]
+    qr, kr = rope(qr), rope(kr)
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype is torch.bfloat16 else dict(rtol=3e-3, atol=3e-3)
+    for a, b in ((q, qr), (k, kr), (v, vr)):
+        assert a.shape == (N, S, H, D) and a.is_contiguous()
+        torch.testing.assert_close(a.transpose(1, 2).float(), b, **tol)
+    gq, gk, gv = (torch.randn(N, S, H, D, device="cuda").to(dtype) for _ in range(3))
+    torch.autograd.backward([q, k, v], [gq, gk, gv])
+    torch.autograd.backward([qr, kr, vr], [g.float().transpose(1, 2) for g in (gq, gk, gv)])
+    torch.testing.assert_close(qkv.grad.float(), ref.grad, **tol)
