@@ -1,7 +1,8 @@
 from .base import ConversionRecipe, FXConversionRecipe, ModuleConversionRecipe
 from .local_threshold_balancing import LocalThresholdBalancingRecipe
 from .rate_coding import RateCodingRecipe
+from .spikezip_qann import SpikeZIPTFQANNRecipe
 from .transformer_td_equivalent import TransformerTDEquivalentRecipe
 
-__all__ = ["ConversionRecipe", "FXConversionRecipe", "ModuleConversionRecipe", "LocalThresholdBalancingRecipe", "RateCodingRecipe",
+__all__ = ["ConversionRecipe", "FXConversionRecipe", "ModuleConversionRecipe", "LocalThresholdBalancingRecipe", "RateCodingRecipe", "SpikeZIPTFQANNRecipe",
            "TransformerTDEquivalentRecipe"]
