@@ -59,3 +59,12 @@ def test_dqn_examples_run_on_builtin_cartpole():
     assert out["best"] >= 1
     out = DQN_state.main(["--episodes", "3", "--hidden", "16", "--batch-size", "8", "--builtin-env"])
     assert out["best"] >= 1
+
+
+def test_actor_critic_examples_run_on_builtin_cartpole():
+    from spikingjelly_b200.activation_based.examples import A2C, PPO, Spiking_A2C, Spiking_PPO
+    common = ["--episodes", "3", "--hidden", "16", "--builtin-env"]
+    assert Spiking_A2C.main(common + ["-T", "4"])["best"] >= 1
+    assert A2C.main(common)["best"] >= 1
+    assert Spiking_PPO.main(common + ["-T", "4", "--horizon", "16", "--minibatch", "8", "--ppo-epochs", "1"])["best"] >= 1
+    assert PPO.main(common + ["--horizon", "16", "--minibatch", "8", "--ppo-epochs", "1"])["best"] >= 1
