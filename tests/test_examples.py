@@ -68,3 +68,11 @@ def test_actor_critic_examples_run_on_builtin_cartpole():
     assert A2C.main(common)["best"] >= 1
     assert Spiking_PPO.main(common + ["-T", "4", "--horizon", "16", "--minibatch", "8", "--ppo-epochs", "1"])["best"] >= 1
     assert PPO.main(common + ["--horizon", "16", "--minibatch", "8", "--ppo-epochs", "1"])["best"] >= 1
+
+
+def test_speechcommands_example_runs_on_synthetic_tones():
+    from spikingjelly_b200.activation_based.examples import speechcommands as sc
+    fb = sc.mel_filter_bank(257, 40, 20.0, 4000.0, 16000)
+    assert fb.shape == (257, 40) and float(fb.min()) >= 0 and float(fb.sum(0).min()) > 0
+    s = sc.main(["--synthetic", "--device", "cpu", "--max-steps", "4", "--channels", "8", "--n-mels", "16", "-b", "16", "--lr", "0.01"])
+    assert s["train_loss"] > 0 and 0 <= s["test_acc"] <= 1
