@@ -16,6 +16,13 @@ class VGGBlock(nn.Module):
         self.neuron = neuron.LIFNode(**kwargs)
 
     def forward(self, x_seq):
+        from spikingjelly_b200.models import _conv_fused as fused
+        conv, bn = self.proj_bn[-2], self.proj_bn[-1]
+        if fused.eligible(conv, bn, self.neuron, x_seq):
+            # channels-last convolution -> fused BatchNorm + LIF kernels (16-bit compute on a CUDA device)
+            for m in self.proj_bn[:-2]:
+                x_seq = m(x_seq)
+            return fused.conv_bn_lif(conv, bn, self.neuron, x_seq)
         return self.neuron(self.proj_bn(x_seq))
 
     def __spatial_split__(self):

@@ -58,7 +58,12 @@ class SpikingVGG(nn.Module):
             self._initialize_weights()
 
     def forward(self, x):
-        x = self.avgpool(self.features(x))
+        if self.avgpool.step_mode == "m" and torch.is_tensor(x) and x.is_cuda and x.ndim == 5:
+            from . import _conv_fused
+            feats = _conv_fused.run_sequential(self.features, x)      # fuses conv -> BN -> neuron triples where eligible
+        else:
+            feats = self.features(x)
+        x = self.avgpool(feats)
         x = torch.flatten(x, 1 if self.avgpool.step_mode == "s" else 2)
         return self.classifier(x)
 

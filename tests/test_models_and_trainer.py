@@ -191,3 +191,42 @@ def test_sew_resnet_fused_channels_last_schedule_matches_module_path(cnf):
     functional.reset_net(net)
     assert stats["fused"].shape == (T, B, 11) and torch.isfinite(stats["fused"]).all()
     assert abs(stats["fused"].std().item() - stats["module"].std().item()) < 0.5 * stats["module"].std().item() + 1e-3
+
+
+@pytest.mark.gpu
+def test_vgg_fused_conv_bn_lif_matches_module_path():
+    """CIFAR10-DVS VGG blocks under bf16 autocast: fused channels-last schedule against the modules' own forward, block by
+    block (spike mismatch from 16-bit rounding stays small; gradients agree within the tolerance of bf16 accumulation)."""
+    from spikingjelly_b200 import ops
+    from spikingjelly_b200.activation_based import functional
+    from spikingjelly_b200.activation_based.examples.memopt.models import CIFAR10DVSVGG
+    from spikingjelly_b200.models import _conv_fused
+    ops.require()
+    torch.manual_seed(0)
+    net = CIFAR10DVSVGG(dropout=0.0, backend="cuda").cuda().train()
+    x = (torch.rand(4, 2, 6, 2, 48, 48, device="cuda") < 0.3).float()[0].transpose(0, 1).contiguous()   # [T=6, N=2, ...] built from [N, T]
+    x = x.reshape(6, 2, 2, 48, 48)
+    blk = net.features[1]                       # 64 -> 128 channels, spikes in
+    s_in = (torch.rand(6, 2, 64, 48, 48, device="cuda") < 0.2).float().requires_grad_(True)
+    conv, bn = blk.proj_bn[-2], blk.proj_bn[-1]
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        assert _conv_fused.eligible(conv, bn, blk.neuron, s_in)
+        out_f = blk(s_in)
+        g = torch.randn_like(out_f)
+        out_f.backward(g)
+    gf, gw_f = s_in.grad.clone(), conv.weight.grad.clone()
+    s_in.grad = None
+    net.zero_grad()
+    functional.reset_net(net)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out_m = blk.neuron(blk.proj_bn(s_in))     # the modules' own path
+        out_m.backward(g.to(out_m.dtype))
+    assert out_f.shape == out_m.shape
+    mismatch = (out_f.float() != out_m.float()).float().mean().item()
+    assert mismatch < 0.02
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()    # noqa: E731
+    assert rel(gw_f, conv.weight.grad) < 0.25 and rel(gf, s_in.grad) < 0.25
+    functional.reset_net(net)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = net(torch.rand(2, 6, 2, 48, 48, device="cuda"))
+    assert y.shape == (6, 2, 10) and torch.isfinite(y.float()).all()
