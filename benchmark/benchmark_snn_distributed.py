@@ -138,8 +138,15 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
         ms, mb = t.tolist()
+        # ranks of one tensor-parallel group work on the SAME samples: only the data-parallel replicas multiply the batch
+        if a.mode == "tp":
+            replicas = 1
+        elif a.mode == "fsdp2_tp":
+            replicas = (a.mesh_shape[0] if a.mesh_shape else max(1, world // 2))
+        else:
+            replicas = world
         rec = {"impl": a.impl, "model": a.model, "mode": a.mode, "n_gpus": world, "per_rank_batch": B, "T": a.T,
-               "dtype": "bf16 autocast" if a.amp else "fp32", "step_ms": round(ms, 2), "samples_per_s": round(world * B / ms * 1e3, 1),
+               "dtype": "bf16 autocast" if a.amp else "fp32", "step_ms": round(ms, 2), "samples_per_s": round(replicas * B / ms * 1e3, 1),
                "peak_allocated_mb": round(mb, 1), "last_loss": round(float(loss), 4)}
         pub = PUBLISHED.get((a.model, a.mode, world))
         if pub and B == 16:
