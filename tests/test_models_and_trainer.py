@@ -230,3 +230,26 @@ def test_vgg_fused_conv_bn_lif_matches_module_path():
     with torch.autocast("cuda", dtype=torch.bfloat16):
         y = net(torch.rand(2, 6, 2, 48, 48, device="cuda"))
     assert y.shape == (6, 2, 10) and torch.isfinite(y.float()).all()
+
+
+@pytest.mark.gpu
+def test_spiking_vgg_fused_triples_under_autocast():
+    from spikingjelly_b200 import ops
+    from spikingjelly_b200.activation_based import functional, neuron, surrogate
+    from spikingjelly_b200.models import spiking_vgg
+    from spikingjelly_b200.ops import counters
+    ops.require()
+    torch.manual_seed(0)
+    net = spiking_vgg.spiking_vgg11_bn(spiking_neuron=neuron.LIFNode, surrogate_function=surrogate.ATan(), detach_reset=True,
+                                       num_classes=10).cuda().train()
+    functional.set_step_mode(net, "m")
+    functional.set_backend(net, "cuda", instance=neuron.LIFNode)
+    x = torch.rand(2, 2, 3, 64, 64, device="cuda")
+    counters.reset()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = net(x)
+        y.float().mean().backward()
+    assert y.shape == (2, 2, 10) and torch.isfinite(y.float()).all()
+    assert counters.by_name().get("bn_lif_forward", 0) == 8          # the eight convolution stages of VGG-11 ran fused
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in net.features.parameters())
+    functional.reset_net(net)
