@@ -1,0 +1,69 @@
+"""``activation_based.cuda_kernel`` / ``triton_kernel`` import paths: spike storage, memory-saving spike layers, helpers."""
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from spikingjelly_b200 import configure
+from spikingjelly_b200.activation_based.cuda_kernel import cuda_utils, spike_op, tensor_cache
+from spikingjelly_b200.activation_based.triton_kernel import bit_spike_compress, bit_spike_decompress, fp8_capability
+
+
+def test_spike_bit_round_trip_and_cache():
+    torch.manual_seed(0)
+    s = (torch.rand(3, 5, 7) < 0.4).float()
+    packed, dt, shape, pad = tensor_cache.float_spike_to_bool(s)
+    assert packed.dtype == torch.uint8 and packed.numel() == (s.numel() + 7) // 8 and pad == (8 - s.numel() % 8) % 8
+    assert torch.equal(tensor_cache.bool_spike_to_float(packed, dt, shape, pad), s)
+    assert torch.equal(bit_spike_decompress(bit_spike_compress(s), s.shape, torch.float32), s)
+    for level in (0, 1):
+        old = configure.save_bool_spike_level
+        configure.save_bool_spike_level = level
+        try:
+            cache = tensor_cache.BoolTensorCache()
+            k1, k2 = cache.store_bool(s), cache.store_bool(s)
+            assert k1 == k2 and len(cache.cache) == 1
+            assert torch.equal(cache.get_float(k1, s.shape), s) and len(cache.cache) == 1
+            assert torch.equal(cache.get_float(k2, s.shape), s) and len(cache.cache) == 0
+        finally:
+            configure.save_bool_spike_level = old
+
+
+def test_helpers():
+    assert cuda_utils.cal_blocks(1000, 256) == 4 and cuda_utils.cal_blocks(1024) == 1024 // configure.cuda_threads
+    assert cuda_utils.cpu_timer(lambda: sum(range(100))) >= 0
+    assert cuda_utils.cal_fun_t(3, "cpu", lambda: None) >= 0
+    a, = cuda_utils.get_contiguous(torch.arange(6).view(2, 3).t())
+    assert a.is_contiguous()
+    cap = fp8_capability.fp8_capability()
+    assert "available" in cap and fp8_capability.is_fp8_dtype(torch.float8_e4m3fn) and not fp8_capability.is_fp8_dtype(torch.float16)
+    lin = spike_op.SpikeLinear(4, 3)
+    x = (torch.rand(2, 4) < 0.5).float()
+    torch.testing.assert_close(lin(x), F.linear(x, lin.weight, lin.bias))        # CPU: the plain operator
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("level", [0, 1])
+def test_spike_layers_match_plain_layers_on_gpu(level):
+    old = configure.save_bool_spike_level
+    configure.save_bool_spike_level = level
+    try:
+        torch.manual_seed(0)
+        for spike_mod, plain, shape in ((spike_op.SpikeLinear(16, 8), nn.Linear(16, 8), (4, 16)),
+                                        (spike_op.SpikeConv1d(4, 6, 3, padding=1), nn.Conv1d(4, 6, 3, padding=1), (2, 4, 10)),
+                                        (spike_op.SpikeConv2d(4, 6, 3, stride=2, padding=1), nn.Conv2d(4, 6, 3, stride=2, padding=1), (2, 4, 9, 9)),
+                                        (spike_op.SpikeConv3d(2, 3, 3, padding=1), nn.Conv3d(2, 3, 3, padding=1), (2, 2, 5, 5, 5))):
+            spike_mod, plain = spike_mod.cuda(), plain.cuda()
+            plain.load_state_dict(spike_mod.state_dict())
+            x = (torch.rand(*shape, device="cuda") < 0.3).float().requires_grad_(True)
+            xr = x.detach().clone().requires_grad_(True)
+            y, yr = spike_mod(x), plain(xr)
+            torch.testing.assert_close(y, yr)
+            g = torch.randn_like(y)
+            y.backward(g); yr.backward(g)
+            torch.testing.assert_close(x.grad, xr.grad)
+            torch.testing.assert_close(spike_mod.weight.grad, plain.weight.grad)
+            torch.testing.assert_close(spike_mod.bias.grad, plain.bias.grad)
+        assert len(tensor_cache.BOOL_TENSOR_CACHE.cache) == 0
+    finally:
+        configure.save_bool_spike_level = old
