@@ -31,6 +31,7 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=4)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--fp8", action="store_true", help="run the four linear layers of every block through the fp8 linear (TP = 1)")
     ap.add_argument("--out", default="")
     a = ap.parse_args()
     world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
@@ -44,6 +45,14 @@ def main():
     if world > 1:
         model = snn_llm.parallelize_snn_llm(model)
     model.to(device)
+    if a.fp8:
+        # per-tensor scaled e4m3 operands on the tcgen05 kind::f8f6f4 GEMM (spikes are exact in e4m3); the LM head stays bf16
+        from spikingjelly_b200.ops import fp8
+        if world > 1:
+            raise SystemExit("--fp8 is wired for TP = 1 in this script")
+        for blk in model.blocks:
+            for lin in (blk.attn.qkv, blk.attn.proj, blk.ffn.up, blk.ffn.down):
+                lin.forward = (lambda x, m=lin: fp8.linear(x, m.weight, m.bias))
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
     tok = torch.randint(0, model.cfg.vocab_size, (a.micro_batch, a.seq), device=device, generator=torch.Generator(device).manual_seed(1))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
@@ -81,7 +90,7 @@ def main():
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
         peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
         tflops = 3.0 * fwd_flops / (ms / 1e3) / 1e12 / world
-        rec = {"config": f"SNN-LLM {a.layers}L d2048 ffn5504 T4 seq{a.seq} mb{a.micro_batch} bf16 tp{world}", "n_gpus": world,
+        rec = {"config": f"SNN-LLM {a.layers}L d2048 ffn5504 T4 seq{a.seq} mb{a.micro_batch} {"fp8" if a.fp8 else "bf16"} tp{world}", "n_gpus": world,
                "ms_per_step": round(ms, 2), "tokens_per_s": round(tokens / ms * 1e3, 1), "model_tflops_per_gpu": round(tflops, 1),
                "of_measured_sustained_bf16_peak": round(tflops / peak, 3), "peak_source": "measured" if peaks else "fallback",
                "last_loss": round(float(loss), 4), "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
