@@ -76,3 +76,10 @@ def test_speechcommands_example_runs_on_synthetic_tones():
     assert fb.shape == (257, 40) and float(fb.min()) >= 0 and float(fb.sum(0).min()) > 0
     s = sc.main(["--synthetic", "--device", "cpu", "--max-steps", "4", "--channels", "8", "--n-mels", "16", "-b", "16", "--lr", "0.01"])
     assert s["train_loss"] > 0 and 0 <= s["test_acc"] <= 1
+
+
+def test_spiking_lstm_text_example_learns_synthetic_languages():
+    from spikingjelly_b200.activation_based.examples import spiking_lstm_text as ex
+    assert ex.to_ascii("Ślusàrski") == "Slusarski" and ex.word_to_tensor("ab").shape == (2, 1, len(ex.LETTERS))
+    s = ex.main(["--synthetic", "--steps", "150", "--hidden", "32"])
+    assert s["last_loss"] < s["first_loss"] and s["test_acc"] > 0.4
