@@ -3,7 +3,7 @@
 (forward, dgrad, wgrad) and on a large square problem.  CUDA-event timing, L2 flushed between
 iterations, median of `--iters`.
 
-    python benchmark/benchmark_gemm.py [--out gpurun_out/gemm.json] [--only NAME]
+    python benchmark/benchmark_gemm.py [--out out/gemm.json] [--only NAME]
 """
 import argparse
 import json

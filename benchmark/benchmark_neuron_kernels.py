@@ -9,7 +9,7 @@ and reports microseconds, achieved GB/s against the algorithmic traffic of OUR k
 reference's fastest backend.  Inputs x ~ N(0.5, 1), upstream gradients ~ N(0, 1); each
 timed iteration follows an L2 flush; CUDA-event timing after warm-up.
 
-    python benchmark/benchmark_neuron_kernels.py --out gpurun_out/neuron_sweep.json
+    python benchmark/benchmark_neuron_kernels.py --out out/neuron_sweep.json
 """
 import argparse
 import json

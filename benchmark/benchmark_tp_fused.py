@@ -6,7 +6,7 @@ One process per GPU (torchrun); with one process the collectives vanish and the 
 GEMM vs cuBLAS.  CUDA-event timing on the launching stream, L2 flushed between iterations, median per rank,
 maximum over ranks.  The roofline line gives, per rank, max(FLOPs / measured bf16 peak, NVLink bytes / 770 GB/s).
 
-    python benchmark/benchmark_tp_fused.py --tokens-per-rank 2048 [--out gpurun_out/tp_fused.json]
+    python benchmark/benchmark_tp_fused.py --tokens-per-rank 2048 [--out out/tp_fused.json]
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 benchmark/benchmark_tp_fused.py ...
 """
 import argparse
