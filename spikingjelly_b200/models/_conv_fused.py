@@ -23,7 +23,7 @@ __all__ = ["eligible", "conv_bn_lif", "run_sequential"]
 def eligible(conv, bn, sn, x_seq: torch.Tensor) -> bool:
     if not (torch.is_tensor(x_seq) and x_seq.is_cuda and x_seq.ndim == 5) or _compute_dtype(x_seq) is None:
         return False
-    if type(conv).__mro__[1] is not nn.Conv2d and not isinstance(conv, nn.Conv2d):
+    if not isinstance(conv, nn.Conv2d):
         return False
     if conv.padding_mode != "zeros" or isinstance(conv.padding, str):
         return False
@@ -33,8 +33,9 @@ def eligible(conv, bn, sn, x_seq: torch.Tensor) -> bool:
         return False
     if getattr(sn, "store_v_seq", False):
         return False
+    # only from the reset state: the fused kernels start every sequence at the initial potential
     v = sn._memories.get("v") if hasattr(sn, "_memories") else None
-    return v == (sn.v_reset if sn.v_reset is not None else 0.0) if isinstance(v, float) else False
+    return isinstance(v, float) and v == (sn.v_reset if sn.v_reset is not None else 0.0)
 
 
 def conv_bn_lif(conv, bn, sn, x_seq: torch.Tensor) -> torch.Tensor:
