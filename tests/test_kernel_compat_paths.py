@@ -67,3 +67,35 @@ def test_spike_layers_match_plain_layers_on_gpu(level):
         assert len(tensor_cache.BOOL_TENSOR_CACHE.cache) == 0
     finally:
         configure.save_bool_spike_level = old
+
+
+def test_cfunction_expression_builders():
+    import math
+    from spikingjelly_b200.activation_based.cuda_kernel.auto_cuda import cfunction as cf
+    assert cf.mul(None, "a", "b", "float") == "(a * b)" and cf.mul("z", "a", "1.0f", "float") == "z = a;"
+    assert cf.add("z", "0.0f", "b", "float") == "z = b;" and cf.sub(None, "a", "b", "half2") == "(__hsub2(a, b))"
+    assert cf.mul(None, "__float2half2_rn(1.0f)", "b", "half2") == "(b)"
+    assert cf.heaviside("s", "h - v_th", "float") == "s = (float) (h - v_th >= 0.0f);"
+    assert cf.constant(None, 2, "float") == "(2.0f)" and "__float2half2_rn" in cf.constant("c", 0.5, "half2")
+    nested = cf.if_else_else("w", "x", "y", "z", "mx", "my", "float")
+    assert nested.startswith("w = x * mx + (y * my + z * (1.0f - my)) * (1.0f - mx)")
+    with pytest.raises(NotImplementedError):
+        cf.add(None, "a", "b", "double")
+    # the fp32 surrogate formulas are plain C: evaluate them with Python after translating the math calls
+    def evaluate(code, v):
+        expr = code.split("=", 1)[1].rstrip(";")
+        for c_name, py in (("expf", "math.exp"), ("fabsf", "abs"), ("__powf", "pow"), ("fminf", "min")):
+            expr = expr.replace(c_name, py)
+        import re
+        expr = re.sub(r"(\d)f\b", r"\1", expr)
+        expr = re.sub(r"\(([^()?]+)\?([^:()]+):([^()]+)\)", r"((\2) if (\1) else (\3))", expr)
+        return eval(expr, {"math": math, "abs": abs, "pow": pow, "min": min, "x": v})
+    from spikingjelly_b200.activation_based import surrogate
+    for v in (-0.7, 0.0, 0.3):
+        xt = torch.tensor(v, dtype=torch.float64, requires_grad=True)
+        surrogate.Sigmoid(alpha=4.0)(xt).backward()
+        assert evaluate(cf.sigmoid_backward("g", "x", 4.0, "float"), v) == pytest.approx(float(xt.grad), rel=1e-6)
+        xt = torch.tensor(v, dtype=torch.float64, requires_grad=True)
+        surrogate.ATan(alpha=2.0)(xt).backward()
+        assert evaluate(cf.atan_backward("g", "x", 2.0, "float"), v) == pytest.approx(float(xt.grad), rel=1e-6)
+    assert "__floats2half2_rn(g_lo, g_hi)" in cf.sigmoid_backward("g", "x", 4.0, "half2")
