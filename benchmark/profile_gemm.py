@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """Three launches of one tensor-core kernel on a case that exceeds L2 but holds well under 1 GB, for use under
-``ncu --set full -k regex:<gemm_kernel|spike_gemm_kernel> -c 1``.  Prints the CUDA-event time of the last launch.
+``ncu --set full --clock-control none -k regex:<gemm_kernel|spike_gemm_kernel> -c 1``.  Prints the CUDA-event time of the last launch.
 
     python benchmark/profile_gemm.py --kind bf16|fp8|spike [--M 16384 --N 4096 --K 2048]
 """

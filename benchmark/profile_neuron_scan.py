@@ -1,6 +1,7 @@
 #!/usr/bin/env python
 """A few forward+backward launches of the multi-step LIF kernels on one tensor, for use
-under a profiler: ``ncu --set full -k regex:scan_ -c 2 python benchmark/profile_neuron_scan.py``.
+under a profiler: ``ncu --set full --clock-control none -k regex:scan_ -c 2 python benchmark/profile_neuron_scan.py --logN 22``
+(a small case: one kernel, two launches, well under 1 GB on the device).
 Prints CUDA-event times of the isolated forward and backward kernels (median of `--iters`)."""
 import argparse
 import sys

@@ -1,6 +1,7 @@
 #!/usr/bin/env python
 """A few SEW-ResNet-18 training steps (config: T = 16, 2 x 128 x 128 event frames, bf16) for use under a profiler:
-``ncu --metrics gpu__time_duration.sum --profile-from-start off ... python benchmark/profile_sew_step.py``.
+``ncu --metrics gpu__time_duration.sum --clock-control none --profile-from-start off --csv python benchmark/profile_sew_step.py``
+(one pass per launch; run the same command without ``ncu`` first).
 Only the last step lies between cudaProfilerStart/Stop."""
 import argparse
 import sys
