@@ -241,6 +241,12 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def check_comm():
+        # a gradient exchange whose peer wait ran out raises here: its throughput must not be reported
+        check = getattr(step_model, "check_communication", None)
+        if check is not None:
+            check()
+
     for _ in range(args.warmup):
         train_step(dev_x, dev_y)
         flush.zero_()
@@ -260,6 +266,7 @@ def main():
         flush.zero_()
     ev1.record()
     barrier()
+    check_comm()
     ms = ev0.elapsed_time(ev1)
     n_launch = launches.total() if launches is not None else None
     t = torch.tensor([ms], device=device)
@@ -295,6 +302,7 @@ def main():
         loss_val = pending.get()
         ev1.record()
         barrier()
+        check_comm()
         wall_ms = (time.perf_counter() - t0) * 1e3
         e_ms = max(ev0.elapsed_time(ev1), 0.0)
         t = torch.tensor([e_ms, wall_ms], device=device)

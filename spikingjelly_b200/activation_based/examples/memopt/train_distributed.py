@@ -112,6 +112,8 @@ def main(argv=None):
         optimizer = D.build_snn_optimizer(net, args.distributed_mode, lr=args.lr, weight_decay=args.weight_decay, optimizer_sharding=args.optimizer_sharding or "none")
     if optimizer is None:
         optimizer = torch.optim.AdamW(net.parameters(), lr=args.lr, weight_decay=args.weight_decay)
+    if hasattr(net, "guard_optimizer"):
+        net.guard_optimizer(optimizer)
 
     loader = synthetic_loader(args, device, rank) if args.synthetic or args.data_dir is None else real_loader(args, rank, world)
     for epoch in range(args.epochs):
@@ -131,6 +133,8 @@ def main(argv=None):
             loss_sum += loss.item()
         if device.type == "cuda":
             torch.cuda.synchronize()
+        if hasattr(net, "check_communication"):
+            net.check_communication()        # raises CommError if a gradient exchange of this epoch gave up on a peer
         if rank == 0:
             print(f"epoch {epoch}: mean loss {loss_sum / max(step, 1):.4f}, {seen * world / (time.time() - t0):.1f} samples/s over {world} rank(s), "
                   f"mode {args.distributed_mode}")

@@ -69,6 +69,16 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
+// TMA im2col load (NHWC tensor, 4-D map made by cuTensorMapEncodeIm2col): `pixels-per-column` pixels starting at the
+// bounding-box position (w, h, n) and walking w, then h, then n in steps of the map's traversal strides, each pixel
+// shifted by the filter-tap offset (off_w, off_h); `channels-per-pixel` channels from `c` on.  Positions outside the
+// tensor read as zero (that is the convolution's padding).  One pixel = one 128-byte swizzled row in shared memory.
+__device__ __forceinline__ void tma_load_im2col_4d(void* smem_dst, const CUtensorMap* map, int c, int w, int h, int n,
+                                                   uint16_t off_w, uint16_t off_h, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
+}
 // TMA store of one box from this CTA's shared memory (bulk async-group completion)
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"

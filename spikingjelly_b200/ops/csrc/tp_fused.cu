@@ -420,9 +420,9 @@ reduce_residual_kernel(HT* __restrict__ h, const __nv_bfloat16* __restrict__ sta
     }
 }
 
-__global__ void tp_barrier_kernel(comm::PeerPtrs pp, int rank, int world, uint32_t epoch, comm::CommStatus* status, long long spin_limit) {
+__global__ void tp_barrier_kernel(comm::PeerPtrs pp, int rank, int world, uint32_t epoch, comm::CommStatus* status, long long timeout_ns) {
     __threadfence_system();
-    comm::block_barrier(pp, rank, world, 1, epoch, 1, status, spin_limit);
+    comm::block_barrier(pp, rank, world, 1, epoch, 1, status, timeout_ns);
 }
 
 template <int BN, int STAGES, int EPI>
@@ -548,9 +548,9 @@ void tp_barrier(std::vector<int64_t> sig_ptrs, int64_t rank, int64_t epoch, at::
     const c10::cuda::CUDAGuard guard(status.device());
     comm::PeerPtrs pp{};
     for (int j = 0; j < world; ++j) pp.sig[j] = reinterpret_cast<uint32_t*>(sig_ptrs[j]);
-    const long long spin_limit = (long long)(timeout_s * 1e7) + 1000;
+    const long long timeout_ns = (long long)(timeout_s * 1e9) + 1000;
     tp_barrier_kernel<<<1, 32, 0, at::cuda::getCurrentCUDAStream()>>>(pp, (int)rank, world, (uint32_t)epoch,
-                                                                     reinterpret_cast<comm::CommStatus*>(status.data_ptr<int>()), spin_limit);
+                                                                     reinterpret_cast<comm::CommStatus*>(status.data_ptr<int>()), timeout_ns);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 

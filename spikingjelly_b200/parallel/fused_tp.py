@@ -27,7 +27,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-from .comm import CommError
+from .comm import CommError, next_epoch
 
 __all__ = ["FusedTPWorkspace", "FusedSpikingSubLayer", "pack_pitch", "fused_ffn_from_block"]
 
@@ -45,7 +45,7 @@ class FusedTPWorkspace:
     """Symmetric buffers shared by every fused sub-layer of a model (they run one after another)."""
 
     def __init__(self, T: int, tokens_per_rank: int, d_model: int, device, group: Optional[dist.ProcessGroup] = None,
-                 timeout_s: float = 2.0):
+                 timeout_s: float = 120.0):
         if tokens_per_rank % 128 or d_model % 256:
             raise ValueError("tokens_per_rank must be a multiple of 128 and d_model a multiple of 256")
         self.T, self.tokens_per_rank, self.d_model = T, tokens_per_rank, d_model
@@ -100,7 +100,7 @@ class FusedTPWorkspace:
         if self.world == 1:
             return
         torch.ops.sjb200.tp_barrier(self.sig_ptrs, self.rank, self._epoch, self._status, self.timeout_s)
-        self._epoch = (self._epoch + 1) & 0x7FFFFFFF
+        self._epoch = next_epoch(self._epoch, 1)
 
     def check(self) -> None:
         """Synchronises; raises if a peer wait or a pipeline wait inside a GEMM expired since the last check."""
