@@ -24,7 +24,7 @@ from ..logger import logger
 
 __all__ = [
     "check_backend_library", "canonical_backend", "StepModule", "SingleStepModule",
-    "MultiStepModule", "MemoryModule", "named_memories", "memories",
+    "MultiStepModule", "MemoryModule", "ElidedState", "elide_states", "named_memories", "memories",
     "extract_memories", "load_memories", "to_functional_forward",
 ]
 
@@ -85,6 +85,25 @@ class MultiStepModule(StepModule):
 def _same_layout(a: Any, b: Any) -> bool:
     return (isinstance(a, torch.Tensor) and isinstance(b, torch.Tensor) and a.shape == b.shape
             and a.dtype == b.dtype and a.device == b.device)
+
+
+class ElidedState:
+    """Placeholder memory value: "this state was advanced by a fused schedule that does not keep it".
+
+    The fused model schedules start every sequence from the reset state and never write the membrane potentials
+    back.  They leave this marker in the neurons' memories so that a second forward without ``reset()`` fails loudly
+    (the module path would carry the state over; silently restarting from the reset value would not).  ``reset()``
+    and ``load_memories`` replace it like any other value."""
+
+    def __repr__(self):
+        return "ElidedState()"
+
+
+def elide_states(modules) -> None:
+    """Mark every memory of the given :class:`MemoryModule` instances as not kept (see :class:`ElidedState`)."""
+    for m in modules:
+        for key in m._memories:
+            m._memories[key] = ElidedState()
 
 
 class MemoryModule(nn.Module, StepModule):
@@ -182,6 +201,11 @@ class MemoryModule(nn.Module, StepModule):
         return outs[0] if len(outs) == 1 else outs
 
     def forward(self, *args, **kwargs):
+        for value in self._memories.values():
+            if isinstance(value, ElidedState):
+                raise RuntimeError(
+                    f"{type(self).__name__}: a fused model schedule advanced this module without storing its state; "
+                    "call functional.reset_net() before the next forward, or set `model.fused = False` for stateful use")
         if self.step_mode == "s":
             return self.single_step_forward(*args, **kwargs)
         if self.step_mode == "m":

@@ -15,7 +15,8 @@ import torch.nn.functional as F
 
 from ..activation_based import base
 from ..ops.bn_lif import bn_lif
-from ._resnet_fused import _compute_dtype, _init_v, _spec
+from ..ops import conv as conv_ops
+from ._resnet_fused import _compute_dtype, _init_v, _spec, bn_is_fusable
 
 __all__ = ["eligible", "conv_bn_lif", "run_sequential"]
 
@@ -27,7 +28,7 @@ def eligible(conv, bn, sn, x_seq: torch.Tensor) -> bool:
         return False
     if conv.padding_mode != "zeros" or isinstance(conv.padding, str):
         return False
-    if not isinstance(bn, nn.BatchNorm2d) or not bn.affine or bn.num_features % 8:
+    if not bn_is_fusable(bn):
         return False
     if getattr(sn, "step_mode", "s") != "m" or not getattr(sn, "native", False) or _spec(sn) is None:
         return False
@@ -43,15 +44,27 @@ def conv_bn_lif(conv, bn, sn, x_seq: torch.Tensor) -> torch.Tensor:
     T, N = x_seq.shape[:2]
     dt = _compute_dtype(x_seq)
     h = x_seq.flatten(0, 1).to(dt).contiguous(memory_format=torch.channels_last)
-    w = conv.weight.to(dtype=dt, memory_format=torch.channels_last)
-    b = None if conv.bias is None else conv.bias.to(dt)
     with torch.autocast("cuda", enabled=False):
-        y = F.conv2d(h, w, b, conv.stride, conv.padding, conv.dilation, conv.groups)
-    TN, C, H, W = y.shape
-    rows = y.permute(0, 2, 3, 1)
-    if not rows.is_contiguous():
-        rows = rows.contiguous()
-    out = bn_lif(rows.reshape(T, N * H * W, C), bn, _spec(sn), v_init=_init_v(sn))
+        if conv_ops.supports(conv, h):
+            # implicit GEMM on the tensor cores.  Without a bias the epilogue's column sums serve the batch norm;
+            # with one the sums are taken again after the add (a batch norm in training mode cancels the bias anyway)
+            training = bn.training or bn.running_mean is None
+            rows, stats, (H, W) = conv_ops.conv2d_rows(h.permute(0, 2, 3, 1), conv.weight, conv.stride, conv.padding, conv.dilation,
+                                                       want_stats=training and conv.bias is None)
+            if conv.bias is not None:
+                rows = rows + conv.bias.to(dt)
+            C = rows.shape[1]
+            out = bn_lif(rows.view(T, N * H * W, C), bn, _spec(sn), v_init=_init_v(sn), stats=stats)
+        else:
+            w = conv.weight.to(dtype=dt, memory_format=torch.channels_last)
+            b = None if conv.bias is None else conv.bias.to(dt)
+            y = F.conv2d(h, w, b, conv.stride, conv.padding, conv.dilation, conv.groups)
+            TN, C, H, W = y.shape
+            rows = y.permute(0, 2, 3, 1)
+            if not rows.is_contiguous():
+                rows = rows.contiguous()
+            out = bn_lif(rows.reshape(T, N * H * W, C), bn, _spec(sn), v_init=_init_v(sn))
+    base.elide_states([sn])
     return out.view(T, N, H, W, C).permute(0, 1, 4, 2, 3)
 
 

@@ -19,7 +19,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..activation_based import layer, neuron, surrogate
+from ..activation_based import base, layer, neuron, surrogate
+from ..ops import conv as conv_ops
 from ..ops import conv_stem as stem_ops
 from ..ops import pool as pool_ops
 from ..ops.bn_lif import bn_lif
@@ -48,6 +49,12 @@ def _compute_dtype(x: torch.Tensor) -> Optional[torch.dtype]:
     return x.dtype if x.dtype in (torch.bfloat16, torch.float16) else None
 
 
+def bn_is_fusable(m) -> bool:
+    """Plain affine BatchNorm2d with per-process statistics.  SyncBatchNorm needs statistics over all ranks, which the
+    fused kernels do not exchange."""
+    return isinstance(m, nn.BatchNorm2d) and not isinstance(m, nn.SyncBatchNorm) and m.affine and m.num_features % 8 == 0
+
+
 def eligible(model, x: torch.Tensor) -> bool:
     if not x.is_cuda or x.ndim != 5 or _compute_dtype(x) is None:
         return False
@@ -62,7 +69,7 @@ def eligible(model, x: torch.Tensor) -> bool:
             if m._memories["v"] != (m.v_reset if m.v_reset is not None else 0.0):
                 return False
         elif isinstance(m, nn.modules.batchnorm._BatchNorm):
-            if not isinstance(m, nn.BatchNorm2d) or not m.affine or m.num_features % 8:
+            if not bn_is_fusable(m):
                 return False
         elif isinstance(m, nn.Conv2d) and (m.bias is not None or m.padding_mode != "zeros"):
             return False
@@ -96,9 +103,18 @@ def _stage(conv, bn, sn, h: torch.Tensor, T: int, residual: Optional[torch.Tenso
         C = rows.shape[1]
         out = bn_lif(rows.view(T, -1, C), bn, _spec(sn), v_init=_init_v(sn), stats=stats)
         return out.view(h.shape[0], H, W, C).permute(0, 3, 1, 2)
+    res_rows = None if residual is None else _rows(residual, T)
+    if conv_ops.supports(conv, h):
+        # implicit GEMM on the tensor cores; the epilogue sums the BN statistics
+        training = bn.training or bn.running_mean is None
+        rows, stats, (H, W) = conv_ops.conv2d_rows(h.permute(0, 2, 3, 1), conv.weight, conv.stride, conv.padding, conv.dilation,
+                                                   want_stats=training)
+        C = rows.shape[1]
+        out = bn_lif(rows.view(T, -1, C), bn, _spec(sn), residual=res_rows, v_init=_init_v(sn), stats=stats)
+        return out.view(h.shape[0], H, W, C).permute(0, 3, 1, 2)
     y = _conv(conv, h)
     TB, C, H, W = y.shape
-    out = bn_lif(_rows(y, T), bn, _spec(sn), residual=None if residual is None else _rows(residual, T), v_init=_init_v(sn))
+    out = bn_lif(_rows(y, T), bn, _spec(sn), residual=res_rows, v_init=_init_v(sn))
     return out.view(TB, H, W, C).permute(0, 3, 1, 2)
 
 
@@ -132,6 +148,7 @@ def forward(model, x: torch.Tensor) -> torch.Tensor:
     for stage in (model.layer1, model.layer2, model.layer3, model.layer4):
         for blk in stage:
             h = _block(blk, h, T)
+    base.elide_states(m for m in model.modules() if isinstance(m, neuron.BaseNode))
     size = model.avgpool.output_size
     size = (size, size) if isinstance(size, int) else tuple(size)
     if size == (1, 1):

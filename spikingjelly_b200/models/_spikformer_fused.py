@@ -23,7 +23,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..activation_based import neuron, surrogate
+from ..activation_based import base, neuron, surrogate
+from ..ops import conv as conv_ops
 from ..ops import conv_stem as stem_ops
 from ..ops import gemm as G
 from ..ops.bn_lif import bn_lif, bn_pool_lif
@@ -63,8 +64,8 @@ def eligible(model, x: torch.Tensor) -> bool:
                 return False
             if m._memories["v"] != (m.v_reset if m.v_reset is not None else 0.0):
                 return False
-        elif isinstance(m, nn.modules.batchnorm._BatchNorm) and not m.affine:
-            return False
+        elif isinstance(m, nn.modules.batchnorm._BatchNorm) and (not m.affine or isinstance(m, nn.SyncBatchNorm)):
+            return False        # SyncBatchNorm needs statistics over all ranks; the fused kernels keep them per process
     return True
 
 
@@ -80,8 +81,13 @@ def _stem_stage(stage, h: torch.Tensor, T: int, static: bool, dt) -> torch.Tenso
         # the image itself (3 channels): patch matrix + tensor-core GEMM instead of cuDNN's padded-channel kernel
         rows, _, (oh, ow) = stem_ops.conv2d_few_channels(h, conv.weight, conv.stride, conv.padding, want_stats=False)
         y = rows.view(h.shape[0], oh, ow, rows.shape[1]).permute(0, 3, 1, 2)
+    elif conv_ops.supports(conv, h) and conv.bias is None:
+        # implicit GEMM on the tensor cores (TMA-gathered patches), output rows are the channels-last result
+        rows, _, (oh, ow) = conv_ops.conv2d_rows(h.permute(0, 2, 3, 1), conv.weight, conv.stride, conv.padding, conv.dilation)
+        y = rows.view(h.shape[0], oh, ow, rows.shape[1]).permute(0, 3, 1, 2)
     else:
-        y = F.conv2d(h, conv.weight.to(dt), None, conv.stride, conv.padding, conv.dilation, conv.groups)
+        y = F.conv2d(h, conv.weight.to(dt), None if conv.bias is None else conv.bias.to(dt), conv.stride, conv.padding,
+                     conv.dilation, conv.groups)
     lif = stage.neuron
     spec = _spec(lif)
     if pool is None:
@@ -173,5 +179,6 @@ def forward(model, x: torch.Tensor) -> torch.Tensor:
         X = h.permute(0, 2, 3, 1).reshape(T, B * L, C)
         for blk in model.blocks:
             X = _block(blk, X, T, B, L, dt)
+        base.elide_states(m for m in model.modules() if isinstance(m, neuron.BaseNode))
         feat = X.view(T, B, L, C).mean(dim=2)
         return F.linear(feat, model.head.weight.to(dt), None if model.head.bias is None else model.head.bias.to(dt))

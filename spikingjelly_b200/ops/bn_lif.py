@@ -17,6 +17,14 @@ from .neuron_scan import NeuronSpec
 __all__ = ["bn_lif", "BNLIFFunction"]
 
 
+def _discarded_forward() -> bool:
+    """True during the first (thrown-away) forward of a gradient-checkpointed segment
+    (``memopt.checkpointing.in_gc_1st_forward``): running statistics are then left alone, exactly like
+    ``layer.BatchNorm*`` do, so that only the forward that counts updates them."""
+    from ..activation_based.memopt.checkpointing import in_gc_1st_forward
+    return in_gc_1st_forward()
+
+
 class BNLIFFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y, gamma, beta, running_mean, running_var, residual, training: bool, momentum: float,
@@ -61,14 +69,7 @@ def bn_lif(y: torch.Tensor, bn: torch.nn.modules.batchnorm._BatchNorm, spec: Neu
     """``y``: contiguous ``[T, ..., C]`` with ``C == bn.num_features`` (channels last).  ``stats``: optional
     ``[blocks, 2, C]`` fp32 partial sums of ``y`` and ``y^2`` per channel (``ops.gemm.linear_with_stats``)."""
     require()
-    training = bn.training or bn.running_mean is None
-    momentum = 0.0 if bn.momentum is None else float(bn.momentum)
-    if bn.training and bn.track_running_stats and bn.num_batches_tracked is not None:
-        bn.num_batches_tracked.add_(1)
-        if bn.momentum is None:
-            momentum = 1.0 / float(bn.num_batches_tracked)
-    rm = bn.running_mean if (bn.track_running_stats and bn.training) or not training else None
-    rv = bn.running_var if (bn.track_running_stats and bn.training) or not training else None
+    training, momentum, rm, rv = _bn_args(bn)
     need_grad = torch.is_grad_enabled() and (y.requires_grad or (bn.weight is not None and bn.weight.requires_grad))
     return BNLIFFunction.apply(y.contiguous(), bn.weight, bn.bias, rm, rv, residual, training, momentum, float(bn.eps),
                                spec, float(v_init), need_grad, stats)
@@ -106,13 +107,16 @@ class BNPoolLIFFunction(torch.autograd.Function):
 
 
 def _bn_args(bn):
+    """``(training, momentum, running_mean, running_var)`` for the statistics kernels; the running tensors are passed
+    (and updated in place) only by a training forward that counts."""
     training = bn.training or bn.running_mean is None
     momentum = 0.0 if bn.momentum is None else float(bn.momentum)
-    if bn.training and bn.track_running_stats and bn.num_batches_tracked is not None:
+    update = bn.training and bn.track_running_stats and not _discarded_forward()
+    if update and bn.num_batches_tracked is not None:
         bn.num_batches_tracked.add_(1)
         if bn.momentum is None:
             momentum = 1.0 / float(bn.num_batches_tracked)
-    use_running = (bn.track_running_stats and bn.training) or not training
+    use_running = update or not training
     return training, momentum, (bn.running_mean if use_running else None), (bn.running_var if use_running else None)
 
 

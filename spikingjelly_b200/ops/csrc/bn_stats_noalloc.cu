@@ -143,11 +143,29 @@ extern "C" SJB200_EXPORT int sjb200_bn_stats_noalloc(const void* y, int dtype, l
     const int rc = scratch_for_current_device(&scratch, &dev);
     if (rc != SJB200_NOALLOC_OK) return rc;
 
-    cudaPointerAttributes attr{};
-    cudaError_t err = cudaPointerGetAttributes(&attr, y);
-    if (err != cudaSuccess) return fail(SJB200_NOALLOC_E_BAD_ARGUMENT, "cudaPointerGetAttributes(y)", err);
-    if (attr.type == cudaMemoryTypeDevice && attr.device != dev)
-        return fail(SJB200_NOALLOC_E_WRONG_DEVICE, "y lives on a device other than the current one");
+    // Every operand must be memory the kernel may dereference: device memory of the current device, or managed
+    // memory.  Host and unregistered pointers are refused here, before anything is launched.
+    const struct { const void* ptr; const char* name; } operands[] = {
+        {y, "y"}, {mean, "mean"}, {invstd, "invstd"}, {scale, "scale"}, {shift, "shift"}, {gamma, "gamma"}, {beta, "beta"}};
+    cudaError_t err = cudaSuccess;
+    for (const auto& op : operands) {
+        if (op.ptr == nullptr) continue;                      // gamma / beta are optional
+        cudaPointerAttributes attr{};
+        err = cudaPointerGetAttributes(&attr, op.ptr);
+        if (err != cudaSuccess) {
+            std::snprintf(t_error, sizeof(t_error), "cudaPointerGetAttributes(%s): %s", op.name, cudaGetErrorString(err));
+            return SJB200_NOALLOC_E_BAD_ARGUMENT;
+        }
+        if (attr.type == cudaMemoryTypeManaged) continue;
+        if (attr.type != cudaMemoryTypeDevice) {
+            std::snprintf(t_error, sizeof(t_error), "%s is not device memory (host or unregistered pointer)", op.name);
+            return SJB200_NOALLOC_E_BAD_ARGUMENT;
+        }
+        if (attr.device != dev) {
+            std::snprintf(t_error, sizeof(t_error), "%s lives on device %d, the current device is %d", op.name, attr.device, dev);
+            return SJB200_NOALLOC_E_WRONG_DEVICE;
+        }
+    }
 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     // the arrival counter is the only part of the scratch that must start at zero

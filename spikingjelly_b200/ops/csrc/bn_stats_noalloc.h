@@ -43,11 +43,11 @@ extern "C" {
 
 enum {
     SJB200_NOALLOC_OK = 0,
-    SJB200_NOALLOC_E_BAD_ARGUMENT = -1,   // null pointer, rows <= 0, channels not a multiple of 8, unknown dtype
+    SJB200_NOALLOC_E_BAD_ARGUMENT = -1,   // null / host / unregistered pointer, rows <= 0, channels not a multiple of 8, unknown dtype
     SJB200_NOALLOC_E_TOO_LARGE = -2,      // channels > SJB200_BN_NOALLOC_MAX_CHANNELS
     SJB200_NOALLOC_E_SETUP = -3,          // the scratch symbol could not be resolved on this device
     SJB200_NOALLOC_E_LAUNCH = -4,         // the CUDA runtime refused the memset or the launch
-    SJB200_NOALLOC_E_WRONG_DEVICE = -5    // `y` does not live on the current device
+    SJB200_NOALLOC_E_WRONG_DEVICE = -5    // an operand lives on a device other than the current one
 };
 
 // dtype: 0 = float32, 1 = float16, 2 = bfloat16

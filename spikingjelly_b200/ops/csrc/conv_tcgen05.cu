@@ -110,7 +110,7 @@ std::tuple<at::Tensor, at::Tensor> conv2d_nhwc_forward(const at::Tensor& x, cons
     const bool bf16 = x.scalar_type() == at::kBFloat16;
     const int64_t M = s.Nb * s.Ho * s.Wo, N = s.K, K = s.R * s.S * s.C;
     const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-    const int BN = N > 128 ? 256 : 128;
+    const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
     const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
 
     GemmArgs g{};
@@ -131,12 +131,13 @@ std::tuple<at::Tensor, at::Tensor> conv2d_nhwc_forward(const at::Tensor& x, cons
     const CUtensorMap ta = make_im2col_map(x.data_ptr(), s.Nb, s.H, s.W, s.C, -s.ph, -s.pw, s.ph - s.dh * ((int)s.R - 1),
                                            s.pw - s.dw * ((int)s.S - 1), s.sh, s.sw, BM, bf16);
     const CUtensorMap tb = make_map(w.data_ptr(), N, K, K, BN, bf16);
-    const CUtensorMap td = make_map(out.data_ptr(), M, N, N, BM, bf16, 32);
+    const CUtensorMap td = make_map(out.data_ptr(), M, N, N, 32, bf16, 32);
     KernelStatus* stp = reinterpret_cast<KernelStatus*>(status_word(x.device()).data_ptr<int>());
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
     const int grid = std::min(tiles, sms);
     if (BN == 256) launch<256, 4, false, false, 2, 1>(ta, tb, td, out.data_ptr(), g, stp, grid, stream, cg);
-    else launch<128, 6, false, false, 2, 1>(ta, tb, td, out.data_ptr(), g, stp, grid, stream, cg);
+    else if (BN == 128) launch<128, 6, false, false, 2, 1>(ta, tb, td, out.data_ptr(), g, stp, grid, stream, cg);
+    else launch<64, 8, false, false, 2, 1>(ta, tb, td, out.data_ptr(), g, stp, grid, stream, cg);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
     return {out, stats};
 }
@@ -168,7 +169,7 @@ at::Tensor conv2d_nhwc_dgrad(const at::Tensor& gy, const at::Tensor& w, int64_t 
     KernelStatus* stp = reinterpret_cast<KernelStatus*>(status_word(gy.device()).data_ptr<int>());
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
     const int64_t N = Cin;
-    const int BN = N > 128 ? 256 : 128;
+    const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
     // the filter as a [Cout, R*S*Cin] matrix read MN-major: boxes of 64 output channels (k) x 64 input channels
     const CUtensorMap tb = make_map(w.data_ptr(), Cout, s.R * s.S * Cin, s.R * s.S * Cin, BK, bf16);
 
@@ -200,10 +201,11 @@ at::Tensor conv2d_nhwc_dgrad(const at::Tensor& gy, const at::Tensor& w, int64_t 
             cg.out_mul_h = s.sh; cg.out_mul_w = s.sw; cg.out_add_h = a; cg.out_add_w = b;
             const CUtensorMap ta = make_im2col_map(gy.data_ptr(), s.Nb, s.Ho, s.Wo, Cout, cg.base_h, cg.base_w,
                                                    (int)(cnt_h + cg.base_h - s.Ho), (int)(cnt_w + cg.base_w - s.Wo), 1, 1, BM, bf16);
-            const CUtensorMap td = dense ? make_map(gx.data_ptr(), M, N, N, BM, bf16, 32) : ta;
+            const CUtensorMap td = dense ? make_map(gx.data_ptr(), M, N, N, 32, bf16, 32) : ta;
             const int grid = std::min(tiles, sms);
             if (BN == 256) launch<256, 4, false, true, 2, 1>(ta, tb, td, gx.data_ptr(), g, stp, grid, stream, cg);
-            else launch<128, 6, false, true, 2, 1>(ta, tb, td, gx.data_ptr(), g, stp, grid, stream, cg);
+            else if (BN == 128) launch<128, 6, false, true, 2, 1>(ta, tb, td, gx.data_ptr(), g, stp, grid, stream, cg);
+            else launch<64, 8, false, true, 2, 1>(ta, tb, td, gx.data_ptr(), g, stp, grid, stream, cg);
             C10_CUDA_KERNEL_LAUNCH_CHECK();
         }
     }

@@ -92,8 +92,8 @@ static at::Tensor gemm_16bit_impl(const at::Tensor& a, const at::Tensor& b, bool
         scratch = at::empty({splits, M, N}, opts.dtype(at::kFloat));
         dptr = scratch.data_ptr();
     }
-    // 16-bit results leave through TMA (box 128 x 32, 64-byte swizzle); fp32 results are stored directly
-    const CUtensorMap td = g.out_f32 ? ta : make_map(out.data_ptr(), M, N, N, BM, bf16, 32);
+    // 16-bit results leave through TMA (one 32 x 32 box per epilogue warp, 64-byte swizzle); fp32 results are stored directly
+    const CUtensorMap td = g.out_f32 ? ta : make_map(out.data_ptr(), M, N, N, 32, bf16, 32);
     at::Tensor& st = status_word(a.device());
     KernelStatus* stp = reinterpret_cast<KernelStatus*>(st.data_ptr<int>());
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
@@ -196,7 +196,7 @@ at::Tensor gemm_fp8(const at::Tensor& a, const at::Tensor& b, const c10::optiona
         scratch = at::empty({splits, M, N}, opts.dtype(at::kFloat));
         dptr = scratch.data_ptr();
     }
-    const CUtensorMap td = g.out_f32 ? ta : make_map(out.data_ptr(), M, N, N, BM, true, 32);
+    const CUtensorMap td = g.out_f32 ? ta : make_map(out.data_ptr(), M, N, N, 32, true, 32);
     at::Tensor& st = status_word(a.device());
     KernelStatus* stp = reinterpret_cast<KernelStatus*>(st.data_ptr<int>());
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();

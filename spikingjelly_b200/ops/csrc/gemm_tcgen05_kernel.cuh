@@ -37,7 +37,8 @@ using namespace tc;
 constexpr int BM = 128;
 constexpr int BK = 64;          // 64 x 2 B = one 128 B swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 320;   // 10 warps: producer, mma, 2 x 4 epilogue (each group of four drains half of the columns)
+constexpr int kThreads = 320;
+constexpr int kWarpStageBytes = 32 * 64;   // one epilogue warp's staging buffer: 32 rows x 32 16-bit columns   // 10 warps: producer, mma, 2 x 4 epilogue (each group of four drains half of the columns)
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -45,7 +46,7 @@ struct SmemLayout {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int OUT_OFFSET = BAR_OFFSET + 1024;    // epilogue staging: 2 groups x 2 x [128 rows][32 cols] 16-bit
+    static constexpr int OUT_OFFSET = BAR_OFFSET + 1024;    // epilogue staging: 8 warps x 2 x [32 rows][32 cols] 16-bit
     static constexpr int OUT_BYTES = BM * 32 * 2;
     static constexpr int TOTAL = OUT_OFFSET + 4 * OUT_BYTES + 1024;   // + slack for 1024 B alignment
 };
@@ -97,6 +98,118 @@ struct ConvGeom {
     int wr0, wr_step, ws0, ws_step, S;
     int scatter, out_H, out_W, out_mul_h, out_mul_w, out_add_h, out_add_w;
 };
+
+// Epilogue of one output tile for one warp: drains NCHUNK chunks of 32 accumulator columns (this warp's 32 TMEM lanes =
+// 32 output rows) starting at chunk `c_begin`.  The TMEM load of chunk i + 1 is in flight while chunk i is converted
+// and stored.  16-bit results are staged in a buffer that belongs to this warp alone (32 rows x 64 bytes, 16-byte
+// chunks XOR-swizzled by (row >> 1) & 3 = the TMA 64-byte swizzle) and written by a TMA store of a 32 x 32 box:
+// full sectors, clipped at the matrix edges, asynchronous, and no barrier between warps.  `oc` counts this warp's
+// staged chunks (two buffers alternate; a buffer is reused once the store that read it has finished reading).
+template <int NCHUNK, int LOADER>
+__device__ __forceinline__ void drain_accumulator(uint32_t taddr, int c_begin, int m0, int n0, int split, int quarter, int lane,
+                                                  void* __restrict__ Dptr, const GemmArgs& g, const ConvGeom& cg, float alpha,
+                                                  const CUtensorMap* tmD, uint8_t* warp_stage, uint32_t& oc) {
+    const int row0 = m0 + quarter * 32, row = row0 + lane;
+    uint32_t r[32];
+    tmem_ld_32x32(taddr + c_begin * 32, r);
+#pragma unroll
+    for (int ci = 0; ci < NCHUNK; ++ci) {
+        const int c = c_begin + ci;
+        tmem_ld_wait();
+        uint32_t cur[32];
+#pragma unroll
+        for (int q = 0; q < 32; ++q) cur[q] = r[q];
+        if (ci + 1 < NCHUNK) tmem_ld_32x32(taddr + (c + 1) * 32, r);      // next chunk travels while this one is stored
+        if (g.alpha != nullptr) {
+#pragma unroll
+            for (int q = 0; q < 32; ++q) cur[q] = __float_as_uint(__uint_as_float(cur[q]) * alpha);
+        }
+        const int col0 = n0 + c * 32;
+        if (g.out_f32) {
+            // split-K partial sums / fp32 results: straight from registers, one 128-byte run per row
+            if (row < g.M && col0 < g.N) {
+                float* dst = reinterpret_cast<float*>(Dptr) + ((size_t)split * g.M + row) * g.ldd + col0;
+                if (col0 + 32 <= g.N) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        reinterpret_cast<uint4*>(dst)[q] = make_uint4(cur[4 * q], cur[4 * q + 1], cur[4 * q + 2], cur[4 * q + 3]);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 32; ++q)
+                        if (col0 + q < g.N) dst[q] = __uint_as_float(cur[q]);
+                }
+            }
+            continue;
+        }
+        uint32_t w[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const float lo = __uint_as_float(cur[2 * e]), hi = __uint_as_float(cur[2 * e + 1]);
+            if (g.out_bf16) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
+            else { __half2 v = __floats2half2_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
+        }
+        if constexpr (LOADER == 1) {
+            if (cg.scatter) {
+                // strided data gradient: this row is one input pixel of the launch's parity class
+                if (row < g.M && col0 + 32 <= g.N) {
+                    const int per_img = cg.Ht * cg.Wt;
+                    const int img = row / per_img, rem = row - img * per_img, i = rem / cg.Wt, j = rem - i * cg.Wt;
+                    const size_t pix = ((size_t)img * cg.out_H + (i * cg.out_mul_h + cg.out_add_h)) * cg.out_W +
+                                       (j * cg.out_mul_w + cg.out_add_w);
+                    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(Dptr) + pix * g.ldd + col0);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+                }
+                continue;
+            }
+        }
+        if (col0 >= g.N) continue;                              // nothing of this box lies inside the matrix (warp-uniform)
+        uint8_t* stage_buf = warp_stage + (oc & 1) * kWarpStageBytes;
+        if (oc >= 2) {
+            if (lane == 0) tma_store_wait_read<1>();               // the store that last read this buffer is done
+            __syncwarp();
+        }
+        ++oc;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int chunk = q ^ ((lane >> 1) & 3);
+            *reinterpret_cast<uint4*>(stage_buf + lane * 64 + chunk * 16) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            // rows past M are clipped by the TMA unit; a box that starts past M is not issued at all (its rows are zero and
+            // still feed the column sums below, so that every statistics slot is written)
+            if (row0 < g.M) tma_store_2d(tmD, stage_buf, col0, row0);
+            tma_store_commit();
+        }
+        if (g.stats != nullptr) {
+            // Column sums over this warp's 32 staged rows (the rounded values a batch norm will read).
+            // Lane = (column pair, row half); the upper half walks its rows one step ahead so that the
+            // two halves hit different 64-byte halves of a bank line.
+            const int cp = lane & 15, hi = lane >> 4;
+            float s1a = 0.f, s1b = 0.f, s2a = 0.f, s2b = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int rr = hi * 16 + ((i + hi) & 15);
+                const int chunk = (cp >> 2) ^ ((rr >> 1) & 3);
+                const uint32_t v = *reinterpret_cast<const uint32_t*>(stage_buf + rr * 64 + chunk * 16 + (cp & 3) * 4);
+                float lo, up;
+                if (g.out_bf16) { lo = __uint_as_float(v << 16); up = __uint_as_float(v & 0xffff0000u); }
+                else { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v)); lo = f.x; up = f.y; }
+                s1a += lo; s1b += up; s2a = fmaf(lo, lo, s2a); s2b = fmaf(up, up, s2b);
+            }
+            s1a += __shfl_xor_sync(0xffffffffu, s1a, 16); s1b += __shfl_xor_sync(0xffffffffu, s1b, 16);
+            s2a += __shfl_xor_sync(0xffffffffu, s2a, 16); s2b += __shfl_xor_sync(0xffffffffu, s2b, 16);
+            const int col = col0 + cp * 2;
+            if (hi == 0 && col < g.N) {
+                float* dst = g.stats + ((size_t)((m0 / BM) * 4 + quarter) * 2) * g.N + col;
+                *reinterpret_cast<float2*>(dst) = make_float2(s1a, s1b);
+                *reinterpret_cast<float2*>(dst + g.N) = make_float2(s2a, s2b);
+            }
+        }
+    }
+}
 
 // ES: operand element size in bytes (2: fp16 / bf16, 1: fp8).  A k-block is always one 128-byte
 // swizzle row, i.e. 128 / ES elements, and is consumed by four MMAs of 32 bytes of K each.
@@ -272,7 +385,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // ---------------------------------------------------------------- epilogue
         const int quarter = warp & 3;              // TMEM lane quarter this warp may read
         const int half = (warp - 2) >> 2;          // which half of the tile's columns this group of four warps drains
-        const int issuer = 64 + half * 128;        // the thread of the group that talks to the TMA unit
         uint32_t tl = 0, oc = 0;                   // tiles / output chunks handled so far
         for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tl) {
             const int split = tile / tiles_mn, mn = tile % tiles_mn;
@@ -285,115 +397,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) { if (lane == 0) { report(status, WAIT_TMEM_FULL, tile); *abort_flag = 1; } break; }
             fence_after_sync();
-            const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-#pragma unroll 1
-            for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + c * 32, r);
-                tmem_ld_wait();
-                if (g.alpha != nullptr) {
-#pragma unroll
-                    for (int q = 0; q < 32; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) * alpha);
-                }
-                const int col0 = n0 + c * 32;
-                if (row < g.M && col0 < g.N) {
-                    if (g.out_f32) {
-                        float* dst = reinterpret_cast<float*>(Dptr) + ((size_t)split * g.M + row) * g.ldd + col0;
-                        if (col0 + 32 <= g.N) {
-#pragma unroll
-                            for (int q = 0; q < 8; ++q)
-                                reinterpret_cast<uint4*>(dst)[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
-                        } else {
-#pragma unroll
-                            for (int q = 0; q < 32; ++q)
-                                if (col0 + q < g.N) dst[q] = __uint_as_float(r[q]);
-                        }
-                    }
-                }
-                if constexpr (LOADER == 1) {
-                    if (!g.out_f32 && cg.scatter) {
-                        // strided data gradient: this row is one input pixel of the launch's parity class
-                        if (row < g.M && col0 + 32 <= g.N) {
-                            const int per_img = cg.Ht * cg.Wt;
-                            const int img = row / per_img, rem = row - img * per_img, i = rem / cg.Wt, j = rem - i * cg.Wt;
-                            const size_t pix = ((size_t)img * cg.out_H + (i * cg.out_mul_h + cg.out_add_h)) * cg.out_W +
-                                               (j * cg.out_mul_w + cg.out_add_w);
-                            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(Dptr) + pix * g.ldd + col0);
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                uint32_t w[4];
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const float lo = __uint_as_float(r[8 * q + 2 * e]), hi = __uint_as_float(r[8 * q + 2 * e + 1]);
-                                    if (g.out_bf16) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
-                                    else { __half2 v = __floats2half2_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
-                                }
-                                dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
-                            }
-                        }
-                        continue;
-                    }
-                }
-                if (!g.out_f32) {
-                    // 16-bit output: stage the 128 x 32 chunk in shared memory (64-byte rows, 16-byte
-                    // chunks XOR-swizzled by (row >> 1) & 3 = the TMA 64B swizzle) and let TMA write it:
-                    // full-sector, clipped at the matrix edges, asynchronous.
-                    uint8_t* stage_buf = smem + L::OUT_OFFSET + (half * 2 + (oc & 1)) * L::OUT_BYTES;
-                    if (oc >= 2 && (int)threadIdx.x == issuer) tma_store_wait_read<1>();  // the store that last read this buffer is done
-                    ++oc;
-                    named_barrier(1 + half, 128);
-                    const int r_in_tile = quarter * 32 + lane;
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float lo = __uint_as_float(r[8 * q + 2 * e]), hi = __uint_as_float(r[8 * q + 2 * e + 1]);
-                            if (g.out_bf16) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
-                            else { __half2 v = __floats2half2_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
-                        }
-                        const int chunk = q ^ ((r_in_tile >> 1) & 3);
-                        *reinterpret_cast<uint4*>(stage_buf + r_in_tile * 64 + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
-                    fence_async_smem();
-                    named_barrier(1 + half, 128);
-                    if ((int)threadIdx.x == issuer) {
-                        tma_store_2d(&tmD, stage_buf, n0 + c * 32, m0);
-                        tma_store_commit();
-                    }
-                    if (g.stats != nullptr) {
-                        // Column sums over this warp's own 32 staged rows (the rounded values BN will read).
-                        // Lane = (column pair, row half); the upper half walks its rows one step ahead so that the
-                        // two halves hit different 64-byte halves of a bank line.
-                        const int cp = lane & 15, hi = lane >> 4;
-                        float s1a = 0.f, s1b = 0.f, s2a = 0.f, s2b = 0.f;
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const int rr = quarter * 32 + hi * 16 + ((i + hi) & 15);
-                            const int chunk = (cp >> 2) ^ ((rr >> 1) & 3);
-                            const uint32_t w = *reinterpret_cast<const uint32_t*>(stage_buf + rr * 64 + chunk * 16 + (cp & 3) * 4);
-                            float lo, up;
-                            if (g.out_bf16) { lo = __uint_as_float(w << 16); up = __uint_as_float(w & 0xffff0000u); }
-                            else { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w)); lo = f.x; up = f.y; }
-                            s1a += lo; s1b += up; s2a = fmaf(lo, lo, s2a); s2b = fmaf(up, up, s2b);
-                        }
-                        s1a += __shfl_xor_sync(0xffffffffu, s1a, 16); s1b += __shfl_xor_sync(0xffffffffu, s1b, 16);
-                        s2a += __shfl_xor_sync(0xffffffffu, s2a, 16); s2b += __shfl_xor_sync(0xffffffffu, s2b, 16);
-                        const int col = n0 + c * 32 + cp * 2;
-                        if (hi == 0 && col < g.N) {
-                            float* dst = g.stats + ((size_t)((m0 / BM) * 4 + quarter) * 2) * g.N + col;
-                            *reinterpret_cast<float2*>(dst) = make_float2(s1a, s1b);
-                            *reinterpret_cast<float2*>(dst + g.N) = make_float2(s2a, s2b);
-                        }
-                    }
-                }
-            }
+            drain_accumulator<BN / 64, LOADER>(taddr, half * (BN / 64), m0, n0, split, quarter, lane, Dptr, g, cg, alpha, &tmD,
+                                               smem + L::OUT_OFFSET + (warp - 2) * 2 * kWarpStageBytes, oc);
             fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar + acc);
         }
-        if ((int)threadIdx.x == issuer) tma_store_wait_all<0>();   // all output boxes written before the CTA retires
+        if (lane == 0) tma_store_wait_all<0>();                    // all output boxes written before the CTA retires
     }
 
     // -------------------------------------------------------------------- teardown
@@ -554,7 +565,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // ---------------------------------------------------------------- epilogue (both CTAs: own 128 rows)
         const int quarter = warp & 3;
         const int half = (warp - 2) >> 2;
-        const int issuer = 64 + half * 128;
         const uint32_t tempty_first = map_to_cta(smem_u32(tempty_bar), 0);
         uint32_t tl = 0, oc = 0;
         for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs, ++tl) {
@@ -562,7 +572,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int tm, tn;
             tile_coords(tile - split * tiles_mn, tiles_m, tiles_n, tm, tn);
             const int m0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * BN;
-            const int row = m0 + quarter * 32 + lane;
             const uint32_t acc = tl & 1, acc_ph = (tl >> 1) & 1;
             bool ok = true;
             if (lane == 0) ok = mbar_wait_bounded(tfull_bar + acc, acc_ph);
@@ -570,83 +579,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!ok) { if (lane == 0) { report(status, WAIT_TMEM_FULL, tile); *abort_flag = 1; } break; }
             fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-#pragma unroll 1
-            for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + c * 32, r);
-                tmem_ld_wait();
-                if (g.alpha != nullptr) {
-#pragma unroll
-                    for (int q = 0; q < 32; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) * alpha);
-                }
-                if (g.out_f32) {
-                    // split-K partial sums / fp32 results: straight from registers, one 128-byte run per row
-                    const int col0 = n0 + c * 32;
-                    if (row < g.M && col0 < g.N) {
-                        float* dst = reinterpret_cast<float*>(Dptr) + ((size_t)split * g.M + row) * g.ldd + col0;
-                        if (col0 + 32 <= g.N) {
-#pragma unroll
-                            for (int q = 0; q < 8; ++q)
-                                reinterpret_cast<uint4*>(dst)[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
-                        } else {
-#pragma unroll
-                            for (int q = 0; q < 32; ++q)
-                                if (col0 + q < g.N) dst[q] = __uint_as_float(r[q]);
-                        }
-                    }
-                    continue;
-                }
-                uint8_t* stage_buf = smem + L::OUT_OFFSET + (half * 2 + (oc & 1)) * L::OUT_BYTES;
-                if (oc >= 2 && (int)threadIdx.x == issuer) tma_store_wait_read<1>();
-                ++oc;
-                named_barrier(1 + half, 128);
-                const int r_in_tile = quarter * 32 + lane;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float lo = __uint_as_float(r[8 * q + 2 * e]), hi = __uint_as_float(r[8 * q + 2 * e + 1]);
-                        if (g.out_bf16) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
-                        else { __half2 v = __floats2half2_rn(lo, hi); w[e] = *reinterpret_cast<uint32_t*>(&v); }
-                    }
-                    const int chunk = q ^ ((r_in_tile >> 1) & 3);
-                    *reinterpret_cast<uint4*>(stage_buf + r_in_tile * 64 + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-                }
-                fence_async_smem();
-                named_barrier(1 + half, 128);
-                if ((int)threadIdx.x == issuer) {
-                    tma_store_2d(&tmD, stage_buf, n0 + c * 32, m0);
-                    tma_store_commit();
-                }
-                if (g.stats != nullptr) {
-                    const int cp = lane & 15, hi = lane >> 4;
-                    float s1a = 0.f, s1b = 0.f, s2a = 0.f, s2b = 0.f;
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int rr = quarter * 32 + hi * 16 + ((i + hi) & 15);
-                        const int chunk = (cp >> 2) ^ ((rr >> 1) & 3);
-                        const uint32_t w = *reinterpret_cast<const uint32_t*>(stage_buf + rr * 64 + chunk * 16 + (cp & 3) * 4);
-                        float lo, up;
-                        if (g.out_bf16) { lo = __uint_as_float(w << 16); up = __uint_as_float(w & 0xffff0000u); }
-                        else { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w)); lo = f.x; up = f.y; }
-                        s1a += lo; s1b += up; s2a = fmaf(lo, lo, s2a); s2b = fmaf(up, up, s2b);
-                    }
-                    s1a += __shfl_xor_sync(0xffffffffu, s1a, 16); s1b += __shfl_xor_sync(0xffffffffu, s1b, 16);
-                    s2a += __shfl_xor_sync(0xffffffffu, s2a, 16); s2b += __shfl_xor_sync(0xffffffffu, s2b, 16);
-                    const int col = n0 + c * 32 + cp * 2;
-                    if (hi == 0 && col < g.N) {
-                        float* dst = g.stats + ((size_t)((m0 / BM) * 4 + quarter) * 2) * g.N + col;
-                        *reinterpret_cast<float2*>(dst) = make_float2(s1a, s1b);
-                        *reinterpret_cast<float2*>(dst + g.N) = make_float2(s2a, s2b);
-                    }
-                }
-            }
+            drain_accumulator<BN / 64, 0>(taddr, half * (BN / 64), m0, n0, split, quarter, lane, Dptr, g, ConvGeom{}, alpha, &tmD,
+                                          smem + L::OUT_OFFSET + (warp - 2) * 2 * kWarpStageBytes, oc);
             fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty_first + acc * 8);      // the MMA thread lives in the first CTA
         }
-        if ((int)threadIdx.x == issuer) tma_store_wait_all<0>();
+        if (lane == 0) tma_store_wait_all<0>();
     }
 
     // -------------------------------------------------------------------- teardown

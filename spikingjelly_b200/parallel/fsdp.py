@@ -1,6 +1,6 @@
-"""FSDP2 (``torch.distributed.fsdp.fully_shard``) applied to chosen roots of an SNN.  Parameter
-sharding is not on a hot path the package owns kernels for, so torch's implementation over NCCL is
-used as is.  Parity: ``spikingjelly/activation_based/distributed/fsdp.py:13-105``."""
+"""FSDP2 (``torch.distributed.fsdp.fully_shard``) over chosen sub-trees of an SNN
+(``spikingjelly/activation_based/distributed/fsdp.py:13-105``).  Parameter sharding is not a path this package owns
+kernels for: torch's implementation over NCCL is used as it is, this module only decides what gets wrapped."""
 from __future__ import annotations
 
 from typing import Optional, Sequence
@@ -8,44 +8,43 @@ from typing import Optional, Sequence
 import torch
 import torch.nn as nn
 
-from .mesh import _resolve_mesh_submesh
+from .mesh import MeshView
 
 try:
     from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
-    FSDP2_AVAILABLE = True
 except ImportError:                                       # pragma: no cover
-    MixedPrecisionPolicy = None
-    fully_shard = None
-    FSDP2_AVAILABLE = False
+    MixedPrecisionPolicy = fully_shard = None
+FSDP2_AVAILABLE = fully_shard is not None
 
 __all__ = ["FSDP2_AVAILABLE", "fully_shard_snn_module", "apply_snn_fsdp2"]
 
 
 def _build_fsdp_mp_policy(param_dtype, reduce_dtype, output_dtype):
-    if MixedPrecisionPolicy is None or (param_dtype is None and reduce_dtype is None and output_dtype is None):
+    """A ``MixedPrecisionPolicy`` when any dtype is given, else ``None`` (FSDP2's default)."""
+    asked = any(d is not None for d in (param_dtype, reduce_dtype, output_dtype))
+    if not asked or MixedPrecisionPolicy is None:
         return None
     return MixedPrecisionPolicy(param_dtype=param_dtype, reduce_dtype=reduce_dtype, output_dtype=output_dtype)
 
 
 def fully_shard_snn_module(module: nn.Module, device_mesh, shard_roots: Optional[Sequence[str]] = None,
                            shard_module_root: bool = True, root_reshard_after_forward: Optional[bool] = False, mp_policy=None) -> nn.Module:
-    """``fully_shard`` every module path in ``shard_roots`` (``""`` = the model itself), then the model
-    (unless ``shard_module_root`` is false).  The root keeps its parameters gathered after forward by
-    default: an SNN's backward starts right away."""
+    """Wrap each path of ``shard_roots`` as its own FSDP unit, then the model itself unless ``shard_module_root`` is false
+    (``""`` among the roots also asks for the model).  The outermost unit keeps its parameters gathered after forward by
+    default, because an SNN's backward starts at once and would only gather them again."""
     if not FSDP2_AVAILABLE:
-        raise RuntimeError("FSDP2 fully_shard is unavailable in the current PyTorch build.")
-    named = dict(module.named_modules())
-    extra = {} if mp_policy is None else {"mp_policy": mp_policy}
-    root_listed = False
-    for name in list(shard_roots or []):
-        if name not in named:
-            raise KeyError(f"Unknown FSDP shard root '{name}'.")
-        if name == "":
-            root_listed = True
-            continue
-        fully_shard(named[name], mesh=device_mesh, **extra)
-    if shard_module_root or root_listed:
-        fully_shard(module, mesh=device_mesh, reshard_after_forward=root_reshard_after_forward, **extra)
+        raise RuntimeError("this PyTorch build has no torch.distributed.fsdp.fully_shard")
+    by_path = dict(module.named_modules())
+    wanted = list(shard_roots or ())
+    missing = [p for p in wanted if p not in by_path]
+    if missing:
+        raise KeyError(f"fsdp shard roots not found in the model: {missing}")
+    options = {} if mp_policy is None else {"mp_policy": mp_policy}
+    for path in wanted:
+        if path:
+            fully_shard(by_path[path], mesh=device_mesh, **options)
+    if shard_module_root or "" in wanted:
+        fully_shard(module, mesh=device_mesh, reshard_after_forward=root_reshard_after_forward, **options)
     return module
 
 
@@ -53,6 +52,7 @@ def apply_snn_fsdp2(module: nn.Module, device_mesh, dp_mesh_dim: Optional[int] =
                     shard_module_root: bool = True, root_reshard_after_forward: Optional[bool] = False,
                     param_dtype: Optional[torch.dtype] = None, reduce_dtype: Optional[torch.dtype] = None,
                     output_dtype: Optional[torch.dtype] = None) -> nn.Module:
-    mesh = _resolve_mesh_submesh(device_mesh, dp_mesh_dim if dp_mesh_dim is not None else 0)
-    return fully_shard_snn_module(module, mesh, shard_roots, shard_module_root, root_reshard_after_forward,
-                                  _build_fsdp_mp_policy(param_dtype, reduce_dtype, output_dtype))
+    """:func:`fully_shard_snn_module` over the data-parallel axis of ``device_mesh`` (axis 0 unless told otherwise)."""
+    axis_mesh = MeshView(device_mesh).axis_submesh(0 if dp_mesh_dim is None else dp_mesh_dim)
+    policy = _build_fsdp_mp_policy(param_dtype, reduce_dtype, output_dtype)
+    return fully_shard_snn_module(module, axis_mesh, shard_roots, shard_module_root, root_reshard_after_forward, policy)

@@ -1,5 +1,5 @@
-"""Classification outputs of a (possibly sharded) model: mean over time, label normalisation and
-materialisation of sharded outputs.  Parity: ``spikingjelly/activation_based/distributed/metrics.py:10-46``."""
+"""Bring the output of a (possibly sharded) classifier and its labels into the form a loss expects
+(``spikingjelly/activation_based/distributed/metrics.py:10-46``): firing rate over time, class indices, full logits."""
 from __future__ import annotations
 
 from typing import NamedTuple
@@ -17,25 +17,27 @@ class PreparedModelOutput(NamedTuple):
     materialized: bool
 
 
-def _labels(target: torch.Tensor) -> torch.Tensor:
-    while target.ndim > 1 and target.shape[-1] == 1:
-        target = target.squeeze(-1)
-    if target.ndim > 1:                                   # one-hot / soft labels
-        target = target.argmax(dim=-1)
-        while target.ndim > 1 and target.shape[-1] == 1:
-            target = target.squeeze(-1)
-    return target
+def _class_indices(target: torch.Tensor) -> torch.Tensor:
+    """``[B]`` class indices from ``[B]``, ``[B, 1]`` (any number of trailing ones) or one-hot / soft ``[B, C]`` labels."""
+    def drop_trailing_ones(t):
+        while t.ndim > 1 and t.shape[-1] == 1:
+            t = t.squeeze(-1)
+        return t
+    target = drop_trailing_ones(target)
+    return drop_trailing_ones(target.argmax(dim=-1)) if target.ndim > 1 else target
 
 
 def prepare_classification_output(output, target: torch.Tensor, *, require_full_logits: bool = True) -> PreparedModelOutput:
-    if output.ndim >= 3:
-        output = output.mean(dim=0)                       # [T, B, C] -> rate
-    target = _labels(target)
-    dev = getattr(output, "device", None)
-    if dev is not None and target.device != dev:
-        target = target.to(device=dev)
-    materialized = False
+    """``output``: ``[T, B, C]`` (averaged over ``T``) or ``[B, C]``.  With ``require_full_logits`` a sharded output is
+    gathered; ``materialized`` reports whether that happened."""
+    logits = output.mean(dim=0) if output.ndim >= 3 else output
+    labels = _class_indices(target)
+    where = getattr(logits, "device", None)
+    if where is not None and labels.device != where:
+        labels = labels.to(where)
+    gathered = False
     if require_full_logits:
-        full = materialize_dtensor_output(output)
-        materialized, output = full is not output, full
-    return PreparedModelOutput(output, target, materialized)
+        whole = materialize_dtensor_output(logits)
+        gathered = whole is not logits
+        logits = whole
+    return PreparedModelOutput(logits, labels, gathered)

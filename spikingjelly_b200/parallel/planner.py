@@ -1,11 +1,16 @@
-"""Strategy recommendation and the immutable execution plan of Analyze -> Plan -> Apply.
-Parity: ``spikingjelly/activation_based/distributed/planner.py:56-490``."""
+"""Strategy recommendation and the frozen execution plan of Analyze -> Plan -> Apply.
+
+Public names follow ``spikingjelly/activation_based/distributed/planner.py:60-110,257-490``.  The recommender is a rule
+table: for each preference an ordered list of ``(applies?, build)`` pairs evaluated against one :class:`_Situation`; the
+first rule that applies wins, and every rule records why it was taken or passed over."""
 from __future__ import annotations
 
-from dataclasses import dataclass, replace
+import importlib
+from dataclasses import dataclass, field, replace
 from types import MappingProxyType
-from typing import Any, List, Mapping, Optional, Tuple, Union
+from typing import Any, Callable, Dict, List, Mapping, Optional, Sequence, Tuple, Union
 
+from . import _schema
 from .topology import SNNDistributedTopology
 
 __all__ = ["SNN_DISTRIBUTED_PREFERENCES", "DistributedFeatureSet", "SNNDistributedPlan", "SNNDistributedRecommendation",
@@ -16,21 +21,23 @@ TensorParallelStyle = Union[str, Any]
 SNN_DISTRIBUTED_PREFERENCES = ("speed", "memory", "capacity")
 
 
-def _has(path: str, name: str) -> bool:
+def _importable(module: str, attribute: str) -> bool:
     try:
-        return hasattr(__import__(path, fromlist=[name]), name)
+        return hasattr(importlib.import_module(module), attribute)
     except ImportError:
         return False
 
 
-FSDP2_AVAILABLE = _has("torch.distributed.fsdp", "fully_shard")
-ZERO_REDUNDANCY_OPTIMIZER_AVAILABLE = _has("torch.distributed.optim", "ZeroRedundancyOptimizer")
-PIPELINING_AVAILABLE = _has("torch.distributed.pipelining", "PipelineStage")
-TENSOR_PARALLEL_AVAILABLE = True          # tensor parallelism is implemented on plain process groups in this package
+FSDP2_AVAILABLE = _importable("torch.distributed.fsdp", "fully_shard")
+ZERO_REDUNDANCY_OPTIMIZER_AVAILABLE = _importable("torch.distributed.optim", "ZeroRedundancyOptimizer")
+PIPELINING_AVAILABLE = _importable("torch.distributed.pipelining", "PipelineStage")
+#: tensor parallelism here runs on plain process groups and needs nothing optional
+TENSOR_PARALLEL_AVAILABLE = True
 
 
 @dataclass(frozen=True)
 class DistributedFeatureSet:
+    """Opt-ins that ``plan()`` / ``apply()`` honour."""
     allow_experimental_conv_tp: bool = False
     allow_experimental_spikformer_tp: bool = False
     allow_zero_optimizer: bool = True
@@ -38,8 +45,7 @@ class DistributedFeatureSet:
 
 @dataclass(frozen=True)
 class SNNDistributedPlan:
-    """The decision of ``plan()``.  ``tensor_parallel_plan`` (module path -> style) is frozen on
-    construction; its keys must be candidates found by the analysis."""
+    """What ``plan()`` decided.  ``tensor_parallel_plan`` (module path -> style) becomes read-only on construction."""
     mode: str
     objective: str
     topology: SNNDistributedTopology
@@ -64,13 +70,12 @@ class SNNDistributedPlan:
 
     @property
     def tp_mesh_dim(self) -> int:
-        names = self.topology.ordered_dim_names
-        return names.index("tp") if "tp" in names else 0
+        at = self.topology.axis("tp")
+        return 0 if at is None else at
 
     @property
     def dp_mesh_dim(self) -> Optional[int]:
-        names = self.topology.ordered_dim_names
-        return names.index("dp") if "dp" in names else None
+        return self.topology.axis("dp")
 
 
 @dataclass(frozen=True)
@@ -94,89 +99,123 @@ class SNNDistributedRecommendation:
 
 
 def recommended_pipeline_microbatches(batch_size: int, num_stages: int) -> int:
-    """Largest divisor of ``batch_size`` in ``[num_stages, min(batch_size, 4 * num_stages)]``."""
-    if batch_size <= 0:
-        raise ValueError(f"batch_size must be positive, but got {batch_size}.")
-    if num_stages <= 0:
-        raise ValueError(f"num_stages must be positive, but got {num_stages}.")
-    if batch_size < num_stages:
-        raise ValueError(f"batch_size ({batch_size}) must be >= num_stages ({num_stages}) for pipeline parallelism with the "
-                         "current microbatch splitting implementation.")
-    target = min(batch_size, num_stages * 4)
-    for candidate in range(target, num_stages - 1, -1):
-        if batch_size % candidate == 0:
-            return candidate
-    raise ValueError(f"batch_size ({batch_size}) must be divisible by at least one microbatch count in [{num_stages}, {target}] "
-                     "for pipeline parallelism.")
+    """The largest micro-batch count between ``num_stages`` and ``4 * num_stages`` (at most ``batch_size``) that divides
+    the batch: enough micro-batches to fill the pipeline, equal sizes so that no stage sees a ragged one."""
+    batch = _schema.positive(batch_size, "batch_size")
+    stages = _schema.positive(num_stages, "num_stages")
+    if batch < stages:
+        raise ValueError(f"batch_size: {batch} samples cannot feed {stages} pipeline stages (one micro-batch per stage is the minimum)")
+    ceiling = min(batch, 4 * stages)
+    fitting = [m for m in range(stages, ceiling + 1) if batch % m == 0]
+    if not fitting:
+        raise ValueError(f"batch_size: {batch} has no divisor between {stages} and {ceiling}, so it cannot be cut into equal micro-batches")
+    return fitting[-1]
 
 
-def _two_d_mesh(world_size: int) -> Optional[Tuple[int, int]]:
-    return None if world_size < 4 or world_size % 2 else (world_size // 2, 2)
+# ----------------------------------------------------------------------------------------------- rule table
+@dataclass
+class _Situation:
+    family: str
+    model: str
+    world: int
+    batch: int
+    backend: str
+    zero: bool
+    pipe: bool
+    fsdp: bool
+    tp: bool
+    why: List[str] = field(default_factory=list)
+
+    @property
+    def grid(self) -> Optional[Tuple[int, int]]:
+        """(replicas, 2) when the ranks split into a two-axis mesh, else None."""
+        return (self.world // 2, 2) if self.world >= 4 and self.world % 2 == 0 else None
+
+    @property
+    def zero_or_none(self) -> str:
+        return "zero" if self.zero else "none"
+
+    def virtual_stages(self) -> int:
+        """Pipeline stages per rank the batch can feed: 2 (interleaved), 1, or 0 (no pipeline possible)."""
+        if self.batch >= 2 * self.world:
+            return 2
+        return 1 if self.batch >= self.world else 0
+
+
+_Fields = Dict[str, Any]
+_Rule = Tuple[Callable[[_Situation], bool], Callable[[_Situation], _Fields], str]
+
+
+def _hybrid(memopt: int) -> Callable[[_Situation], _Fields]:
+    return lambda s: dict(mode="fsdp2_tp", memopt_level=memopt, mesh_shape=s.grid, tp_mesh_dim=1, dp_mesh_dim=0)
+
+
+def _pipeline(s: _Situation) -> _Fields:
+    v = s.virtual_stages()
+    return dict(mode="pp", memopt_level=1, pp_virtual_stages=v, pp_schedule="interleaved" if v > 1 else "1f1b",
+                pp_microbatches=recommended_pipeline_microbatches(s.batch, s.world * v), pp_memopt_stage_budget_ratio=0.5)
+
+
+_MEMORY_RULES: Sequence[_Rule] = (
+    (lambda s: s.fsdp and s.tp and s.grid is not None, _hybrid(1),
+     "parameters sharded over one mesh axis (FSDP2) and activations over the other (tensor parallel), plus input-compressed "
+     "checkpointing (memopt level 1): the largest saving available"),
+    (lambda s: s.tp, lambda s: dict(mode="tp", memopt_level=1, mesh_shape=(s.world,)),
+     "no two-axis mesh possible here, so tensor parallelism alone with memopt level 1"),
+    (lambda s: s.fsdp, lambda s: dict(mode="fsdp2", memopt_level=1, dp_mesh_dim=0),
+     "tensor parallelism unavailable: FSDP2 with memopt level 1"),
+    (lambda s: True, lambda s: dict(mode="dp", memopt_level=1, dp_mesh_dim=0, optimizer_sharding=s.zero_or_none),
+     "neither tensor parallelism nor FSDP2 available: data parallel with memopt level 1"),
+)
+
+_RULES: Dict[str, Sequence[_Rule]] = {
+    "speed": (
+        (lambda s: s.family == "cifar10dvs_vgg" and s.fsdp and s.tp and s.grid is not None, _hybrid(0),
+         "the CIFAR10-DVS VGG measured fastest as FSDP2 x tensor parallel on several GPUs"),
+        (lambda s: True, lambda s: dict(mode="dp", dp_mesh_dim=0, optimizer_sharding=s.zero_or_none),
+         "data parallel is the shortest path to throughput; optimizer state is sharded (ZeRO-1) where torch offers it"),
+    ),
+    "memory": _MEMORY_RULES,
+    "capacity": (
+        (lambda s: s.pipe and s.virtual_stages() > 0, _pipeline,
+         "pipeline parallel with memopt level 1 fits the largest model; two virtual stages per rank (interleaved) when the batch "
+         "can feed them"),
+    ) + tuple(_MEMORY_RULES),
+}
+
+_PASSED_OVER = {
+    "capacity": lambda s: ("pipeline parallelism is not available in this PyTorch build" if not s.pipe else
+                           f"a batch of {s.batch} cannot feed {s.world} pipeline stages") + "; falling back to the memory rules",
+}
 
 
 def recommend_snn_distributed_strategy(model: str, world_size: int, prefer: str, batch_size: int, backend: str = "inductor",
                                        zero_redundancy_optimizer_available: Optional[bool] = None,
                                        pipelining_available: Optional[bool] = None, fsdp2_available: Optional[bool] = None,
                                        tensor_parallel_available: Optional[bool] = None) -> SNNDistributedRecommendation:
-    """speed -> data parallel (+ZeRO) (FSDP2 x TP for the CIFAR10-DVS VGG); memory -> FSDP2 x TP, TP,
-    FSDP2 or DP with memopt level 1; capacity -> pipeline parallel when the batch allows it, else the
-    memory strategy.  One rank -> no parallelism."""
-    prefer = prefer.lower()
-    if prefer not in SNN_DISTRIBUTED_PREFERENCES:
-        raise ValueError(f"Unsupported prefer='{prefer}'. Expected one of {SNN_DISTRIBUTED_PREFERENCES}.")
-    zero = ZERO_REDUNDANCY_OPTIMIZER_AVAILABLE if zero_redundancy_optimizer_available is None else zero_redundancy_optimizer_available
-    pipe = PIPELINING_AVAILABLE if pipelining_available is None else pipelining_available
-    fsdp = FSDP2_AVAILABLE if fsdp2_available is None else fsdp2_available
-    tp = TENSOR_PARALLEL_AVAILABLE if tensor_parallel_available is None else tensor_parallel_available
-    family = "spikformer" if model.startswith("spikformer") else model
-    why: List[str] = [f"prefer='{prefer}' with model='{family}', world_size={world_size}, backend='{backend}'."]
+    """``speed``: data parallel (+ ZeRO-1), or FSDP2 x TP for the CIFAR10-DVS VGG.  ``memory``: FSDP2 x TP, else TP, else
+    FSDP2, else DP — each with memopt level 1.  ``capacity``: pipeline parallel if the batch can feed the stages, else the
+    memory rules.  A single rank always trains locally.  The ``*_available`` arguments override what was detected at import."""
+    prefer = _schema.one_of(prefer, SNN_DISTRIBUTED_PREFERENCES, "prefer")
 
-    def result(mode: str, **kw) -> SNNDistributedRecommendation:
-        return SNNDistributedRecommendation(prefer=prefer, model=model, world_size=world_size, mode=mode, rationale=tuple(why), **kw)
+    def given(value: Optional[bool], detected: bool) -> bool:
+        return detected if value is None else bool(value)
 
-    if world_size <= 1:
-        why.append("Single-rank run keeps the simplest local path with no distributed overhead." if prefer == "speed"
-                   else "Single-rank run falls back to local training and uses memopt for memory savings.")
-        return result("none", memopt_level=0 if prefer == "speed" else 1)
-
-    if prefer == "speed":
-        mesh = _two_d_mesh(world_size)
-        if family == "cifar10dvs_vgg" and fsdp and tp and mesh is not None:
-            why.append("Use fsdp2_tp on multi-GPU CIFAR10DVSVGG because benchmarks show the best global throughput there.")
-            return result("fsdp2_tp", mesh_shape=mesh, tp_mesh_dim=1, dp_mesh_dim=0)
-        why.append("Use data parallel training for the simplest throughput-oriented path, enabling ZeRO optimizer state "
-                   "sharding when available.")
-        return result("dp", optimizer_sharding="zero" if zero else "none", dp_mesh_dim=0)
-
-    if prefer == "memory":
-        mesh = _two_d_mesh(world_size)
-        if fsdp and tp and mesh is not None:
-            why.append("Combine FSDP2 and TP to shard both parameters and activations, and enable memopt level 1 for the "
-                       "strongest memory reduction.")
-            return result("fsdp2_tp", memopt_level=1, mesh_shape=mesh, tp_mesh_dim=1, dp_mesh_dim=0)
-        if tp:
-            why.append("Use tensor parallel with memopt level 1 when two-dimensional FSDP2+TP is unavailable.")
-            return result("tp", memopt_level=1, mesh_shape=(world_size,))
-        if fsdp:
-            why.append("Fall back to FSDP2 with memopt level 1 when TP is unavailable.")
-            return result("fsdp2", memopt_level=1, dp_mesh_dim=0)
-        why.append("Fall back to DP + memopt level 1 because TP/FSDP2 are unavailable.")
-        return result("dp", optimizer_sharding="zero" if zero else "none", memopt_level=1, dp_mesh_dim=0)
-
-    # capacity
-    if pipe:
-        virtual = 2 if (batch_size >= world_size * 2 and world_size >= 2) else (1 if batch_size >= world_size else 0)
-        if virtual == 0:
-            why.append("Pipeline parallelism is skipped because the global batch is smaller than the number of physical stages.")
-        else:
-            why.append("Use pipeline parallelism with memopt level 1 when capacity is the priority; prefer the interleaved "
-                       "schedule when several virtual stages per rank are possible.")
-            return result("pp", memopt_level=1, pp_microbatches=recommended_pipeline_microbatches(batch_size, world_size * virtual),
-                          pp_memopt_stage_budget_ratio=0.5, pp_schedule="interleaved" if virtual > 1 else "1f1b",
-                          pp_virtual_stages=virtual)
-        why.append("Pipeline parallelism is infeasible for this batch size, so capacity preference falls back to the strongest "
-                   "memory-oriented strategy.")
+    s = _Situation(family="spikformer" if model.startswith("spikformer") else model, model=model, world=int(world_size),
+                   batch=int(batch_size), backend=backend, zero=given(zero_redundancy_optimizer_available, ZERO_REDUNDANCY_OPTIMIZER_AVAILABLE),
+                   pipe=given(pipelining_available, PIPELINING_AVAILABLE), fsdp=given(fsdp2_available, FSDP2_AVAILABLE),
+                   tp=given(tensor_parallel_available, TENSOR_PARALLEL_AVAILABLE))
+    s.why.append(f"asked for {prefer!r}: model family {s.family!r}, {s.world} rank(s), batch {s.batch}, backend {backend!r}")
+    if s.world <= 1:
+        local_memopt = 0 if prefer == "speed" else 1
+        s.why.append("one rank: local training" + ("" if local_memopt == 0 else " with memopt level 1 for the memory saving"))
+        fields: _Fields = dict(mode="none", memopt_level=local_memopt)
     else:
-        why.append("Pipeline APIs are unavailable, so capacity preference falls back to the strongest memory-oriented strategy.")
-    fb = recommend_snn_distributed_strategy(model, world_size, "memory", batch_size, backend, zero, False, fsdp, tp)
-    return replace(fb, prefer=prefer, rationale=tuple(why + list(fb.rationale[1:])))
+        rules = _RULES[prefer]
+        chosen = next(i for i, (applies, _, _) in enumerate(rules) if applies(s))
+        if chosen > 0 and prefer in _PASSED_OVER:
+            s.why.append(_PASSED_OVER[prefer](s))
+        _, build, reason = rules[chosen]
+        s.why.append(reason)
+        fields = build(s)
+    return SNNDistributedRecommendation(prefer=prefer, model=model, world_size=s.world, rationale=tuple(s.why), **fields)

@@ -1,6 +1,5 @@
-"""``SNNDistributedRuntime``: what ``apply()`` returns — configured model, mesh, analysis and plan, with
-helpers for the optimizer, state reset, classification outputs and data loading.
-Parity: ``spikingjelly/activation_based/distributed/runtime.py:22-160``."""
+"""``SNNDistributedRuntime``: what ``apply()`` hands back — the configured model with its mesh, analysis and plan, and the
+few things a training loop needs from them (``spikingjelly/activation_based/distributed/runtime.py:22-160``)."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -22,6 +21,8 @@ from .planner import SNNDistributedPlan
 
 __all__ = ["SNNDistributedRuntime"]
 
+_BATCH_SHARDING_MODES = ("dp", "fsdp2", "fsdp2_tp")
+
 
 @dataclass
 class SNNDistributedRuntime:
@@ -30,45 +31,50 @@ class SNNDistributedRuntime:
     analysis: Optional[SNNDistributedAnalysis]
     plan: SNNDistributedPlan
 
+    # ------------------------------------------------------------------ optimizer and state
     def build_optimizer(self, optimizer_cls=torch.optim.Adam, lr: float = 1e-3, weight_decay: float = 0.0, **kwargs):
-        return build_snn_optimizer(self.model, mode=self.plan.mode, optimizer_cls=optimizer_cls, lr=lr, weight_decay=weight_decay,
-                                   optimizer_sharding=self.plan.optimizer_strategy, **kwargs)
+        """The plan's optimizer strategy (ZeRO-1 or plain) applied to ``optimizer_cls``."""
+        return build_snn_optimizer(self.model, self.plan.mode, lr, weight_decay, self.plan.optimizer_strategy,
+                                   optimizer_cls=optimizer_cls, **kwargs)
 
-    def reset_state(self):
-        """Reset every stateful module (call once per batch, after the optimizer step)."""
+    def reset_state(self) -> None:
+        """Put every stateful module back to its initial state; once per batch, after the optimizer step."""
         functional.reset_net(self.model)
 
+    # ------------------------------------------------------------------ outputs
     @staticmethod
     def reduce_classification_output(outputs: torch.Tensor, labels: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-        p = prepare_classification_output(outputs, labels, require_full_logits=False)
-        return p.logits, p.target
+        """Rate over time and class indices, leaving a sharded output sharded."""
+        prepared = prepare_classification_output(outputs, labels, require_full_logits=False)
+        return prepared.logits, prepared.target
 
     def prepare_classification_output(self, outputs, labels: torch.Tensor, *, return_metadata: bool = False):
-        p = prepare_classification_output(outputs, labels, require_full_logits=True)
-        return p if return_metadata else (p.logits, p.target)
+        """Rate over time, class indices and full (gathered) logits; ``return_metadata`` returns the named tuple that also
+        says whether a gather took place."""
+        prepared: PreparedModelOutput = prepare_classification_output(outputs, labels, require_full_logits=True)
+        return prepared if return_metadata else (prepared.logits, prepared.target)
 
     def forward_loss(self, criterion, images: torch.Tensor, labels: torch.Tensor):
-        try:
-            ref = next(self.model.parameters())
-            dtype, device = ref.dtype, ref.device
-        except StopIteration:
-            dtype, device = torch.float32, torch.device("cpu")
-        outputs, labels = self.prepare_classification_output(self.model(images.to(device=device, dtype=dtype)), labels)
-        return outputs, labels, criterion(outputs, labels)
+        """``(logits, labels, criterion(logits, labels))`` with the images moved to the model's device and dtype."""
+        first = next(self.model.parameters(), None)
+        if first is not None:
+            images = images.to(device=first.device, dtype=first.dtype)
+        logits, labels = self.prepare_classification_output(self.model(images), labels)
+        return logits, labels, criterion(logits, labels)
 
+    # ------------------------------------------------------------------ data
     def prepare_dataloader(self, *, dataset, batch_size: int, shuffle: bool, num_workers: int, drop_last: bool,
                            pin_memory: bool = True) -> DataLoader:
-        """A ``DistributedSampler`` over the data-parallel replicas only (tensor-parallel ranks of one
-        replica must see the same samples)."""
-        sampler, replicas, rank = None, 1, 0
+        """A loader whose sampler splits the data over the REPLICAS of the model only: ranks that share a replica through
+        tensor parallelism must be fed identical samples."""
+        sampler = None
+        replicas, index = 1, 0
         if dist.is_initialized():
-            replicas, rank = resolve_data_parallel_partition(self.mesh, dp_mesh_dim=self.plan.dp_mesh_dim,
-                                                             sharded_by_data_parallel=self.plan.mode in ("dp", "fsdp2", "fsdp2_tp"))
-            if replicas > 1:
-                sampler = DistributedSampler(dataset, num_replicas=replicas, rank=rank, shuffle=shuffle)
-        loader = DataLoader(dataset, batch_size=batch_size, sampler=sampler, shuffle=shuffle if sampler is None else False,
+            replicas, index = resolve_data_parallel_partition(self.mesh, self.plan.dp_mesh_dim, self.plan.mode in _BATCH_SHARDING_MODES)
+        if replicas > 1:
+            sampler = DistributedSampler(dataset, num_replicas=replicas, rank=index, shuffle=shuffle)
+        loader = DataLoader(dataset, batch_size=batch_size, sampler=sampler, shuffle=shuffle and sampler is None,
                             num_workers=num_workers, pin_memory=pin_memory, drop_last=drop_last)
-        logger.info("distributed_dataloader_prepared dataset=%s batch_size=%s num_workers=%s sampler=%s replicas=%s rank=%s "
-                    "drop_last=%s pin_memory=%s", type(dataset).__name__, batch_size, num_workers,
-                    type(sampler).__name__ if sampler is not None else None, replicas, rank, drop_last, pin_memory)
+        logger.info("data loader: %s, batch %d, replica %d of %d, %d worker(s)", type(dataset).__name__, batch_size, index, replicas,
+                    num_workers)
         return loader

@@ -1,24 +1,21 @@
-"""Logical rank grid: named dimensions whose sizes multiply to the world size.
-Parity: ``spikingjelly/activation_based/distributed/topology.py:20-87``."""
+"""The logical rank grid of a job: named axes (``dp``, ``tp``, ...) whose sizes multiply to the world size.
+
+Same role and public surface as ``spikingjelly/activation_based/distributed/topology.py:20-87`` (``world_size``, ``dims``,
+``ordered_dim_names``, ``mesh_shape``, ``from_mapping``), plus :meth:`SNNDistributedTopology.axis` /
+:meth:`SNNDistributedTopology.has` used by the planner."""
 from __future__ import annotations
 
 from dataclasses import dataclass
 from math import prod
-from numbers import Integral
 from types import MappingProxyType
 from typing import Mapping, Optional, Tuple
 
+from . import _schema
+
 __all__ = ["SNNDistributedTopology"]
 
-
-def _as_integer(value, name: str) -> int:
-    if isinstance(value, bool):
-        raise TypeError(f"{name} must be an integer, but got bool.")
-    if isinstance(value, Integral):
-        return int(value)
-    if isinstance(value, float) and value.is_integer():
-        return int(value)
-    raise TypeError(f"{name} must be an integer, but got {type(value).__name__}.")
+#: axes with a conventional position in the device mesh; any other axis follows in the order it was given
+CANONICAL_AXES = ("dp", "tp", "pp", "vpp")
 
 
 @dataclass(frozen=True)
@@ -27,38 +24,44 @@ class SNNDistributedTopology:
     dims: Mapping[str, int]
 
     def __post_init__(self):
-        dims = MappingProxyType(dict(self.dims))
-        object.__setattr__(self, "dims", dims)
-        if not isinstance(self.world_size, Integral) or isinstance(self.world_size, bool):
-            raise TypeError(f"world_size must be an integer, but got {type(self.world_size).__name__}.")
-        if self.world_size <= 0:
-            raise ValueError(f"world_size must be positive, but got {self.world_size}.")
-        if not dims:
-            raise ValueError("dims must not be empty.")
-        for name, size in dims.items():
-            if not isinstance(name, str):
-                raise TypeError(f"Topology dimension names must be strings, but got {type(name).__name__}.")
-            if not name:
-                raise ValueError("Topology dimension names must be non-empty.")
-            if not isinstance(size, Integral) or isinstance(size, bool):
-                raise TypeError(f"Topology dimension '{name}' must be an integer, but got {type(size).__name__}.")
-            if size <= 0:
-                raise ValueError(f"Topology dimension '{name}' must be positive, but got {size}.")
-        if prod(dims.values()) != self.world_size:
-            raise ValueError(f"Topology dims {dict(dims)} multiply to {prod(dims.values())}, but world_size={self.world_size}.")
+        world = _schema.positive(self.world_size, "world_size")
+        if len(self.dims) == 0:
+            raise ValueError("dims: a topology needs at least one axis, e.g. {'dp': 8}")
+        sizes = {}
+        for axis, size in self.dims.items():
+            if not isinstance(axis, str) or not axis:
+                raise (TypeError if not isinstance(axis, str) else ValueError)(f"dims: axis names are non-empty strings, got {axis!r}")
+            if isinstance(size, float):
+                raise TypeError(f"dims[{axis!r}]: expected an integer, got float")
+            sizes[axis] = _schema.positive(size, f"dims[{axis!r}]")
+        volume = prod(sizes.values())
+        if volume != world:
+            raise ValueError(f"dims: the axes {sizes} multiply to {volume}, which is not world_size = {world}")
+        object.__setattr__(self, "world_size", world)
+        object.__setattr__(self, "dims", MappingProxyType(sizes))
+
+    # ------------------------------------------------------------------ queries
+    def has(self, *axes: str) -> bool:
+        return all(a in self.dims for a in axes)
+
+    def axis(self, name: str) -> Optional[int]:
+        """Position of ``name`` in the mesh, or ``None`` when the topology has no such axis."""
+        order = self.ordered_dim_names
+        return order.index(name) if name in order else None
 
     @property
     def ordered_dim_names(self) -> Tuple[str, ...]:
-        """dp, tp, pp, vpp first (in that order), then any other names in insertion order."""
-        first = [n for n in ("dp", "tp", "pp", "vpp") if n in self.dims]
-        return tuple(first + [n for n in self.dims if n not in first])
+        head = tuple(a for a in CANONICAL_AXES if a in self.dims)
+        return head + tuple(a for a in self.dims if a not in CANONICAL_AXES)
 
     @property
     def mesh_shape(self) -> Tuple[int, ...]:
-        return tuple(int(self.dims[n]) for n in self.ordered_dim_names)
+        return tuple(self.dims[a] for a in self.ordered_dim_names)
 
+    # ------------------------------------------------------------------ construction
     @classmethod
     def from_mapping(cls, dims: Mapping[str, int], *, world_size: Optional[int] = None) -> "SNNDistributedTopology":
-        norm = {k: _as_integer(v, f"Topology dimension '{k}'") for k, v in dims.items()}
-        ws = prod(norm.values()) if world_size is None else _as_integer(world_size, "world_size")
-        return cls(world_size=ws, dims=norm)
+        """Build from ``{"dp": 4, "tp": 2}``; integral floats are accepted here, ``world_size`` defaults to the product."""
+        sizes = {axis: _schema.whole_number(size, f"dims[{axis!r}]") for axis, size in dims.items()}
+        world = prod(sizes.values()) if world_size is None else _schema.whole_number(world_size, "world_size")
+        return cls(world_size=world, dims=sizes)

@@ -62,7 +62,7 @@ def test_analysis_and_planning_rules():
     p = D.plan(analysis=a, objective="speed", topology={"dp": 2}, backend="cuda", batch_size=8)
     assert p.mode == "dp" and p.optimizer_strategy == "zero" and p.dp_mesh_dim == 0 and p.tp_mesh_dim == 0
     p = D.plan(analysis=a, objective="speed", topology={"dp": 2}, backend="cuda", batch_size=8, features=D.DistributedFeatureSet(allow_zero_optimizer=False))
-    assert p.optimizer_strategy == "none" and any("Zero optimizer was disabled" in n for n in p.notes)
+    assert p.optimizer_strategy == "none" and any("ZeRO optimizer sharding was switched off" in n for n in p.notes)
     p = D.plan(analysis=a, objective="memory", topology={"tp": 4}, backend="cuda", batch_size=8)
     assert p.mode == "tp" and any("reduced to 'tp'" in n for n in p.notes)
     with pytest.raises(ValueError, match="requires both 'dp' and 'tp'"):

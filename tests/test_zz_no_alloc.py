@@ -75,3 +75,31 @@ def test_sizes_beyond_the_fixed_scratch_are_rejected(lib):
     assert all(bool((o == 7.0).all()) for o in outs)                   # nothing was launched
     y = torch.zeros(16, 12, device="cuda")
     assert _call(lib, y, None, None, 1e-5, [o[:12] for o in outs]) == E_BAD_ARGUMENT
+
+
+def test_operands_that_are_not_device_memory_are_refused_before_any_launch(lib):
+    """A host pointer (pageable or pinned) or a buffer of another device for ANY operand yields an error code and
+    nothing is launched: a C or ctypes caller that passes the wrong buffer must not fault the device."""
+    E_WRONG_DEVICE = -5
+    y = torch.randn(256, 64, device="cuda")
+    outs = [torch.full((64,), 7.0, device="cuda") for _ in range(4)]
+    host = torch.zeros(64)
+    pinned = torch.zeros(64).pin_memory()
+    for bad_index in range(4):
+        for bad in (host, pinned):
+            trial = list(outs)
+            trial[bad_index] = bad
+            assert _call(lib, y, None, None, 1e-5, trial) == E_BAD_ARGUMENT
+            assert b"not device memory" in lib.sjb200_noalloc_last_error()
+    assert _call(lib, torch.randn(256, 64), None, None, 1e-5, outs) == E_BAD_ARGUMENT        # y on the host
+    assert _call(lib, y, host, None, 1e-5, outs) == E_BAD_ARGUMENT                           # gamma on the host
+    assert _call(lib, y, None, pinned, 1e-5, outs) == E_BAD_ARGUMENT                         # beta on the host
+    if torch.cuda.device_count() > 1:
+        other = torch.zeros(64, device="cuda:1")
+        assert _call(lib, y, None, None, 1e-5, [other] + outs[1:]) == E_WRONG_DEVICE
+        assert _call(lib, y, other, None, 1e-5, outs) == E_WRONG_DEVICE
+    torch.cuda.synchronize()
+    assert all(bool((o == 7.0).all()) for o in outs)                                         # nothing was launched
+    assert _call(lib, y, None, None, 1e-5, outs) == OK                                       # and the entry point still works
+    torch.cuda.synchronize()
+    torch.testing.assert_close(outs[0], y.mean(0), rtol=1e-4, atol=1e-5)
