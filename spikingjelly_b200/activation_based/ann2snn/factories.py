@@ -1,5 +1,5 @@
-"""``NeuronFactory``: how a conversion recipe builds the neuron that replaces an activation.
-Parity: ``spikingjelly/activation_based/ann2snn/factories.py:9-140``."""
+"""``NeuronFactory``: the recipe-side description of the spiking neuron that takes an activation's place
+(``spikingjelly/activation_based/ann2snn/factories.py:9-140``)."""
 from __future__ import annotations
 
 import math
@@ -12,29 +12,43 @@ from .. import neuron
 __all__ = ["NeuronFactory"]
 
 
+def _finite_real(value, what: str, *, allow_none: bool = False):
+    if value is None and allow_none:
+        return None
+    if isinstance(value, bool) or not isinstance(value, (int, float)):
+        raise TypeError(f"{what}: a real number is required{' (or None)' if allow_none else ''}, got {value!r}")
+    if not math.isfinite(value):
+        raise ValueError(f"{what}: must be finite, got {value!r}")
+    return value
+
+
 class NeuronFactory:
-    """``create(scale)`` returns ``neuron_type(v_threshold=..., v_reset=..., **kwargs)``; the default is a
-    soft-reset IF neuron with threshold 1 (the activation scale is applied by the scalers around it)."""
+    """Builds ``neuron_type(v_threshold=..., v_reset=..., **kwargs)`` on demand.  The default — an IF neuron with threshold 1
+    and soft reset — is what rate coding wants: the activation's scale lives in the scalers placed around the neuron, and
+    the soft reset keeps the charge above threshold."""
+
+    #: set through the factory's own parameters, so they may not appear among the extra keyword arguments
+    RESERVED = frozenset({"v_threshold", "v_reset"})
 
     def __init__(self, neuron_type: Type[nn.Module] = neuron.IFNode, v_threshold: float = 1.0, v_reset: Optional[float] = None, **kwargs):
-        if not isinstance(neuron_type, type) or not issubclass(neuron_type, nn.Module):
-            raise TypeError(f"neuron_type must be an nn.Module subclass, but got {neuron_type!r}.")
-        if not isinstance(v_threshold, (int, float)) or isinstance(v_threshold, bool):
-            raise TypeError(f"v_threshold must be a real number, got {type(v_threshold).__name__}.")
-        if not math.isfinite(float(v_threshold)) or not v_threshold > 0:
-            raise ValueError(f"v_threshold must be finite and positive, got {v_threshold}.")
-        if v_reset is not None and (not isinstance(v_reset, (int, float)) or isinstance(v_reset, bool)):
-            raise TypeError(f"v_reset must be None or a real number, got {v_reset!r}.")
-        if v_reset is not None and not math.isfinite(float(v_reset)):
-            raise ValueError(f"v_reset must be finite, got {v_reset}.")
-        reserved = self.neuron_kwargs_reserved_keys() & kwargs.keys()
-        if reserved:
-            raise TypeError(f"neuron kwargs contain reserved key(s): {', '.join(sorted(reserved))}. Use NeuronFactory parameters instead.")
-        self.neuron_type, self.v_threshold, self.v_reset, self.neuron_kwargs = neuron_type, v_threshold, v_reset, kwargs
+        if not (isinstance(neuron_type, type) and issubclass(neuron_type, nn.Module)):
+            raise TypeError(f"neuron_type: a subclass of nn.Module is required, got {neuron_type!r}")
+        if _finite_real(v_threshold, "v_threshold") <= 0:
+            raise ValueError(f"v_threshold: must be positive, got {v_threshold!r}")
+        _finite_real(v_reset, "v_reset", allow_none=True)
+        clash = sorted(self.RESERVED.intersection(kwargs))
+        if clash:
+            raise TypeError(f"{', '.join(clash)}: pass these as NeuronFactory arguments, not among the neuron's extra keyword arguments")
+        self.neuron_type = neuron_type
+        self.v_threshold = v_threshold
+        self.v_reset = v_reset
+        self.neuron_kwargs = kwargs
 
-    @staticmethod
-    def neuron_kwargs_reserved_keys():
-        return {"v_threshold", "v_reset"}
+    @classmethod
+    def neuron_kwargs_reserved_keys(cls):
+        return set(cls.RESERVED)
 
     def create(self, scale: float) -> nn.Module:
+        """A fresh neuron.  ``scale`` (the calibrated activation scale at this site) is offered to subclasses that want a
+        scale-dependent threshold; the default ignores it."""
         return self.neuron_type(v_threshold=self.v_threshold, v_reset=self.v_reset, **self.neuron_kwargs)

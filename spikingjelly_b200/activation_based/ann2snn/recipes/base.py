@@ -1,50 +1,59 @@
-"""Recipe protocol of the converters.  An FX recipe transforms a traced ``GraphModule`` in stages
-(validate, before_trace, after_trace, insert_observers, calibrate, replace, finalize); a module recipe
-rewrites the module tree directly.  Parity: ``spikingjelly/activation_based/ann2snn/recipes/base.py:15-492``."""
+"""What a conversion recipe is (``spikingjelly/activation_based/ann2snn/recipes/base.py:22-492``).
+
+An FX recipe works on a traced ``GraphModule`` and is asked, in the order of :data:`FX_STAGES`, to validate its settings,
+touch the model before and after tracing, insert observers, calibrate, replace nodes and finalise.  A module recipe gets
+the module tree itself.  Every stage is optional: a recipe overrides the ones it needs, the rest pass their argument
+through."""
 from __future__ import annotations
 
 import torch.nn as nn
 from torch import fx
 
-__all__ = ["ConversionRecipe", "FXConversionRecipe", "ModuleConversionRecipe", "replace_submodule"]
+__all__ = ["ConversionRecipe", "FXConversionRecipe", "ModuleConversionRecipe", "replace_submodule", "FX_STAGES"]
+
+#: graph stages in execution order (``validate`` and ``before_trace`` come before there is a graph)
+FX_STAGES = ("after_trace", "insert_observers", "calibrate", "replace", "finalize")
 
 
 def replace_submodule(fx_model: fx.GraphModule, target: str, module: nn.Module) -> None:
-    parent_name, _, child = target.rpartition(".")
-    setattr(fx_model.get_submodule(parent_name) if parent_name else fx_model, child, module)
+    """``fx_model.<target> = module`` for a dotted ``target``."""
+    *owner_path, leaf = target.split(".")
+    owner = fx_model.get_submodule(".".join(owner_path)) if owner_path else fx_model
+    setattr(owner, leaf, module)
+
+
+def _pass_through(self, converter, graph_or_module):
+    return graph_or_module
 
 
 class FXConversionRecipe:
-    """Every stage defaults to the identity; ``converter`` gives access to ``converter.device``."""
+    """Base of the graph recipes.  ``converter`` is the running converter (``converter.device`` is where the result goes)."""
 
     def validate(self, converter) -> None:
-        return None
+        """Check the recipe's own settings; raise on a contradiction."""
 
-    def before_trace(self, converter, ann: nn.Module) -> nn.Module:
-        return ann
+    before_trace = _pass_through        # (converter, ann) -> ann            e.g. switch to eval mode
+    after_trace = _pass_through         # (converter, graph) -> graph        e.g. fold batch norms
+    insert_observers = _pass_through    # (converter, graph) -> graph
+    calibrate = _pass_through           # (converter, graph) -> graph        run the calibration data
+    replace = _pass_through             # (converter, graph) -> graph        put the spiking modules in
+    finalize = _pass_through            # (converter, graph) -> nn.Module
 
-    def after_trace(self, converter, fx_model: fx.GraphModule) -> fx.GraphModule:
-        return fx_model
-
-    def insert_observers(self, converter, fx_model: fx.GraphModule) -> fx.GraphModule:
-        return fx_model
-
-    def calibrate(self, converter, fx_model: fx.GraphModule) -> fx.GraphModule:
-        return fx_model
-
-    def replace(self, converter, fx_model: fx.GraphModule) -> fx.GraphModule:
-        return fx_model
-
-    def finalize(self, converter, fx_model: fx.GraphModule) -> nn.Module:
-        return fx_model
+    def run_graph_stages(self, converter, graph: fx.GraphModule) -> nn.Module:
+        """All stages that take the traced graph, in order."""
+        for stage in FX_STAGES:
+            graph = getattr(self, stage)(converter, graph)
+        return graph
 
 
+#: historical name of the graph recipe base
 ConversionRecipe = FXConversionRecipe
 
 
 class ModuleConversionRecipe:
-    def validate(self, converter) -> None:
-        return None
+    """Base of the recipes that rewrite modules in place, without tracing."""
 
-    def convert_module(self, converter, ann: nn.Module) -> nn.Module:
-        return ann
+    def validate(self, converter) -> None:
+        """Check the recipe's own settings; raise on a contradiction."""
+
+    convert_module = _pass_through      # (converter, ann) -> converted module

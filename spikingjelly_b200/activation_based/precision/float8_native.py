@@ -180,7 +180,7 @@ class Float8NativePolicy(PrecisionPolicy):
 
     def check_capability(self, model, device) -> None:
         super().check_capability(model, device)
-        report = self._capability_report
+        report = self._capability
         report["te_recipe_requested"] = self.fp8_recipe
         if self.fp8_recipe not in _SUPPORTED_RECIPES:
             report["te_recipe_fallback_reason"] = f"unsupported fp8 recipe {self.fp8_recipe!r}"

@@ -97,6 +97,7 @@ struct ConvGeom {
     int CN;                 // LOADER 1 with MN-major B: filter columns per tap (= Cin); LOADER 2: channels per tap
     int wr0, wr_step, ws0, ws_step, S;
     int scatter, out_H, out_W, out_mul_h, out_mul_w, out_add_h, out_add_w;
+    int tiled;              // the gathered operand comes by tiled 4-D loads of (bw x bh x bn) pixel blocks instead of im2col loads
 };
 
 // Epilogue of one output tile for one warp: drains NCHUNK chunks of 32 accumulator columns (this warp's 32 TMEM lanes =
@@ -302,8 +303,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         mbar_expect_tx(full_bar + s, L::STAGE_BYTES);
                         const int tap = kb / cpb, chan = (kb - tap * cpb) * 64;
                         const int th = tap / cg.taps_w, tw = tap - th * cg.taps_w;
-                        tma_load_im2col_4d(sa, &tmA, chan, cv_w, cv_h, cv_img, (uint16_t)(tw * cg.dil_w), (uint16_t)(th * cg.dil_h),
-                                           full_bar + s);
+                        if (cg.tiled) tma_load_4d(sa, &tmA, chan, cv_w + tw * cg.dil_w, cv_h + th * cg.dil_h, cv_img, full_bar + s);
+                        else tma_load_im2col_4d(sa, &tmA, chan, cv_w, cv_h, cv_img, (uint16_t)(tw * cg.dil_w), (uint16_t)(th * cg.dil_h),
+                                                full_bar + s);
                         const int wtap = (cg.wr0 + cg.wr_step * th) * cg.S + (cg.ws0 + cg.ws_step * tw);
                         if (B_MN) {
 #pragma unroll

@@ -69,6 +69,13 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
+// Tiled 4-D load: a (c, w, h, n) box of an NHWC tensor; coordinates may lie outside the tensor (zero fill), which is how a
+// convolution's padding and a filter tap's shift are expressed.  Rows land in (n, h, w) order, 128 bytes of channels each.
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int c, int w, int h, int n, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n) : "memory");
+}
 // TMA im2col load (NHWC tensor, 4-D map made by cuTensorMapEncodeIm2col): `pixels-per-column` pixels starting at the
 // bounding-box position (w, h, n) and walking w, then h, then n in steps of the map's traversal strides, each pixel
 // shifted by the filter-tap offset (off_w, off_h); `channels-per-pixel` channels from `c` on.  Positions outside the
