@@ -295,232 +295,276 @@ class Trainer:
 
     # ------------------------------------------------------------------ main
     def main(self, args):
+        """Runs the whole job: set-up (:meth:`_set_up`), optional resume, then the epoch loop or a single evaluation."""
+        run = self._set_up(args)
+        if run is None:                       # --print-logdir
+            return
+        if args.resume is not None:
+            self._resume(args, run)
+        self._wrap_for_training(args, run)
+        if args.test_only:
+            target, tag = (run.model_ema, "EMA") if run.model_ema else (run.eval_model, "")
+            self.evaluate(args, target, run.criterion, run.test_loader, device=run.device, log_suffix=tag)
+            return
+        for epoch in range(args.start_epoch, args.epochs):
+            began = time.time()
+            if args.distributed:
+                run.train_sampler.set_epoch(epoch)
+            self.before_train_one_epoch(args, run.model, epoch)
+            loss, acc1, acc5 = self.train_one_epoch(run.model, run.criterion, run.optimizer, run.train_loader, run.device, epoch, args,
+                                                    run.model_ema, run.scaler)
+            if hasattr(run.model, "check_communication"):
+                run.model.check_communication()        # a gradient exchange that gave up on a peer ends the job here
+            run.log_scalars(epoch, train_loss=loss, train_acc1=acc1, train_acc5=acc5)
+            if run.lr_scheduler is not None:
+                run.lr_scheduler.step()
+            self.before_test_one_epoch(args, run.eval_model, epoch)
+            loss, acc1, acc5 = self.evaluate(args, run.eval_model, run.criterion, run.test_loader, device=run.device)
+            run.log_scalars(epoch, test_loss=loss, test_acc1=acc1, test_acc5=acc5)
+            ema_acc1 = None
+            if run.model_ema:
+                ema_loss, ema_acc1, ema_acc5 = self.evaluate(args, run.model_ema, run.criterion, run.test_loader, device=run.device,
+                                                             log_suffix="EMA")
+                run.log_scalars(epoch, ema_test_loss=ema_loss, ema_test_acc1=ema_acc1, ema_test_acc5=ema_acc5)
+            self._save_checkpoints(args, run, epoch, acc1, ema_acc1)
+            if run.is_main:
+                left = (time.time() - began) * (args.epochs - epoch)
+                logger.info("expected to finish at %s", (datetime.datetime.now() + datetime.timedelta(seconds=left)).strftime("%Y-%m-%d %H:%M:%S"))
+
+    # ---------------------------------------------------------------- set-up, in the order main() needs it
+    def _set_up(self, args):
         set_deterministic(args.seed, args.disable_uda)
         if args.workers > 0 and args.prefetch_factor < 1:
-            raise ValueError(f"--prefetch-factor must be >= 1 when --workers > 0, but got {args.prefetch_factor}.")
+            raise ValueError(f"--prefetch-factor {args.prefetch_factor}: loader workers prefetch at least one batch each")
         if args.output_dir:
             utils.mkdir(args.output_dir)
         utils.init_distributed_mode(args)
-        main_proc = utils.is_main_process()
-        if main_proc:
-            logger.info("Training arguments: %s", args)
-        device = torch.device(args.device)
+        run = _Run(device=torch.device(args.device), is_main=utils.is_main_process())
+        if run.is_main:
+            logger.info("arguments: %s", args)
+        train_set, test_set, run.train_sampler, test_sampler = self.load_data(args)
+        classes = len(train_set.classes)
+        shared = dict(batch_size=args.batch_size, num_workers=args.workers, pin_memory=not args.disable_pinmemory,
+                      worker_init_fn=seed_worker, persistent_workers=args.persistent_workers and args.workers > 0,
+                      prefetch_factor=args.prefetch_factor if args.workers > 0 else None)
+        run.train_loader = torch.utils.data.DataLoader(train_set, sampler=run.train_sampler, collate_fn=_batch_mixer(args, classes), **shared)
+        run.test_loader = torch.utils.data.DataLoader(test_set, sampler=test_sampler, **shared)
 
-        dataset, dataset_test, train_sampler, test_sampler = self.load_data(args)
-        num_classes = len(dataset.classes)
-        collate_fn = None
-        mixers = []
-        if args.mixup_alpha > 0.0 or args.cutmix_alpha > 0.0:
-            from torch.utils.data.dataloader import default_collate
-            from .tv_ref_classify import transforms as T
-            if args.mixup_alpha > 0.0:
-                mixers.append(T.RandomMixup(num_classes, p=1.0, alpha=args.mixup_alpha))
-            if args.cutmix_alpha > 0.0:
-                mixers.append(T.RandomCutmix(num_classes, p=1.0, alpha=args.cutmix_alpha))
-
-            def collate_fn(batch):
-                return random.choice(mixers)(*default_collate(batch))
-        loader_kw = dict(batch_size=args.batch_size, num_workers=args.workers, pin_memory=not args.disable_pinmemory,
-                         worker_init_fn=seed_worker, persistent_workers=args.persistent_workers and args.workers > 0,
-                         prefetch_factor=(args.prefetch_factor if args.workers > 0 else None))
-        data_loader = torch.utils.data.DataLoader(dataset, sampler=train_sampler, collate_fn=collate_fn, **loader_kw)
-        data_loader_test = torch.utils.data.DataLoader(dataset_test, sampler=test_sampler, **loader_kw)
-
-        model = self.load_model(args, num_classes)
-        model.to(device)
-        if main_proc:
-            logger.info("Model created: %s", type(model).__name__)
-            logger.debug("Model architecture:\n%s", model)
+        run.bare_model = self.load_model(args, classes).to(run.device)
+        if run.is_main:
+            logger.info("model: %s", type(run.bare_model).__name__)
+            logger.debug("%s", run.bare_model)
         if args.distributed and args.sync_bn:
-            model = torch.nn.SyncBatchNorm.convert_sync_batchnorm(model)
-        criterion = nn.CrossEntropyLoss(label_smoothing=args.label_smoothing)
-
-        if args.norm_weight_decay is None:
-            parameters = model.parameters()
-        else:
-            norm_classes = (nn.modules.batchnorm._BatchNorm, nn.LayerNorm, nn.GroupNorm, nn.modules.instancenorm._InstanceNorm,
-                            nn.LocalResponseNorm)
-            norm_params, other_params = [], []
-            for m in model.modules():
-                bucket = norm_params if isinstance(m, norm_classes) else other_params
-                bucket.extend(p for p in m.parameters(recurse=False) if p.requires_grad)
-            parameters = [{"params": p, "weight_decay": w} for p, w in
-                          ((norm_params, args.norm_weight_decay), (other_params, args.weight_decay)) if p]
-        optimizer = self.set_optimizer(args, parameters)
-        use_scaler = (not args.disable_amp) and device.type == "cuda" and getattr(args, "amp_dtype", "bf16") == "fp16"
-        scaler = torch.amp.GradScaler("cuda") if use_scaler else None
-        lr_scheduler = self.set_lr_scheduler(args, optimizer)
-        model_without_ddp = model
-
-        model_ema = None
+            run.bare_model = nn.SyncBatchNorm.convert_sync_batchnorm(run.bare_model)
+        run.criterion = nn.CrossEntropyLoss(label_smoothing=args.label_smoothing)
+        run.optimizer = self.set_optimizer(args, _parameter_groups(run.bare_model, args.weight_decay, args.norm_weight_decay))
+        fp16 = getattr(args, "amp_dtype", "bf16") == "fp16"
+        run.scaler = torch.amp.GradScaler("cuda") if (fp16 and not args.disable_amp and run.device.type == "cuda") else None
+        run.lr_scheduler = self.set_lr_scheduler(args, run.optimizer)
         if args.model_ema:
-            # keep the EMA horizon independent of world size, batch size, update period and epoch count
-            adjust = args.world_size * args.batch_size * args.model_ema_steps / args.epochs
-            alpha = min(1.0, (1.0 - args.model_ema_decay) * adjust)
-            model_ema = utils.ExponentialMovingAverage(model_without_ddp, device=device, decay=1.0 - alpha)
+            # decay rescaled so that the averaging horizon (in samples) does not depend on world size, batch size,
+            # update period or epoch count
+            per_update = args.world_size * args.batch_size * args.model_ema_steps / args.epochs
+            keep = 1.0 - min(1.0, (1.0 - args.model_ema_decay) * per_update)
+            run.model_ema = utils.ExponentialMovingAverage(run.bare_model, device=run.device, decay=keep)
 
-        tb_name = self.get_tb_logdir_name(args)
-        pt_dir = os.path.join(args.output_dir, "pt", tb_name)
-        tb_dir = os.path.join(args.output_dir, tb_name)
+        name = self.get_tb_logdir_name(args)
+        run.tb_dir, run.pt_dir = os.path.join(args.output_dir, name), os.path.join(args.output_dir, "pt", name)
         if args.print_logdir:
-            if main_proc:
-                logger.info("TensorBoard log directory: %s", tb_dir)
-                logger.info("Checkpoint directory: %s", pt_dir)
-            sys.exit()
-        if args.clean and main_proc:
-            for d in (tb_dir, pt_dir):
-                if os.path.exists(d):
-                    shutil.rmtree(d)
-            logger.info("remove %s and %s.", tb_dir, pt_dir)
-        if main_proc:
-            os.makedirs(tb_dir, exist_ok=args.resume is not None)
-            os.makedirs(pt_dir, exist_ok=args.resume is not None)
+            if run.is_main:
+                logger.info("TensorBoard directory: %s", run.tb_dir)
+                logger.info("checkpoint directory: %s", run.pt_dir)
+            return None
+        if run.is_main:
+            if args.clean:
+                for folder in (run.tb_dir, run.pt_dir):
+                    shutil.rmtree(folder, ignore_errors=True)
+                logger.info("removed %s and %s", run.tb_dir, run.pt_dir)
+            for folder in (run.tb_dir, run.pt_dir):
+                os.makedirs(folder, exist_ok=args.resume is not None)      # a fresh run must not land in a used directory
+        return run
 
-        max_test_acc1, max_ema_test_acc1 = -1.0, -1.0
-        if args.resume is not None:
-            path = os.path.join(pt_dir, "checkpoint_latest.pth") if args.resume == "latest" else args.resume
-            checkpoint = torch.load(path, map_location="cpu", weights_only=False)
-            model_without_ddp.load_state_dict(checkpoint["model"])
-            if not args.test_only:
-                optimizer.load_state_dict(checkpoint["optimizer"])
-                lr_scheduler.load_state_dict(checkpoint["lr_scheduler"])
-            args.start_epoch = checkpoint["epoch"] + 1
-            if model_ema:
-                model_ema.load_state_dict(checkpoint["model_ema"])
-                max_ema_test_acc1 = checkpoint.get("max_ema_test_acc1", -1.0)
-            if scaler and "scaler" in checkpoint:
-                scaler.load_state_dict(checkpoint["scaler"])
-            max_test_acc1 = checkpoint.get("max_test_acc1", -1.0)
+    def _resume(self, args, run) -> None:
+        path = os.path.join(run.pt_dir, "checkpoint_latest.pth") if args.resume == "latest" else args.resume
+        saved = torch.load(path, map_location="cpu", weights_only=False)
+        run.bare_model.load_state_dict(saved["model"])
+        if not args.test_only:
+            run.optimizer.load_state_dict(saved["optimizer"])
+            if run.lr_scheduler is not None and saved.get("lr_scheduler") is not None:
+                run.lr_scheduler.load_state_dict(saved["lr_scheduler"])
+        args.start_epoch = saved["epoch"] + 1
+        run.best = saved.get("max_test_acc1", -1.0)
+        if run.model_ema:
+            run.model_ema.load_state_dict(saved["model_ema"])
+            run.best_ema = saved.get("max_ema_test_acc1", -1.0)
+        if run.scaler and "scaler" in saved:
+            run.scaler.load_state_dict(saved["scaler"])
 
-        model = self.compile_model(args, model_without_ddp)
-        eval_model = self.get_eval_model(args, model, model_without_ddp)
+    def _wrap_for_training(self, args, run) -> None:
+        run.model = self.compile_model(args, run.bare_model)
+        run.eval_model = self.get_eval_model(args, run.model, run.bare_model)
         if args.distributed:
-            model = self._wrap_distributed(args, model, device)
-
-        tb_writer = None
-        if main_proc:
+            run.model = self._wrap_distributed(args, run.model, run.device)
+            if hasattr(run.model, "guard_optimizer"):
+                run.model.guard_optimizer(run.optimizer)
+        if run.is_main:
             try:
                 from torch.utils.tensorboard import SummaryWriter
-                tb_writer = SummaryWriter(tb_dir, purge_step=args.start_epoch)
-            except Exception as e:                 # TensorBoard is optional
-                logger.warning("TensorBoard unavailable (%s); scalars are only logged.", e)
-            with open(os.path.join(tb_dir, "args.txt"), "w", encoding="utf-8") as f:
-                f.write(str(args) + "\n" + " ".join(sys.argv))
+                run.writer = SummaryWriter(run.tb_dir, purge_step=args.start_epoch)
+            except Exception as problem:           # TensorBoard is optional
+                logger.warning("no TensorBoard (%s): scalars go to the log only", problem)
+            with open(os.path.join(run.tb_dir, "args.txt"), "w", encoding="utf-8") as f:
+                f.write(f"{args}\n{' '.join(sys.argv)}")
 
-        def scalars(epoch, **kv):
-            if tb_writer is not None:
-                for k, v in kv.items():
-                    tb_writer.add_scalar(k, v, epoch)
-
-        if args.test_only:
-            if model_ema:
-                self.evaluate(args, model_ema, criterion, data_loader_test, device=device, log_suffix="EMA")
-            else:
-                self.evaluate(args, eval_model, criterion, data_loader_test, device=device)
-            return
-
-        for epoch in range(args.start_epoch, args.epochs):
-            t0 = time.time()
-            if args.distributed:
-                train_sampler.set_epoch(epoch)
-            self.before_train_one_epoch(args, model, epoch)
-            train_loss, train_acc1, train_acc5 = self.train_one_epoch(model, criterion, optimizer, data_loader, device, epoch,
-                                                                      args, model_ema, scaler)
-            scalars(epoch, train_loss=train_loss, train_acc1=train_acc1, train_acc5=train_acc5)
-            if lr_scheduler is not None:
-                lr_scheduler.step()
-            self.before_test_one_epoch(args, eval_model, epoch)
-            test_loss, test_acc1, test_acc5 = self.evaluate(args, eval_model, criterion, data_loader_test, device=device)
-            scalars(epoch, test_loss=test_loss, test_acc1=test_acc1, test_acc5=test_acc5)
-            if model_ema:
-                ema_loss, ema_acc1, ema_acc5 = self.evaluate(args, model_ema, criterion, data_loader_test, device=device,
-                                                             log_suffix="EMA")
-                scalars(epoch, ema_test_loss=ema_loss, ema_test_acc1=ema_acc1, ema_test_acc5=ema_acc5)
-            if main_proc:
-                is_best = test_acc1 > max_test_acc1
-                max_test_acc1 = max(max_test_acc1, test_acc1)
-                checkpoint = {"model": model_without_ddp.state_dict(), "optimizer": optimizer.state_dict(),
-                              "lr_scheduler": lr_scheduler.state_dict() if lr_scheduler is not None else None,
-                              "epoch": epoch, "args": args, "max_test_acc1": max_test_acc1}
-                is_best_ema = False
-                if model_ema:
-                    is_best_ema = ema_acc1 > max_ema_test_acc1
-                    max_ema_test_acc1 = max(max_ema_test_acc1, ema_acc1)
-                    checkpoint["model_ema"] = model_ema.state_dict()
-                    checkpoint["max_ema_test_acc1"] = max_ema_test_acc1
-                if scaler:
-                    checkpoint["scaler"] = scaler.state_dict()
-                names = [f"checkpoint_{epoch}.pth", "checkpoint_latest.pth"]
-                names += ["checkpoint_max_test_acc1.pth"] if is_best else []
-                names += ["checkpoint_max_ema_test_acc1.pth"] if is_best_ema else []
-                for name in names:
-                    utils.save_on_master(checkpoint, os.path.join(pt_dir, name))
-                previous = os.path.join(pt_dir, f"checkpoint_{epoch - 1}.pth")
-                if epoch > 0 and os.path.exists(previous):
-                    os.remove(previous)
-                eta = datetime.datetime.now() + datetime.timedelta(seconds=(time.time() - t0) * (args.epochs - epoch))
-                logger.info("Estimated finish time: %s", eta.strftime("%Y-%m-%d %H:%M:%S"))
+    def _save_checkpoints(self, args, run, epoch: int, acc1: float, ema_acc1) -> None:
+        """Rank 0 writes ``checkpoint_<epoch>.pth`` and ``checkpoint_latest.pth`` (plus the ``max_*`` files when a record
+        fell) and drops the previous epoch's file; then ALL ranks meet at a barrier, so that nobody races ahead into the
+        next epoch's collectives while rank 0 is still writing."""
+        if run.is_main:
+            record, run.best = acc1 > run.best, max(run.best, acc1)
+            state = {"model": run.bare_model.state_dict(), "optimizer": run.optimizer.state_dict(),
+                     "lr_scheduler": None if run.lr_scheduler is None else run.lr_scheduler.state_dict(), "epoch": epoch,
+                     "args": args, "max_test_acc1": run.best}
+            files = [f"checkpoint_{epoch}.pth", "checkpoint_latest.pth"] + (["checkpoint_max_test_acc1.pth"] if record else [])
+            if run.model_ema:
+                if ema_acc1 > run.best_ema:
+                    files.append("checkpoint_max_ema_test_acc1.pth")
+                run.best_ema = max(run.best_ema, ema_acc1)
+                state.update(model_ema=run.model_ema.state_dict(), max_ema_test_acc1=run.best_ema)
+            if run.scaler:
+                state["scaler"] = run.scaler.state_dict()
+            for name in files:
+                utils.save_on_master(state, os.path.join(run.pt_dir, name))
+            stale = os.path.join(run.pt_dir, f"checkpoint_{epoch - 1}.pth")
+            if epoch > 0 and os.path.exists(stale):
+                os.remove(stale)
+        if utils.is_dist_avail_and_initialized():
+            torch.distributed.barrier()
 
     # ------------------------------------------------------------- arguments
     def get_args_parser(self, add_help=True):
-        p = argparse.ArgumentParser(description="PyTorch Classification Training", add_help=add_help)
-        a = p.add_argument
-        a("--data-path", default="/datasets01/imagenet_full_size/061417/", type=str, help="dataset path")
-        a("--model", default="resnet18", type=str, help="model name")
-        a("--device", default="cuda", type=str, help="device (Use cuda or cpu Default: cuda)")
-        a("-b", "--batch-size", default=32, type=int, help="images per gpu, the total batch size is $NGPU x batch_size")
-        a("--epochs", default=90, type=int, metavar="N", help="number of total epochs to run")
-        a("-j", "--workers", default=16, type=int, metavar="N", help="number of data loading workers (default: 16)")
-        a("--opt", default="sgd", type=str, help="optimizer")
-        a("--lr", default=0.1, type=float, help="initial learning rate")
-        a("--momentum", default=0.9, type=float, metavar="M", help="momentum")
-        a("--wd", "--weight-decay", default=0.0, type=float, metavar="W", help="weight decay (default: 0.)", dest="weight_decay")
-        a("--norm-weight-decay", default=None, type=float, help="weight decay for Normalization layers (default: None, same value as --wd)")
-        a("--label-smoothing", default=0.1, type=float, help="label smoothing (default: 0.1)", dest="label_smoothing")
-        a("--mixup-alpha", default=0.2, type=float, help="mixup alpha (default: 0.2)")
-        a("--cutmix-alpha", default=1.0, type=float, help="cutmix alpha (default: 1.0)")
-        a("--lr-scheduler", default="cosa", type=str, help="the lr scheduler (default: cosa)")
-        a("--lr-warmup-epochs", default=5, type=int, help="the number of epochs to warmup (default: 5)")
-        a("--lr-warmup-method", default="linear", type=str, help="the warmup method (default: linear)")
-        a("--lr-warmup-decay", default=0.01, type=float, help="the decay for lr")
-        a("--lr-step-size", default=30, type=int, help="decrease lr every step-size epochs")
-        a("--lr-gamma", default=0.1, type=float, help="decrease lr by a factor of lr-gamma")
-        a("--output-dir", default="./logs", type=str, help="path to save outputs")
-        a("--resume", default=None, type=str, help="path of checkpoint. If set to 'latest', it will try to load the latest checkpoint")
-        a("--start-epoch", default=0, type=int, metavar="N", help="start epoch")
-        a("--cache-dataset", dest="cache_dataset", action="store_true", help="Cache the datasets for quicker initialization. It also serializes the transforms")
-        a("--sync-bn", dest="sync_bn", action="store_true", help="Use sync batch norm")
-        a("--test-only", dest="test_only", action="store_true", help="Only test the model")
-        a("--pretrained", dest="pretrained", action="store_true", help="Use pre-trained models from the modelzoo")
-        a("--auto-augment", default="ta_wide", type=str, help="auto augment policy (default: ta_wide)")
-        a("--random-erase", default=0.1, type=float, help="random erasing probability (default: 0.1)")
-        a("--world-size", default=1, type=int, help="number of distributed processes")
-        a("--dist-url", default="env://", type=str, help="url used to set up distributed training")
-        a("--model-ema", action="store_true", help="enable tracking Exponential Moving Average of model parameters")
-        a("--model-ema-steps", type=int, default=32, help="the number of iterations that controls how often to update the EMA model (default: 32)")
-        a("--model-ema-decay", type=float, default=0.99998, help="decay factor for Exponential Moving Average of model parameters (default: 0.99998)")
-        a("--interpolation", default="bilinear", type=str, help="the interpolation method (default: bilinear)")
-        a("--val-resize-size", default=232, type=int, help="the resize size used for validation (default: 232)")
-        a("--val-crop-size", default=224, type=int, help="the central crop size used for validation (default: 224)")
-        a("--train-crop-size", default=176, type=int, help="the random crop size used for training (default: 176)")
-        a("--clip-grad-norm", default=None, type=float, help="the maximum gradient norm (default None)")
-        a("--ra-sampler", action="store_true", help="whether to use Repeated Augmentation in training")
-        a("--ra-reps", default=4, type=int, help="number of repetitions for Repeated Augmentation (default: 4)")
-        a("--prototype", dest="prototype", action="store_true", help="accepted for compatibility; torchvision's prototype API no longer exists")
-        a("--weights", default=None, type=str, help="the weights enum name to load")
-        a("--seed", default=2020, type=int, help="the random seed")
-        a("--print-logdir", action="store_true", help="print the dirs for tensorboard logs and pt files and exit")
-        a("--clean", action="store_true", help="delete the dirs for tensorboard logs and pt files")
-        a("--disable-pinmemory", action="store_true", help="not use pin memory in dataloader, which can help reduce memory consumption")
-        a("--persistent-workers", action="store_true", help="keep DataLoader workers alive across epochs")
-        a("--prefetch-factor", default=2, type=int, help="number of batches loaded in advance by each worker")
-        a("--disable-amp", action="store_true", help="not use automatic mixed precision training")
-        a("--amp-dtype", default="bf16", choices=("bf16", "fp16"), help="autocast dtype (bf16 needs no gradient scaler)")
-        a("--compile", action="store_true", help="wrap the model with torch.compile")
-        a("--compile-backend", default="inductor", type=str, help="torch.compile backend")
-        a("--compile-mode", default=None, type=str, help="torch.compile mode")
-        a("--compile-disable-cudagraphs", action="store_true", help="disable CUDA graphs inside the inductor backend")
-        a("--compile-eval", action="store_true", help="also evaluate with the compiled model")
-        a("--local_rank", type=int, help="args for DDP, which should not be set by user")
-        a("--disable-uda", action="store_true", help="not set 'torch.use_deterministic_algorithms(True)', which can avoid the error raised by some functions that do not have a deterministic implementation")
-        return p
+        """The command line of the reference trainer (same flags, destinations and defaults), built from :data:`ARGUMENTS`."""
+        parser = argparse.ArgumentParser(description="Train an image classifier (spiking or not)", add_help=add_help)
+        for flags, options in ARGUMENTS:
+            parser.add_argument(*flags, **options)
+        return parser
+
+
+class _Run:
+    """Everything one call of ``Trainer.main`` builds, in one place."""
+
+    def __init__(self, device, is_main: bool):
+        self.device, self.is_main = device, is_main
+        self.train_loader = self.test_loader = self.train_sampler = None
+        self.bare_model = self.model = self.eval_model = self.model_ema = None
+        self.criterion = self.optimizer = self.lr_scheduler = self.scaler = None
+        self.tb_dir = self.pt_dir = None
+        self.writer = None
+        self.best = self.best_ema = -1.0
+
+    def log_scalars(self, epoch: int, **values) -> None:
+        if self.writer is not None:
+            for tag, value in values.items():
+                self.writer.add_scalar(tag, value, epoch)
+
+
+def _batch_mixer(args, num_classes: int):
+    """Collate function applying mixup or cutmix (one of them, chosen per batch) when either is switched on."""
+    if args.mixup_alpha <= 0.0 and args.cutmix_alpha <= 0.0:
+        return None
+    from torch.utils.data.dataloader import default_collate
+    from .tv_ref_classify import transforms as T
+    choices = []
+    if args.mixup_alpha > 0.0:
+        choices.append(T.RandomMixup(num_classes, p=1.0, alpha=args.mixup_alpha))
+    if args.cutmix_alpha > 0.0:
+        choices.append(T.RandomCutmix(num_classes, p=1.0, alpha=args.cutmix_alpha))
+    return lambda batch: random.choice(choices)(*default_collate(batch))
+
+
+_NORM_LAYERS = (nn.modules.batchnorm._BatchNorm, nn.LayerNorm, nn.GroupNorm, nn.modules.instancenorm._InstanceNorm, nn.LocalResponseNorm)
+
+
+def _parameter_groups(model: nn.Module, weight_decay: float, norm_weight_decay):
+    """All parameters, or two groups when normalisation layers get their own weight decay."""
+    if norm_weight_decay is None:
+        return model.parameters()
+    norm, rest = [], []
+    for module in model.modules():
+        own = [p for p in module.parameters(recurse=False) if p.requires_grad]
+        (norm if isinstance(module, _NORM_LAYERS) else rest).extend(own)
+    groups = [{"params": rest, "weight_decay": weight_decay}, {"params": norm, "weight_decay": norm_weight_decay}]
+    return [g for g in groups if g["params"]]
+
+
+def _flag(*names, **options):
+    return names, options
+
+
+#: the command line: flag names, destinations and defaults are those of the reference trainer; the help text is ours
+ARGUMENTS = (
+    # data and model
+    _flag("--data-path", default="/datasets01/imagenet_full_size/061417/", type=str, help="root folder of the dataset"),
+    _flag("--model", default="resnet18", type=str, help="name handed to load_model()"),
+    _flag("--device", default="cuda", type=str, help="cuda or cpu"),
+    _flag("-b", "--batch-size", default=32, type=int, help="samples per process and step (global batch = processes x this)"),
+    _flag("--epochs", default=90, type=int, metavar="N", help="passes over the training set"),
+    _flag("-j", "--workers", default=16, type=int, metavar="N", help="loader worker processes"),
+    _flag("--pretrained", dest="pretrained", action="store_true", help="start from the model zoo's weights"),
+    _flag("--weights", default=None, type=str, help="name of a weights enum to load"),
+    _flag("--prototype", dest="prototype", action="store_true", help="ignored (kept so that old command lines still parse)"),
+    # optimisation
+    _flag("--opt", default="sgd", type=str, help="sgd, sgd_nesterov, rmsprop or adamw"),
+    _flag("--lr", default=0.1, type=float, help="peak learning rate"),
+    _flag("--momentum", default=0.9, type=float, metavar="M", help="momentum of SGD / RMSprop"),
+    _flag("--wd", "--weight-decay", default=0.0, type=float, metavar="W", dest="weight_decay", help="weight decay"),
+    _flag("--norm-weight-decay", default=None, type=float, help="separate weight decay for normalisation layers (default: same as --wd)"),
+    _flag("--label-smoothing", default=0.1, type=float, dest="label_smoothing", help="label smoothing of the cross entropy"),
+    _flag("--mixup-alpha", default=0.2, type=float, help="mixup strength, 0 switches it off"),
+    _flag("--cutmix-alpha", default=1.0, type=float, help="cutmix strength, 0 switches it off"),
+    _flag("--clip-grad-norm", default=None, type=float, help="clip the global gradient norm to this value"),
+    _flag("--lr-scheduler", default="cosa", type=str, help="step, cosa (cosine annealing) or exp"),
+    _flag("--lr-warmup-epochs", default=5, type=int, help="epochs of warm-up before the main schedule, 0 for none"),
+    _flag("--lr-warmup-method", default="linear", type=str, help="linear or constant"),
+    _flag("--lr-warmup-decay", default=0.01, type=float, help="learning-rate factor at the start of the warm-up"),
+    _flag("--lr-step-size", default=30, type=int, help="period of the step schedule in epochs"),
+    _flag("--lr-gamma", default=0.1, type=float, help="factor of the step / exponential schedule"),
+    _flag("--model-ema", action="store_true", help="keep an exponential moving average of the weights and evaluate it too"),
+    _flag("--model-ema-steps", type=int, default=32, help="update the average every this many steps"),
+    _flag("--model-ema-decay", type=float, default=0.99998, help="decay of the average, before rescaling to the run's size"),
+    # augmentation and evaluation geometry
+    _flag("--auto-augment", default="ta_wide", type=str, help="ra, ta_wide, augmix or an AutoAugment policy name"),
+    _flag("--random-erase", default=0.1, type=float, help="probability of random erasing"),
+    _flag("--interpolation", default="bilinear", type=str, help="resampling filter of the resizes"),
+    _flag("--val-resize-size", default=232, type=int, help="shorter side after the validation resize"),
+    _flag("--val-crop-size", default=224, type=int, help="centre crop used for validation"),
+    _flag("--train-crop-size", default=176, type=int, help="random crop used for training"),
+    _flag("--ra-sampler", action="store_true", help="repeated augmentation: every sample appears --ra-reps times per epoch, spread over the ranks"),
+    _flag("--ra-reps", default=4, type=int, help="repetitions under --ra-sampler"),
+    _flag("--cache-dataset", dest="cache_dataset", action="store_true", help="pickle the scanned image folders (with their transforms) for faster start-up"),
+    # bookkeeping
+    _flag("--output-dir", default="./logs", type=str, help="where logs and checkpoints go"),
+    _flag("--resume", default=None, type=str, help="checkpoint to continue from; 'latest' picks checkpoint_latest.pth of this configuration"),
+    _flag("--start-epoch", default=0, type=int, metavar="N", help="first epoch (set by --resume)"),
+    _flag("--test-only", dest="test_only", action="store_true", help="evaluate and exit"),
+    _flag("--seed", default=2020, type=int, help="seed of python, numpy and torch"),
+    _flag("--print-logdir", action="store_true", help="print the log and checkpoint directories of this configuration and exit"),
+    _flag("--clean", action="store_true", help="delete those directories first"),
+    _flag("--disable-uda", action="store_true", help="do not call torch.use_deterministic_algorithms(True) (for operators without a deterministic kernel)"),
+    # loader and precision
+    _flag("--disable-pinmemory", action="store_true", help="unpinned host batches (less host memory, slower copies)"),
+    _flag("--persistent-workers", action="store_true", help="keep loader workers between epochs"),
+    _flag("--prefetch-factor", default=2, type=int, help="batches each worker keeps ready"),
+    _flag("--disable-amp", action="store_true", help="full fp32 instead of autocast"),
+    _flag("--amp-dtype", default="bf16", choices=("bf16", "fp16"), help="autocast dtype; only fp16 needs (and gets) a gradient scaler"),
+    _flag("--compile", action="store_true", help="pass the model through torch.compile"),
+    _flag("--compile-backend", default="inductor", type=str, help="torch.compile backend"),
+    _flag("--compile-mode", default=None, type=str, help="torch.compile mode"),
+    _flag("--compile-disable-cudagraphs", action="store_true", help="no CUDA graphs inside the inductor backend"),
+    _flag("--compile-eval", action="store_true", help="evaluate the compiled model too (default: the eager one)"),
+    # multi-process
+    _flag("--sync-bn", dest="sync_bn", action="store_true", help="batch-norm statistics over all ranks"),
+    _flag("--world-size", default=1, type=int, help="number of processes (filled in from the launcher's environment)"),
+    _flag("--dist-url", default="env://", type=str, help="rendezvous URL"),
+    _flag("--local_rank", type=int, help="set by old launchers; leave alone"),
+)

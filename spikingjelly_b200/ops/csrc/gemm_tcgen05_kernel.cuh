@@ -97,6 +97,7 @@ struct ConvGeom {
     int CN;                 // LOADER 1 with MN-major B: filter columns per tap (= Cin); LOADER 2: channels per tap
     int wr0, wr_step, ws0, ws_step, S;
     int scatter, out_H, out_W, out_mul_h, out_mul_w, out_add_h, out_add_w;
+    int debug;              // timing experiments only: 1 = epilogue drains but stores nothing, 2 = no A loads, 4 = no MMAs, 8 = no B loads
     int tiled;              // the gathered operand comes by tiled 4-D loads of (bw x bh x bn) pixel blocks instead of im2col loads
 };
 
@@ -126,6 +127,7 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int c_begin, i
             for (int q = 0; q < 32; ++q) cur[q] = __float_as_uint(__uint_as_float(cur[q]) * alpha);
         }
         const int col0 = n0 + c * 32;
+        if (cg.debug & 1) continue;
         if (g.out_f32) {
             // split-K partial sums / fp32 results: straight from registers, one 128-byte run per row
             if (row < g.M && col0 < g.N) {
@@ -300,6 +302,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     uint8_t* sa = smem + s * L::STAGE_BYTES;
                     uint8_t* sb = sa + L::A_BYTES;
                     if constexpr (LOADER == 1) {
+                        if (cg.debug & 10) {
+                            const int nb = ((cg.debug & 2) ? 0 : L::A_BYTES) + ((cg.debug & 8) ? 0 : L::B_BYTES);
+                            if (nb == 0) { mbar_arrive(full_bar + s); continue; }
+                            mbar_expect_tx(full_bar + s, nb);
+                            const int tap = kb / cpb, chan = (kb - tap * cpb) * 64;
+                            const int th = tap / cg.taps_w, tw = tap - th * cg.taps_w;
+                            if (!(cg.debug & 2)) tma_load_im2col_4d(sa, &tmA, chan, cv_w, cv_h, cv_img, (uint16_t)(tw * cg.dil_w), (uint16_t)(th * cg.dil_h), full_bar + s);
+                            if (!(cg.debug & 8)) tma_load_2d(sb, &tmB, 0, n0, full_bar + s);
+                            continue;
+                        }
                         mbar_expect_tx(full_bar + s, L::STAGE_BYTES);
                         const int tap = kb / cpb, chan = (kb - tap * cpb) * 64;
                         const int th = tap / cg.taps_w, tw = tap - th * cg.taps_w;
@@ -375,6 +387,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                                  : make_smem_desc(sa + j * (UMMA_K * 2), 16, 1024);
                         const uint64_t db = B_MN ? make_smem_desc(sb + j * (UMMA_K * 128), BK * 128, 1024)
                                                  : make_smem_desc(sb + j * (UMMA_K * 2), 16, 1024);
+                        if (LOADER == 1 && (cg.debug & 4)) continue;
                         if constexpr (ES == 2) mma_f16_ss(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
                         else mma_f8_ss(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
                     }
