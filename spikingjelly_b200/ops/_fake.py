@@ -80,3 +80,117 @@ def register() -> None:
     @reg("sjb200::ssa_backward")
     def _(dO, S, L, H, scale):
         return torch.empty_like(S)
+
+    # ------------------------------------------------------------------ neuron scan
+    def _state_dtype(x):
+        return torch.bfloat16 if x.dtype == torch.float8_e4m3fn else x.dtype
+
+    @reg("sjb200::scan_forward")
+    def _(x_seq, v_init, v_init_scalar, r, kind, tau, q0, q1, q2, v_th, v_reset, soft_reset, store_v_seq, pack_bits, save_ckpt):
+        sd = _state_dtype(x_seq)
+        T = x_seq.shape[0]
+        N = x_seq.numel() // T if T else 0
+        chunk = 4 if T <= 4 else 8
+        n_ckpt = (T + chunk - 1) // chunk - 1
+        none = lambda: x_seq.new_empty((0,))
+        return (x_seq.new_empty(x_seq.shape, dtype=sd), x_seq.new_empty(x_seq.shape[1:], dtype=sd),
+                x_seq.new_empty(x_seq.shape, dtype=sd) if store_v_seq else none(),
+                x_seq.new_empty((T, (N + 31) // 32), dtype=torch.int32) if pack_bits else none(),
+                x_seq.new_empty((n_ckpt, N), dtype=torch.float32) if (save_ckpt and n_ckpt > 0) else none())
+
+    @reg("sjb200::scan_backward")
+    def _(grad_spike_seq, grad_v_last, grad_v_seq, x_seq, v_init, v_init_scalar, r, ckpt, kind, tau, q0, q1, q2, v_th, v_reset,
+          soft_reset, sg_id, sg_p0, sg_p1, detach_reset, need_grad_v_init):
+        sd = _state_dtype(x_seq)
+        gvi = x_seq.new_empty(x_seq.shape[1:], dtype=sd) if need_grad_v_init else x_seq.new_empty((0,), dtype=sd)
+        grad_r = x_seq.new_empty((1,), dtype=torch.float32) if r is not None else x_seq.new_empty((0,))
+        return x_seq.new_empty(x_seq.shape, dtype=sd), gvi, grad_r
+
+    # ------------------------------------------------------------------ batch norm + neuron
+    def _bn_four(like, C):
+        return tuple(like.new_empty((C,), dtype=torch.float32) for _ in range(4))
+
+    @reg("sjb200::bn_coefficients")
+    def _(y, gamma, beta, running_mean, running_var, training, momentum, eps):
+        return _bn_four(y, y.shape[-1])
+
+    @reg("sjb200::bn_coefficients_partial")
+    def _(partial, rows, gamma, beta, running_mean, running_var, momentum, eps):
+        return _bn_four(partial, partial.shape[-1])
+
+    @reg("sjb200::bn_lif_forward")
+    def _(y, scale, shift, residual, kind, tau, v_th, v_reset, soft_reset, v_init, save_ckpt):
+        T = y.shape[0]
+        n_ckpt = (T + 3) // 4 - 1
+        ckpt = y.new_empty((n_ckpt, y.numel() // T), dtype=torch.float32) if (save_ckpt and n_ckpt > 0) else y.new_empty((0,), dtype=torch.float32)
+        return torch.empty_like(y), ckpt
+
+    @reg("sjb200::bn_lif_backward")
+    def _(g_out, y, scale, shift, mean, invstd, gamma, ckpt, training, kind, tau, v_th, v_reset, soft_reset, v_init, sg_id, sg_p0,
+          sg_p1, detach_reset):
+        C = y.shape[-1]
+        return torch.empty_like(y), y.new_empty((C,), dtype=torch.float32), y.new_empty((C,), dtype=torch.float32)
+
+    @reg("sjb200::bn_pool_lif_forward")
+    def _(y, scale, shift, T, is_static, kind, tau, v_th, v_reset, soft_reset, v_init):
+        nb, h, w, c = y.shape
+        oh, ow = (h - 1) // 2 + 1, (w - 1) // 2 + 1
+        b = nb if is_static else nb // T
+        return y.new_empty((T, b, oh, ow, c)), y.new_empty((nb, oh, ow, c), dtype=torch.uint8)
+
+    @reg("sjb200::bn_pool_lif_backward")
+    def _(g_out, y, idx, scale, shift, mean, invstd, gamma, training, T, is_static, kind, tau, v_th, v_reset, soft_reset, v_init,
+          sg_id, sg_p0, sg_p1, detach_reset):
+        C = y.shape[-1]
+        return torch.empty_like(y), y.new_empty((C,), dtype=torch.float32), y.new_empty((C,), dtype=torch.float32)
+
+    # ------------------------------------------------------------------ implicit-GEMM convolution
+    def _conv_extent(size, pad, k, dil, stride):
+        return (size + 2 * pad - dil * (k - 1) - 1) // stride + 1
+
+    @reg("sjb200::conv2d_nhwc_forward")
+    def _(x, w, stride, padding, dilation, want_stats):
+        n, h, wd, _ = x.shape
+        co, r, s_, _ = w.shape
+        oh, ow = _conv_extent(h, padding[0], r, dilation[0], stride[0]), _conv_extent(wd, padding[1], s_, dilation[1], stride[1])
+        rows = n * oh * ow
+        stats = x.new_empty(((rows + 127) // 128 * 4, 2, co), dtype=torch.float32) if want_stats else x.new_empty((0,), dtype=torch.float32)
+        return x.new_empty((rows, co)), stats
+
+    @reg("sjb200::conv2d_nhwc_dgrad")
+    def _(gy, w, H, W, stride, padding):
+        co, r, s_, ci = w.shape
+        oh, ow = _conv_extent(H, padding[0], r, 1, stride[0]), _conv_extent(W, padding[1], s_, 1, stride[1])
+        return gy.new_empty((gy.numel() // (oh * ow * co), H, W, ci))
+
+    @reg("sjb200::conv2d_nhwc_wgrad")
+    def _(x, gy, R, S, stride, padding, dilation):
+        n, h, wd, ci = x.shape
+        oh, ow = _conv_extent(h, padding[0], R, dilation[0], stride[0]), _conv_extent(wd, padding[1], S, dilation[1], stride[1])
+        return x.new_empty((gy.numel() // (n * oh * ow), R, S, ci), dtype=torch.float32)
+
+    # ------------------------------------------------------------------ collectives and the fused tensor-parallel path
+    @reg("sjb200::allreduce_bucket")
+    def _(bucket, buf_ptrs, sig_ptrs, multicast_ptr, rank, epoch, scale, blocks, status, timeout_s, wire=0):
+        return None
+
+    @reg("sjb200::spike_gemm")
+    def _(a_ptrs, a_pitch, M, K, w, rows_per_t, rows_per_src, rank, push_ptrs, slot_elems):
+        # with push pointers the partial product is scattered to its owners and an empty tensor comes back
+        return w.new_empty((0,)) if len(push_ptrs) > 0 else w.new_empty((M, w.shape[0]))
+
+    @reg("sjb200::lif_pack")
+    def _(x, out_ptr, pitch, tau, v_th):
+        return None
+
+    @reg("sjb200::rmsnorm_lif_pack")
+    def _(h, weight, out_ptrs, pitch, eps, tau, v_th):
+        return None
+
+    @reg("sjb200::tp_reduce_residual")
+    def _(h, stage_ptr, slot_elems, world):
+        return None
+
+    @reg("sjb200::tp_barrier")
+    def _(sig_ptrs, rank, epoch, status, timeout_s):
+        return None

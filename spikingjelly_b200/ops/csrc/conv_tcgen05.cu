@@ -148,7 +148,6 @@ std::tuple<at::Tensor, at::Tensor> conv2d_nhwc_forward(const at::Tensor& x, cons
     const bool tiled = std::getenv("SJB200_CONV_TILED") != nullptr && s.sh == 1 && s.sw == 1 && s.Wo <= 128 && 128 % s.Wo == 0 &&
                        s.Ho % (128 / s.Wo) == 0;
     cg.tiled = tiled ? 1 : 0;
-    if (const char* e = std::getenv("SJB200_CONV_DEBUG")) cg.debug = std::atoi(e);
     const CUtensorMap ta = tiled ? make_tiled4d_map(x.data_ptr(), s.Nb, s.H, s.W, s.C, (int)s.Wo, (int)(128 / s.Wo), 1, 1, 1, bf16)
                                  : make_im2col_map(x.data_ptr(), s.Nb, s.H, s.W, s.C, -s.ph, -s.pw, s.ph - s.dh * ((int)s.R - 1),
                                                    s.pw - s.dw * ((int)s.S - 1), s.sh, s.sw, BM, bf16);

@@ -97,7 +97,6 @@ struct ConvGeom {
     int CN;                 // LOADER 1 with MN-major B: filter columns per tap (= Cin); LOADER 2: channels per tap
     int wr0, wr_step, ws0, ws_step, S;
     int scatter, out_H, out_W, out_mul_h, out_mul_w, out_add_h, out_add_w;
-    int debug;              // timing experiments only: 1 = epilogue drains but stores nothing, 2 = no A loads, 4 = no MMAs, 8 = no B loads
     int tiled;              // the gathered operand comes by tiled 4-D loads of (bw x bh x bn) pixel blocks instead of im2col loads
 };
 
@@ -127,7 +126,6 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int c_begin, i
             for (int q = 0; q < 32; ++q) cur[q] = __float_as_uint(__uint_as_float(cur[q]) * alpha);
         }
         const int col0 = n0 + c * 32;
-        if (cg.debug & 1) continue;
         if (g.out_f32) {
             // split-K partial sums / fp32 results: straight from registers, one 128-byte run per row
             if (row < g.M && col0 < g.N) {
@@ -260,10 +258,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
+    // The producer and the MMA issuer are single threads: their loops run at one dependent instruction every few
+    // cycles, so the instruction count per k-block IS the time per k-block when tiles are small.  Both keep the ring
+    // position (stage, phase, shared-memory addresses, descriptor words) in registers and update it by increments;
+    // nothing in the k-block loops divides or rebuilds a 64-bit descriptor.
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t full_base = smem_u32(full_bar), empty_base = smem_u32(empty_bar);
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t stage = 0, phase = 0;                         // ring position, carried across tiles
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
                 const int split = tile / tiles_mn, mn = tile % tiles_mn;
                 int tm, tn;
@@ -275,12 +279,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 // (tap, channel) each 64-column chunk of the tile is (LOADER 2)
                 int cv_img = 0, cv_h = 0, cv_w = 0, cv_valid = BN / 64;
                 int cv_chan[BN / 64], cv_offw[BN / 64], cv_offh[BN / 64];
+                int tap_h = 0, tap_w = 0, chan = 0;                // LOADER 1: position inside the contraction
+                int px_img = 0, px_i = 0, px_j = 0;                // LOADER 2: first pixel of the k-block on the traversal grid
                 if constexpr (LOADER == 1) {
                     const int per_img = cg.Ht * cg.Wt;
                     cv_img = m0 / per_img;
                     const int rem = m0 - cv_img * per_img, i = rem / cg.Wt;
                     cv_h = cg.base_h + i * cg.step_h;
                     cv_w = cg.base_w + (rem - i * cg.Wt) * cg.step_w;
+                    const int cpb = cg.CA / 64, tap = kb0 / cpb;
+                    chan = (kb0 - tap * cpb) * 64;
+                    tap_h = tap / cg.taps_w;
+                    tap_w = tap - tap_h * cg.taps_w;
                 }
                 if constexpr (LOADER == 2) {
                     cv_valid = 0;
@@ -293,69 +303,63 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         cv_offw[c] = (tap - th * cg.taps_w) * cg.dil_w;
                         if (nn < g.N) cv_valid = c + 1;
                     }
+                    const int p0 = kb0 * BK, per_img = cg.Ht * cg.Wt;
+                    px_img = p0 / per_img;
+                    const int rem = p0 - px_img * per_img;
+                    px_i = rem / cg.Wt;
+                    px_j = rem - px_i * cg.Wt;
                 }
-                const int cpb = LOADER == 1 ? cg.CA / 64 : 1;     // k-blocks per filter tap
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    if (!mbar_wait_bounded(empty_bar + s, ph ^ 1)) { report(status, WAIT_EMPTY, s); *abort_flag = 1; break; }
-                    uint8_t* sa = smem + s * L::STAGE_BYTES;
+                int k0 = kb0 * BKE;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    uint64_t* const fb = full_bar + stage;
+                    if (!mbar_try_wait(empty_bar + stage, phase ^ 1) && !mbar_wait_bounded(empty_bar + stage, phase ^ 1)) {
+                        report(status, WAIT_EMPTY, stage); *abort_flag = 1; break;
+                    }
+                    uint8_t* sa = smem + stage * L::STAGE_BYTES;
                     uint8_t* sb = sa + L::A_BYTES;
                     if constexpr (LOADER == 1) {
-                        if (cg.debug & 10) {
-                            const int nb = ((cg.debug & 2) ? 0 : L::A_BYTES) + ((cg.debug & 8) ? 0 : L::B_BYTES);
-                            if (nb == 0) { mbar_arrive(full_bar + s); continue; }
-                            mbar_expect_tx(full_bar + s, nb);
-                            const int tap = kb / cpb, chan = (kb - tap * cpb) * 64;
-                            const int th = tap / cg.taps_w, tw = tap - th * cg.taps_w;
-                            if (!(cg.debug & 2)) tma_load_im2col_4d(sa, &tmA, chan, cv_w, cv_h, cv_img, (uint16_t)(tw * cg.dil_w), (uint16_t)(th * cg.dil_h), full_bar + s);
-                            if (!(cg.debug & 8)) tma_load_2d(sb, &tmB, 0, n0, full_bar + s);
-                            continue;
-                        }
-                        mbar_expect_tx(full_bar + s, L::STAGE_BYTES);
-                        const int tap = kb / cpb, chan = (kb - tap * cpb) * 64;
-                        const int th = tap / cg.taps_w, tw = tap - th * cg.taps_w;
-                        if (cg.tiled) tma_load_4d(sa, &tmA, chan, cv_w + tw * cg.dil_w, cv_h + th * cg.dil_h, cv_img, full_bar + s);
-                        else tma_load_im2col_4d(sa, &tmA, chan, cv_w, cv_h, cv_img, (uint16_t)(tw * cg.dil_w), (uint16_t)(th * cg.dil_h),
-                                                full_bar + s);
-                        const int wtap = (cg.wr0 + cg.wr_step * th) * cg.S + (cg.ws0 + cg.ws_step * tw);
+                        mbar_expect_tx(fb, L::STAGE_BYTES);
+                        if (cg.tiled) tma_load_4d(sa, &tmA, chan, cv_w + tap_w * cg.dil_w, cv_h + tap_h * cg.dil_h, cv_img, fb);
+                        else tma_load_im2col_4d(sa, &tmA, chan, cv_w, cv_h, cv_img, (uint16_t)(tap_w * cg.dil_w), (uint16_t)(tap_h * cg.dil_h), fb);
+                        const int wtap = (cg.wr0 + cg.wr_step * tap_h) * cg.S + (cg.ws0 + cg.ws_step * tap_w);
                         if (B_MN) {
 #pragma unroll
                             for (int c = 0; c < BN / 64; ++c)
-                                tma_load_2d(sb + c * (BK * 128), &tmB, wtap * cg.CN + n0 + c * 64, chan, full_bar + s);
+                                tma_load_2d(sb + c * (BK * 128), &tmB, wtap * cg.CN + n0 + c * 64, chan, fb);
                         } else {
-                            tma_load_2d(sb, &tmB, wtap * cg.CA + chan, n0, full_bar + s);
+                            tma_load_2d(sb, &tmB, wtap * cg.CA + chan, n0, fb);
                         }
-                        continue;
-                    }
-                    if constexpr (LOADER == 2) {
-                        mbar_expect_tx(full_bar + s, L::A_BYTES + cv_valid * (BK * 128));
-                        const int p0 = kb * BK, per_img = cg.Ht * cg.Wt;
-                        const int img = p0 / per_img, rem = p0 - img * per_img, i = rem / cg.Wt;
-                        const int ph0 = cg.base_h + i * cg.step_h, pw0 = cg.base_w + (rem - i * cg.Wt) * cg.step_w;
+                        chan += 64;
+                        if (chan == cg.CA) { chan = 0; if (++tap_w == cg.taps_w) { tap_w = 0; ++tap_h; } }
+                    } else if constexpr (LOADER == 2) {
+                        mbar_expect_tx(fb, L::A_BYTES + cv_valid * (BK * 128));
+                        const int ph0 = cg.base_h + px_i * cg.step_h, pw0 = cg.base_w + px_j * cg.step_w;
 #pragma unroll
-                        for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmA, m0 + c * 64, p0, full_bar + s);
+                        for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmA, m0 + c * 64, kb * BK, fb);
 #pragma unroll
                         for (int c = 0; c < BN / 64; ++c)
                             if (c < cv_valid)
-                                tma_load_im2col_4d(sb + c * (BK * 128), &tmB, cv_chan[c], pw0, ph0, img, (uint16_t)cv_offw[c],
-                                                   (uint16_t)cv_offh[c], full_bar + s);
-                        continue;
-                    }
-                    mbar_expect_tx(full_bar + s, L::STAGE_BYTES);
-                    const int k0 = kb * BKE;
-                    if (A_MN) {
-#pragma unroll
-                        for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmA, m0 + c * 64, k0, full_bar + s);
+                                tma_load_im2col_4d(sb + c * (BK * 128), &tmB, cv_chan[c], pw0, ph0, px_img, (uint16_t)cv_offw[c],
+                                                   (uint16_t)cv_offh[c], fb);
+                        px_j += BK;                                  // 64 pixels further along the traversal
+                        while (px_j >= cg.Wt) { px_j -= cg.Wt; if (++px_i == cg.Ht) { px_i = 0; ++px_img; } }
                     } else {
-                        tma_load_2d(sa, &tmA, k0, m0, full_bar + s);
-                    }
-                    if (B_MN) {
+                        mbar_expect_tx(fb, L::STAGE_BYTES);
+                        if (A_MN) {
 #pragma unroll
-                        for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), &tmB, n0 + c * 64, k0, full_bar + s);
-                    } else {
-                        tma_load_2d(sb, &tmB, k0, n0, full_bar + s);
+                            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmA, m0 + c * 64, k0, fb);
+                        } else {
+                            tma_load_2d(sa, &tmA, k0, m0, fb);
+                        }
+                        if (B_MN) {
+#pragma unroll
+                            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), &tmB, n0 + c * 64, k0, fb);
+                        } else {
+                            tma_load_2d(sb, &tmB, k0, n0, fb);
+                        }
+                        k0 += BKE;
                     }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
         }
@@ -363,7 +367,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // -------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             const uint32_t idesc = make_idesc_f16(g.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
-            uint32_t it = 0, tl = 0;
+            // Descriptor words.  High word: stride offset 1024 B, version 1, 128-byte swizzle.  Low word: start address >> 4
+            // plus the leading-dimension offset (16 B for K-major; the distance between 64-element chunks for MN-major).
+            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            constexpr uint32_t kLboA = A_MN ? ((BK * 128u) >> 4) : 1u, kLboB = B_MN ? ((BK * 128u) >> 4) : 1u;
+            constexpr uint32_t kStepA = (A_MN ? UMMA_K * 128u : UMMA_K * 2u) >> 4, kStepB = (B_MN ? UMMA_K * 128u : UMMA_K * 2u) >> 4;
+            const uint32_t a_lo0 = (smem_base >> 4) | (kLboA << 16), b_lo0 = ((smem_base + L::A_BYTES) >> 4) | (kLboB << 16);
+            uint32_t stage = 0, phase = 0, a_lo = a_lo0, b_lo = b_lo0, tl = 0;
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tl) {
                 const int split = tile / tiles_mn;
                 const int kb0 = split * g.kb_per_split;
@@ -372,26 +382,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (!mbar_wait_bounded(tempty_bar + acc, acc_ph ^ 1)) { report(status, WAIT_TMEM_EMPTY, tile); *abort_flag = 1; break; }
                 fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    if (!mbar_wait_bounded(full_bar + s, ph)) { report(status, WAIT_FULL, s); *abort_flag = 1; break; }
+                uint32_t accumulate = 0;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_try_wait(full_bar + stage, phase) && !mbar_wait_bounded(full_bar + stage, phase)) {
+                        report(status, WAIT_FULL, stage); *abort_flag = 1; break;
+                    }
                     fence_after_sync();
-                    const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
-                    const uint32_t sb = sa + L::A_BYTES;
 #pragma unroll
                     for (int j = 0; j < BK / UMMA_K; ++j) {
-                        // K-major: 16 elements = 32 B further along the swizzled row;
-                        // MN-major: 16 k-rows of 128 B further down.
-                        const uint64_t da = A_MN ? make_smem_desc(sa + j * (UMMA_K * 128), BK * 128, 1024)
-                                                 : make_smem_desc(sa + j * (UMMA_K * 2), 16, 1024);
-                        const uint64_t db = B_MN ? make_smem_desc(sb + j * (UMMA_K * 128), BK * 128, 1024)
-                                                 : make_smem_desc(sb + j * (UMMA_K * 2), 16, 1024);
-                        if (LOADER == 1 && (cg.debug & 4)) continue;
-                        if constexpr (ES == 2) mma_f16_ss(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
-                        else mma_f8_ss(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+                        // K-major: 16 elements = 32 B further along the swizzled row; MN-major: 16 k-rows of 128 B further down
+                        if constexpr (ES == 2) mma_f16_ss_words(d_tmem, a_lo + j * kStepA, b_lo + j * kStepB, kDescHi, idesc, accumulate);
+                        else mma_f8_ss_words(d_tmem, a_lo + j * kStepA, b_lo + j * kStepB, kDescHi, idesc, accumulate);
+                        accumulate = 1;
                     }
-                    mma_commit(empty_bar + s);     // stage reusable once these MMAs have read it
+                    mma_commit(empty_bar + stage);     // stage reusable once these MMAs have read it
+                    a_lo += L::STAGE_BYTES >> 4;
+                    b_lo += L::STAGE_BYTES >> 4;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
                 }
                 mma_commit(tfull_bar + acc);       // accumulator complete
             }
@@ -507,7 +514,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (one thread in each CTA)
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t stage = 0, phase = 0;
+            const uint32_t full0 = map_to_cta(smem_u32(full_bar), 0);          // the full barriers live in the pair's first CTA
             for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs) {
                 const int split = tile / tiles_mn;
                 int tm, tn;
@@ -515,15 +523,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const int m0 = tm * (2 * BM) + (int)rank * BM;
                 const int nb0 = tn * BN + (int)rank * (BN / 2);                    // this CTA's half of the B columns
                 const int kb0 = split * g.kb_per_split, kb1 = min(kb_total, kb0 + g.kb_per_split);
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    if (!mbar_wait_bounded(empty_bar + s, ph ^ 1)) { report(status, WAIT_EMPTY, s); *abort_flag = 1; break; }
-                    uint8_t* sa = smem + s * L::STAGE_BYTES;
+                int k0 = kb0 * BKE;
+                for (int kb = kb0; kb < kb1; ++kb, k0 += BKE) {
+                    if (!mbar_try_wait(empty_bar + stage, phase ^ 1) && !mbar_wait_bounded(empty_bar + stage, phase ^ 1)) {
+                        report(status, WAIT_EMPTY, stage); *abort_flag = 1; break;
+                    }
+                    uint8_t* sa = smem + stage * L::STAGE_BYTES;
                     uint8_t* sb = sa + L::A_BYTES;
-                    if (first) mbar_expect_tx(full_bar + s, 2 * L::STAGE_BYTES);
-                    const uint32_t bar = map_to_cta(smem_u32(full_bar + s), 0);
-                    const int k0 = kb * BKE;
+                    if (first) mbar_expect_tx(full_bar + stage, 2 * L::STAGE_BYTES);
+                    const uint32_t bar = full0 + stage * 8;
                     if (A_MN) {
 #pragma unroll
                         for (int c = 0; c < BM / 64; ++c) tma_load_2d_pair(sa + c * (BK * 128), &tmA, m0 + c * 64, k0, bar);
@@ -536,6 +544,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     } else {
                         tma_load_2d_pair(sb, &tmB, k0, nb0, bar);
                     }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
         }
@@ -543,7 +552,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // -------------------------------------------------------------- MMA issuer (first CTA only)
         if (lane == 0 && first) {
             const uint32_t idesc = make_idesc_f16(g.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, 2 * BM, BN);
-            uint32_t it = 0, tl = 0;
+            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            constexpr uint32_t kLboA = A_MN ? ((BK * 128u) >> 4) : 1u, kLboB = B_MN ? ((BK * 128u) >> 4) : 1u;
+            constexpr uint32_t kStepA = (A_MN ? UMMA_K * 128u : UMMA_K * 2u) >> 4, kStepB = (B_MN ? UMMA_K * 128u : UMMA_K * 2u) >> 4;
+            const uint32_t smem_base = smem_u32(smem);
+            const uint32_t a_lo0 = (smem_base >> 4) | (kLboA << 16), b_lo0 = ((smem_base + L::A_BYTES) >> 4) | (kLboB << 16);
+            const uint32_t empty_self = smem_u32(empty_bar), empty_peer = map_to_cta(empty_self, 1);
+            uint32_t stage = 0, phase = 0, a_lo = a_lo0, b_lo = b_lo0, tl = 0;
             for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs, ++tl) {
                 const int split = tile / tiles_mn;
                 const int kb0 = split * g.kb_per_split, kb1 = min(kb_total, kb0 + g.kb_per_split);
@@ -551,25 +566,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (!mbar_wait_bounded(tempty_bar + acc, acc_ph ^ 1)) { report(status, WAIT_TMEM_EMPTY, tile); *abort_flag = 1; break; }
                 fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    if (!mbar_wait_bounded(full_bar + s, ph)) { report(status, WAIT_FULL, s); *abort_flag = 1; break; }
+                uint32_t accumulate = 0;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_try_wait(full_bar + stage, phase) && !mbar_wait_bounded(full_bar + stage, phase)) {
+                        report(status, WAIT_FULL, stage); *abort_flag = 1; break;
+                    }
                     fence_after_sync();
-                    const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
-                    const uint32_t sb = sa + L::A_BYTES;
 #pragma unroll
                     for (int j = 0; j < BK / UMMA_K; ++j) {
-                        const uint64_t da = A_MN ? make_smem_desc(sa + j * (UMMA_K * 128), BK * 128, 1024)
-                                                 : make_smem_desc(sa + j * (UMMA_K * 2), 16, 1024);
-                        const uint64_t db = B_MN ? make_smem_desc(sb + j * (UMMA_K * 128), BK * 128, 1024)
-                                                 : make_smem_desc(sb + j * (UMMA_K * 2), 16, 1024);
-                        if constexpr (ES == 2) mma_f16_ss_pair(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
-                        else mma_f8_ss_pair(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+                        if constexpr (ES == 2) mma_f16_ss_pair_words(d_tmem, a_lo + j * kStepA, b_lo + j * kStepB, kDescHi, idesc, accumulate);
+                        else mma_f8_ss_pair_words(d_tmem, a_lo + j * kStepA, b_lo + j * kStepB, kDescHi, idesc, accumulate);
+                        accumulate = 1;
                     }
-                    const uint32_t eb = smem_u32(empty_bar + s);
-                    mma_commit_pair(eb);                       // this CTA's stage is reusable ...
-                    mma_commit_pair(map_to_cta(eb, 1));        // ... and the partner's
+                    mma_commit_pair(empty_self + stage * 8);          // this CTA's stage is reusable ...
+                    mma_commit_pair(empty_peer + stage * 8);          // ... and the partner's
+                    a_lo += L::STAGE_BYTES >> 4;
+                    b_lo += L::STAGE_BYTES >> 4;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
                 }
                 const uint32_t tb = smem_u32(tfull_bar + acc);
                 mma_commit_pair(tb);

@@ -1,0 +1,49 @@
+"""``torch.compile`` of networks that run on the native kernels: the custom operators carry fake (shape) implementations,
+so Dynamo / AOT autograd can trace through the autograd functions that wrap them; compiled results equal eager ones
+(role of ``test/activation_based/test_compile_compat.py`` of the reference)."""
+import pytest
+import torch
+import torch.nn as nn
+
+pytestmark = pytest.mark.gpu
+
+
+def _net(dev):
+    from spikingjelly_b200.activation_based import functional, layer, neuron, surrogate
+    torch.manual_seed(0)
+    net = nn.Sequential(
+        layer.Linear(48, 64), neuron.LIFNode(surrogate_function=surrogate.ATan(), detach_reset=True, backend="cuda"),
+        layer.Linear(64, 32), neuron.IFNode(surrogate_function=surrogate.Sigmoid(), backend="cuda"),
+        layer.Linear(32, 10), neuron.ParametricLIFNode(surrogate_function=surrogate.ATan(), backend="cuda")).to(dev)
+    functional.set_step_mode(net, "m")
+    return net
+
+
+@pytest.mark.parametrize("backend", ["aot_eager", "inductor"])
+def test_compiled_network_matches_eager(backend):
+    from spikingjelly_b200.activation_based import functional
+    dev = torch.device("cuda")
+    net = _net(dev)
+    x = torch.rand(5, 7, 48, device=dev)
+    y = torch.rand(7, 10, device=dev)
+
+    def step(model):
+        functional.reset_net(net)
+        net.zero_grad(set_to_none=True)
+        out = model(x)
+        loss = ((out.mean(0) - y) ** 2).mean()
+        loss.backward()
+        functional.reset_net(net)
+        return out.detach().clone(), [p.grad.detach().clone() for p in net.parameters()]
+
+    out_e, grads_e = step(net)
+    try:
+        compiled = torch.compile(net, backend=backend)
+        out_c, grads_c = step(compiled)
+    except Exception as exc:        # a missing host compiler for inductor is not this package's concern
+        if backend == "inductor" and ("compiler" in str(exc).lower() or "triton" in str(exc).lower()):
+            pytest.skip(f"inductor unavailable here: {type(exc).__name__}")
+        raise
+    assert torch.equal(out_e, out_c)                       # spikes are 0 / 1: any difference would be a flipped spike
+    for ge, gc in zip(grads_e, grads_c):
+        torch.testing.assert_close(ge, gc, rtol=1e-5, atol=1e-6)
