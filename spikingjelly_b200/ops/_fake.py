@@ -191,6 +191,18 @@ def register() -> None:
     def _(h, stage_ptr, slot_elems, world):
         return None
 
+    @reg("sjb200::tp_push_chunks")
+    def _(src, dst_ptrs, chunks, dst_stride_bytes, dst_offset_bytes):
+        return None
+
+    @reg("sjb200::tp_reduce_chunks")
+    def _(src_ptrs, out, chunks, src_stride_elems, src_offset_elems):
+        return None
+
+    @reg("sjb200::gemm_16bit_into")
+    def _(a, b, a_mn, b_mn, out):
+        return out
+
     @reg("sjb200::tp_barrier")
     def _(sig_ptrs, rank, epoch, status, timeout_s):
         return None

@@ -65,21 +65,6 @@ CUtensorMap make_im2col_map(const void* base, int64_t Nb, int64_t H, int64_t W, 
     return m;
 }
 
-// Tiled 4-D map over a contiguous NHWC tensor: box = 64 channels x bw x bh x bn pixels, traversal steps as given.
-CUtensorMap make_tiled4d_map(const void* base, int64_t Nb, int64_t H, int64_t W, int64_t C, int bw, int bh, int bn, int step_h, int step_w,
-                             bool bf16) {
-    CUtensorMap m;
-    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)Nb};
-    cuuint64_t strides[3] = {(cuuint64_t)C * 2, (cuuint64_t)W * C * 2, (cuuint64_t)H * W * C * 2};
-    cuuint32_t box[4] = {64u, (cuuint32_t)(bw * step_w), (cuuint32_t)(bh * step_h), (cuuint32_t)bn};
-    cuuint32_t estr[4] = {1u, (cuuint32_t)step_w, (cuuint32_t)step_h, 1u};
-    CUresult r = encode_fn()(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base),
-                             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (4-D) failed with code ", (int)r);
-    return m;
-}
-
 int64_t out_extent(int64_t in, int64_t pad, int64_t k, int64_t dil, int64_t stride) {
     return (in + 2 * pad - dil * (k - 1) - 1) / stride + 1;
 }
@@ -143,14 +128,8 @@ std::tuple<at::Tensor, at::Tensor> conv2d_nhwc_forward(const at::Tensor& x, cons
     cg.taps_h = (int)s.R; cg.taps_w = (int)s.S; cg.dil_h = s.dh; cg.dil_w = s.dw;
     cg.CA = (int)s.C; cg.CN = (int)s.C;
     cg.wr0 = 0; cg.wr_step = 1; cg.ws0 = 0; cg.ws_step = 1; cg.S = (int)s.S;
-    // experiment: when a 128-pixel run of the linear output order is exactly Wo x (128 / Wo) rows of one image, the gather
-    // can be a tiled 4-D load
-    const bool tiled = std::getenv("SJB200_CONV_TILED") != nullptr && s.sh == 1 && s.sw == 1 && s.Wo <= 128 && 128 % s.Wo == 0 &&
-                       s.Ho % (128 / s.Wo) == 0;
-    cg.tiled = tiled ? 1 : 0;
-    const CUtensorMap ta = tiled ? make_tiled4d_map(x.data_ptr(), s.Nb, s.H, s.W, s.C, (int)s.Wo, (int)(128 / s.Wo), 1, 1, 1, bf16)
-                                 : make_im2col_map(x.data_ptr(), s.Nb, s.H, s.W, s.C, -s.ph, -s.pw, s.ph - s.dh * ((int)s.R - 1),
-                                                   s.pw - s.dw * ((int)s.S - 1), s.sh, s.sw, BM, bf16);
+    const CUtensorMap ta = make_im2col_map(x.data_ptr(), s.Nb, s.H, s.W, s.C, -s.ph, -s.pw, s.ph - s.dh * ((int)s.R - 1),
+                                           s.pw - s.dw * ((int)s.S - 1), s.sh, s.sw, BM, bf16);
     const CUtensorMap tb = make_map(w.data_ptr(), N, K, K, BN, bf16);
     const CUtensorMap td = make_map(out.data_ptr(), M, N, N, 32, bf16, 32);
     KernelStatus* stp = reinterpret_cast<KernelStatus*>(status_word(x.device()).data_ptr<int>());

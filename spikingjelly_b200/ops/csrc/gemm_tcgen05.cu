@@ -26,7 +26,7 @@ using namespace tc;
 //   b_mn == false: `b` is [N, K] (K contiguous);  b_mn == true: `b` is [K, N] (N contiguous)
 //   out_f32: result dtype fp32 instead of the input dtype;  split_k: 0 = choose, else forced
 static at::Tensor gemm_16bit_impl(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, bool out_f32, int64_t split_k,
-                                  at::Tensor* stats) {
+                                  at::Tensor* stats, const at::Tensor* into = nullptr) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda(), "gemm_16bit: CUDA tensors required");
     TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm_16bit: 2-D operands required");
     TORCH_CHECK(a.scalar_type() == b.scalar_type() && (a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf),
@@ -85,7 +85,16 @@ static at::Tensor gemm_16bit_impl(const at::Tensor& a, const at::Tensor& b, bool
                                 : make_map(B.data_ptr(), N, K, B.stride(0), use_pair ? kPairBN / 2 : BN, bf16);
 
     auto opts = a.options();
-    at::Tensor out = at::empty({M, N}, out_f32 ? opts.dtype(at::kFloat) : opts);
+    at::Tensor out;
+    if (into != nullptr) {
+        // the caller's buffer (e.g. one in symmetric memory that peers will read): same shape, dtype and device, contiguous
+        TORCH_CHECK(into->is_cuda() && into->device() == a.device() && into->is_contiguous() && into->numel() == M * N &&
+                    into->scalar_type() == (out_f32 ? at::kFloat : a.scalar_type()) &&
+                    reinterpret_cast<uintptr_t>(into->data_ptr()) % 16 == 0, "gemm_16bit_into: output buffer does not fit the product");
+        out = into->view({M, N});
+    } else {
+        out = at::empty({M, N}, out_f32 ? opts.dtype(at::kFloat) : opts);
+    }
     at::Tensor scratch;
     void* dptr = out.data_ptr();
     if (splits > 1) {
@@ -132,6 +141,12 @@ static at::Tensor gemm_16bit_impl(const at::Tensor& a, const at::Tensor& b, bool
 
 at::Tensor gemm_16bit(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, bool out_f32, int64_t split_k) {
     return gemm_16bit_impl(a, b, a_mn, b_mn, out_f32, split_k, nullptr);
+}
+
+// The same product written into `out` (shape [M, N], the operands' dtype or fp32): lets a caller place the result in a
+// buffer of its choosing, e.g. symmetric memory that other ranks read afterwards.
+at::Tensor gemm_16bit_into(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, at::Tensor out) {
+    return gemm_16bit_impl(a, b, a_mn, b_mn, out.scalar_type() == at::kFloat, 0, nullptr, &out);
 }
 
 // The same product plus partial[blk][0 | 1][n] = sum | sum of squares of D[32 * blk .. 32 * blk + 31][n] (rows past M
@@ -235,6 +250,7 @@ std::vector<int64_t> gemm_status(const at::Tensor& like) {
 TORCH_LIBRARY_FRAGMENT(sjb200, m) {
     m.def("gemm_16bit(Tensor a, Tensor b, bool a_mn, bool b_mn, bool out_f32, int split_k) -> Tensor");
     m.def("gemm_16bit_stats(Tensor a, Tensor b, bool a_mn, bool b_mn) -> (Tensor, Tensor)");
+    m.def("gemm_16bit_into(Tensor a, Tensor b, bool a_mn, bool b_mn, Tensor(a!) out) -> Tensor(a!)");
     m.def("gemm_fp8(Tensor a, Tensor b, Tensor? alpha, bool out_f32, int split_k) -> Tensor");
     m.def("gemm_status(Tensor like) -> int[]");
     m.def("gemm_set_pair_mode(int mode) -> int");
@@ -245,6 +261,7 @@ TORCH_LIBRARY_IMPL(sjb200, CompositeExplicitAutograd, m) {
 TORCH_LIBRARY_IMPL(sjb200, CUDA, m) {
     m.impl("gemm_16bit", &sjb200::gemm_16bit);
     m.impl("gemm_16bit_stats", &sjb200::gemm_16bit_stats);
+    m.impl("gemm_16bit_into", &sjb200::gemm_16bit_into);
     m.impl("gemm_fp8", &sjb200::gemm_fp8);
     m.impl("gemm_status", &sjb200::gemm_status);
 }

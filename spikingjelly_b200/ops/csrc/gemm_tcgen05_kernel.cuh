@@ -38,6 +38,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;          // 64 x 2 B = one 128 B swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 320;
+constexpr int kSpinPolls = 512;            // non-suspending probes of a ring barrier before falling back to the bounded, suspending wait
 constexpr int kWarpStageBytes = 32 * 64;   // one epilogue warp's staging buffer: 32 rows x 32 16-bit columns   // 10 warps: producer, mma, 2 x 4 epilogue (each group of four drains half of the columns)
 
 template <int BN, int STAGES>
@@ -97,7 +98,6 @@ struct ConvGeom {
     int CN;                 // LOADER 1 with MN-major B: filter columns per tap (= Cin); LOADER 2: channels per tap
     int wr0, wr_step, ws0, ws_step, S;
     int scatter, out_H, out_W, out_mul_h, out_mul_w, out_add_h, out_add_w;
-    int tiled;              // the gathered operand comes by tiled 4-D loads of (bw x bh x bn) pixel blocks instead of im2col loads
 };
 
 // Epilogue of one output tile for one warp: drains NCHUNK chunks of 32 accumulator columns (this warp's 32 TMEM lanes =
@@ -312,15 +312,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 int k0 = kb0 * BKE;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     uint64_t* const fb = full_bar + stage;
-                    if (!mbar_try_wait(empty_bar + stage, phase ^ 1) && !mbar_wait_bounded(empty_bar + stage, phase ^ 1)) {
+                    if (!mbar_spin(empty_bar + stage, phase ^ 1, kSpinPolls) && !mbar_wait_bounded(empty_bar + stage, phase ^ 1)) {
                         report(status, WAIT_EMPTY, stage); *abort_flag = 1; break;
                     }
                     uint8_t* sa = smem + stage * L::STAGE_BYTES;
                     uint8_t* sb = sa + L::A_BYTES;
                     if constexpr (LOADER == 1) {
                         mbar_expect_tx(fb, L::STAGE_BYTES);
-                        if (cg.tiled) tma_load_4d(sa, &tmA, chan, cv_w + tap_w * cg.dil_w, cv_h + tap_h * cg.dil_h, cv_img, fb);
-                        else tma_load_im2col_4d(sa, &tmA, chan, cv_w, cv_h, cv_img, (uint16_t)(tap_w * cg.dil_w), (uint16_t)(tap_h * cg.dil_h), fb);
+                        tma_load_im2col_4d(sa, &tmA, chan, cv_w, cv_h, cv_img, (uint16_t)(tap_w * cg.dil_w), (uint16_t)(tap_h * cg.dil_h), fb);
                         const int wtap = (cg.wr0 + cg.wr_step * tap_h) * cg.S + (cg.ws0 + cg.ws_step * tap_w);
                         if (B_MN) {
 #pragma unroll
@@ -384,10 +383,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 uint32_t accumulate = 0;
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_try_wait(full_bar + stage, phase) && !mbar_wait_bounded(full_bar + stage, phase)) {
+                    if (!mbar_spin(full_bar + stage, phase, kSpinPolls) && !mbar_wait_bounded(full_bar + stage, phase)) {
                         report(status, WAIT_FULL, stage); *abort_flag = 1; break;
                     }
-                    fence_after_sync();
+                    // no tcgen05 fence here: the operands were written by the TMA unit (async proxy) and published through
+                    // the mbarrier this thread just observed; a fence per k-block would only serialise the MMA stream
 #pragma unroll
                     for (int j = 0; j < BK / UMMA_K; ++j) {
                         // K-major: 16 elements = 32 B further along the swizzled row; MN-major: 16 k-rows of 128 B further down
@@ -525,7 +525,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const int kb0 = split * g.kb_per_split, kb1 = min(kb_total, kb0 + g.kb_per_split);
                 int k0 = kb0 * BKE;
                 for (int kb = kb0; kb < kb1; ++kb, k0 += BKE) {
-                    if (!mbar_try_wait(empty_bar + stage, phase ^ 1) && !mbar_wait_bounded(empty_bar + stage, phase ^ 1)) {
+                    if (!mbar_spin(empty_bar + stage, phase ^ 1, kSpinPolls) && !mbar_wait_bounded(empty_bar + stage, phase ^ 1)) {
                         report(status, WAIT_EMPTY, stage); *abort_flag = 1; break;
                     }
                     uint8_t* sa = smem + stage * L::STAGE_BYTES;
@@ -568,10 +568,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 uint32_t accumulate = 0;
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_try_wait(full_bar + stage, phase) && !mbar_wait_bounded(full_bar + stage, phase)) {
+                    if (!mbar_spin(full_bar + stage, phase, kSpinPolls) && !mbar_wait_bounded(full_bar + stage, phase)) {
                         report(status, WAIT_FULL, stage); *abort_flag = 1; break;
                     }
-                    fence_after_sync();
+                    // no tcgen05 fence here: the operands were written by the TMA unit (async proxy) and published through
+                    // the mbarrier this thread just observed; a fence per k-block would only serialise the MMA stream
 #pragma unroll
                     for (int j = 0; j < BK / UMMA_K; ++j) {
                         if constexpr (ES == 2) mma_f16_ss_pair_words(d_tmem, a_lo + j * kStepA, b_lo + j * kStepB, kDescHi, idesc, accumulate);

@@ -53,6 +53,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// Non-suspending probe of a phase; a short spin on it reacts faster than try_wait's suspend / wake-up when the
+// phase is about to complete (the steady state of a running pipeline).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, int polls) {
+    for (int i = 0; i < polls; ++i)
+        if (mbar_test_wait(bar, parity)) return true;
+    return false;
+}
 // Polls at most `limit` times (each poll may itself suspend for a hardware-defined
 // interval).  Returns false if the phase never completed.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 24)) {
@@ -68,13 +84,6 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-// Tiled 4-D load: a (c, w, h, n) box of an NHWC tensor; coordinates may lie outside the tensor (zero fill), which is how a
-// convolution's padding and a filter tap's shift are expressed.  Rows land in (n, h, w) order, 128 bytes of channels each.
-__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int c, int w, int h, int n, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n) : "memory");
 }
 // TMA im2col load (NHWC tensor, 4-D map made by cuTensorMapEncodeIm2col): `pixels-per-column` pixels starting at the
 // bounding-box position (w, h, n) and walking w, then h, then n in steps of the map's traversal strides, each pixel

@@ -420,6 +420,60 @@ reduce_residual_kernel(HT* __restrict__ h, const __nv_bfloat16* __restrict__ sta
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Pieces of the training path: an all-gather as peer stores of whole chunks, and a reduce-scatter as peer loads.
+struct ChunkPeers {
+    uint8_t* p[comm::kMaxWorld];
+    int n;
+};
+
+// Chunk c (chunk_bytes, contiguous in src) is stored at dst + c * dst_stride for every destination: with
+// chunks = T this lays one rank's [T][n][row] block into everybody's [T][world * n][row] buffer.
+__global__ void __launch_bounds__(256)
+push_chunks_kernel(const uint4* __restrict__ src, ChunkPeers dst, long long vec_per_chunk, long long dst_stride_vec, long long total_vec) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec; i += (long long)gridDim.x * blockDim.x) {
+        const long long c = i / vec_per_chunk, r = i - c * vec_per_chunk;
+        const uint4 v = src[i];
+        for (int d = 0; d < dst.n; ++d) reinterpret_cast<uint4*>(dst.p[d])[c * dst_stride_vec + r] = v;
+    }
+    __threadfence_system();
+}
+
+// out[c][r] = sum over sources j (rank order, fp32) of src_j[c * src_stride + r]: this rank's chunk of every peer's
+// partial result, read in place over NVLink.
+template <typename OT>
+__global__ void __launch_bounds__(256)
+reduce_chunks_kernel(ChunkPeers src, OT* __restrict__ out, long long vec_per_chunk, long long src_stride_vec, long long total_vec) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec; i += (long long)gridDim.x * blockDim.x) {
+        const long long c = i / vec_per_chunk, r = i - c * vec_per_chunk;
+        uint4 v[comm::kMaxWorld];
+#pragma unroll
+        for (int j = 0; j < comm::kMaxWorld; ++j)
+            if (j < src.n) v[j] = reinterpret_cast<const uint4*>(src.p[j])[c * src_stride_vec + r];
+        float acc[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+#pragma unroll
+        for (int j = 0; j < comm::kMaxWorld; ++j)
+            if (j < src.n) {
+                const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v[j]);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { const float2 f = __bfloat1622float2(p[q]); acc[2 * q] += f.x; acc[2 * q + 1] += f.y; }
+            }
+        if constexpr (sizeof(OT) == 4) {
+            float4* o = reinterpret_cast<float4*>(out + i * 8);
+            o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        } else {
+            uint4 w;
+            __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) p[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+            reinterpret_cast<uint4*>(out)[i] = w;
+        }
+    }
+}
+
 __global__ void tp_barrier_kernel(comm::PeerPtrs pp, int rank, int world, uint32_t epoch, comm::CommStatus* status, long long timeout_ns) {
     __threadfence_system();
     comm::block_barrier(pp, rank, world, 1, epoch, 1, status, timeout_ns);
@@ -541,6 +595,57 @@ void tp_reduce_residual(at::Tensor h, int64_t stage_ptr, int64_t slot_elems, int
     C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
+// src: contiguous, `chunks` pieces of equal size.  Piece c is written to dst_ptrs[j] + dst_offset_bytes + c * dst_stride_bytes
+// on every rank j of the list (this rank's own buffer included).  All sizes are multiples of 16 bytes.
+void tp_push_chunks(const at::Tensor& src, std::vector<int64_t> dst_ptrs, int64_t chunks, int64_t dst_stride_bytes, int64_t dst_offset_bytes) {
+    TORCH_CHECK(src.is_cuda() && src.is_contiguous(), "tp_push_chunks: contiguous CUDA tensor required");
+    const int64_t total = src.numel() * src.element_size();
+    TORCH_CHECK(chunks >= 1 && total % chunks == 0, "tp_push_chunks: the tensor does not split into equal chunks");
+    const int64_t chunk_bytes = total / chunks;
+    TORCH_CHECK(chunk_bytes % 16 == 0 && dst_stride_bytes % 16 == 0 && dst_offset_bytes % 16 == 0 &&
+                reinterpret_cast<uintptr_t>(src.data_ptr()) % 16 == 0, "tp_push_chunks: 16-byte granularity required");
+    TORCH_CHECK(!dst_ptrs.empty() && (int)dst_ptrs.size() <= comm::kMaxWorld, "tp_push_chunks: 1..16 destinations");
+    const c10::cuda::CUDAGuard guard(src.device());
+    ChunkPeers dst{};
+    dst.n = (int)dst_ptrs.size();
+    for (int j = 0; j < dst.n; ++j) {
+        TORCH_CHECK(dst_ptrs[j] % 16 == 0, "tp_push_chunks: destinations must be 16-byte aligned");
+        dst.p[j] = reinterpret_cast<uint8_t*>(dst_ptrs[j] + dst_offset_bytes);
+    }
+    const long long total_vec = total / 16;
+    const unsigned blocks = (unsigned)std::min<long long>((total_vec + 255) / 256, 1184);
+    push_chunks_kernel<<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(reinterpret_cast<const uint4*>(src.data_ptr()), dst, chunk_bytes / 16,
+                                                                           dst_stride_bytes / 16, total_vec);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// out: contiguous [chunks, chunk_elems] (bf16 or fp32).  out[c] = sum over j of the bf16 piece at
+// src_ptrs[j] + (src_offset_elems + c * src_stride_elems) elements.
+void tp_reduce_chunks(std::vector<int64_t> src_ptrs, at::Tensor out, int64_t chunks, int64_t src_stride_elems, int64_t src_offset_elems) {
+    TORCH_CHECK(out.is_cuda() && out.is_contiguous() && (out.scalar_type() == at::kFloat || out.scalar_type() == at::kBFloat16),
+                "tp_reduce_chunks: contiguous fp32 or bf16 output required");
+    TORCH_CHECK(chunks >= 1 && out.numel() % chunks == 0, "tp_reduce_chunks: the output does not split into equal chunks");
+    const int64_t chunk_elems = out.numel() / chunks;
+    TORCH_CHECK(chunk_elems % 8 == 0 && src_stride_elems % 8 == 0 && src_offset_elems % 8 == 0, "tp_reduce_chunks: 8-element granularity required");
+    TORCH_CHECK(!src_ptrs.empty() && (int)src_ptrs.size() <= comm::kMaxWorld, "tp_reduce_chunks: 1..16 sources");
+    const c10::cuda::CUDAGuard guard(out.device());
+    ChunkPeers src{};
+    src.n = (int)src_ptrs.size();
+    for (int j = 0; j < src.n; ++j) {
+        TORCH_CHECK(src_ptrs[j] % 16 == 0, "tp_reduce_chunks: sources must be 16-byte aligned");
+        src.p[j] = reinterpret_cast<uint8_t*>(src_ptrs[j] + src_offset_elems * 2);
+    }
+    const long long total_vec = out.numel() / 8;
+    const unsigned blocks = (unsigned)std::min<long long>((total_vec + 255) / 256, 1184);
+    cudaStream_t st = at::cuda::getCurrentCUDAStream();
+    if (out.scalar_type() == at::kFloat)
+        reduce_chunks_kernel<float><<<blocks, 256, 0, st>>>(src, out.data_ptr<float>(), chunk_elems / 8, src_stride_elems / 8, total_vec);
+    else
+        reduce_chunks_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(src, reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), chunk_elems / 8,
+                                                                   src_stride_elems / 8, total_vec);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 void tp_barrier(std::vector<int64_t> sig_ptrs, int64_t rank, int64_t epoch, at::Tensor status, double timeout_s) {
     const int world = (int)sig_ptrs.size();
     TORCH_CHECK(world >= 1 && world <= comm::kMaxWorld, "tp_barrier: bad world size");
@@ -562,6 +667,8 @@ TORCH_LIBRARY_FRAGMENT(sjb200, m) {
     m.def("rmsnorm_lif_pack(Tensor h, Tensor weight, int[] out_ptrs, int pitch, float eps, float tau, float v_th) -> ()");
     m.def("tp_reduce_residual(Tensor(a!) h, int stage_ptr, int slot_elems, int world) -> ()");
     m.def("tp_barrier(int[] sig_ptrs, int rank, int epoch, Tensor(a!) status, float timeout_s) -> ()");
+    m.def("tp_push_chunks(Tensor src, int[] dst_ptrs, int chunks, int dst_stride_bytes, int dst_offset_bytes) -> ()");
+    m.def("tp_reduce_chunks(int[] src_ptrs, Tensor(a!) out, int chunks, int src_stride_elems, int src_offset_elems) -> ()");
 }
 TORCH_LIBRARY_IMPL(sjb200, CUDA, m) {
     m.impl("spike_gemm", &sjb200::spike_gemm);
@@ -569,4 +676,6 @@ TORCH_LIBRARY_IMPL(sjb200, CUDA, m) {
     m.impl("rmsnorm_lif_pack", &sjb200::rmsnorm_lif_pack);
     m.impl("tp_reduce_residual", &sjb200::tp_reduce_residual);
     m.impl("tp_barrier", &sjb200::tp_barrier);
+    m.impl("tp_push_chunks", &sjb200::tp_push_chunks);
+    m.impl("tp_reduce_chunks", &sjb200::tp_reduce_chunks);
 }

@@ -12,9 +12,9 @@ def _net(dev):
     from spikingjelly_b200.activation_based import functional, layer, neuron, surrogate
     torch.manual_seed(0)
     net = nn.Sequential(
-        layer.Linear(48, 64), neuron.LIFNode(surrogate_function=surrogate.ATan(), detach_reset=True, backend="cuda"),
-        layer.Linear(64, 32), neuron.IFNode(surrogate_function=surrogate.Sigmoid(), backend="cuda"),
-        layer.Linear(32, 10), neuron.ParametricLIFNode(surrogate_function=surrogate.ATan(), backend="cuda")).to(dev)
+        layer.Linear(48, 64), neuron.LIFNode(surrogate_function=surrogate.ATan(), detach_reset=True, step_mode="m", backend="cuda"),
+        layer.Linear(64, 32), neuron.IFNode(surrogate_function=surrogate.Sigmoid(), step_mode="m", backend="cuda"),
+        layer.Linear(32, 10), neuron.ParametricLIFNode(surrogate_function=surrogate.ATan(), step_mode="m", backend="cuda")).to(dev)
     functional.set_step_mode(net, "m")
     return net
 
