@@ -5,6 +5,7 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29511 bench.py --gpus 8 --steps 20 --warmup 5
     python bench.py --impl reference ...      # the unmodified reference from baseline/_ref
+    python bench.py --config sew_resnet|snn_llm|neuron ...   # the other benchmark configurations, same JSON contract
 
 Workload (identical for both arms): Spikformer with 8 encoder blocks, d=512, 8 heads, MLP
 ratio 4, T=4, 224x224x3 synthetic N(0,1) images, 1000 random classes, per-GPU batch 32 (global
@@ -44,6 +45,10 @@ def parse():
     p.add_argument("--batch", type=int, default=PER_GPU_BATCH, help="per-GPU batch")
     p.add_argument("--ref-backend", default="auto", help="reference neuron backend: auto|triton|torch")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--config", choices=["spikformer", "sew_resnet", "snn_llm", "neuron"], default="spikformer",
+                   help="spikformer (default, the headline): Spikformer-8-512 data parallel; sew_resnet: SEW-ResNet-18 on event frames, "
+                        "data parallel; snn_llm: the 24-layer spike-driven LM, tensor parallel; neuron: multi-step LIF forward + backward")
+    p.add_argument("--batch-default", action="store_true", help=argparse.SUPPRESS)
     return p.parse_args()
 
 
@@ -137,6 +142,30 @@ class _Deferred:
         return float(self.host.item())
 
 
+# Workloads that share the data-parallel training loop below.  ``x``: shape of one per-GPU batch, ``classes``, how the
+# synthetic input is drawn, and how each arm builds the network.
+def _sew_build(impl, device, ref_backend):
+    sys.path.insert(0, str(ROOT))
+    from benchmark.benchmark_sew_resnet import build
+    net, functional = build(impl, device)
+    return net, functional, ("triton" if impl == "reference" else None)
+
+
+WORKLOADS = {
+    "spikformer": dict(
+        model="Spikformer-8-512", T=4, batch=PER_GPU_BATCH, classes=1000, seq_len=196,
+        shape=lambda B: (B, 3, 224, 224), draw=lambda torch, shape, device: torch.randn(*shape, device=device),
+        metric="train samples/sec (Spikformer-8-512, T=4, bf16, data parallel, device-timed, max over ranks)",
+        data="synthetic N(0,1) 224x224x3 images, random labels, random-init weights"),
+    "sew_resnet": dict(
+        model="SEW-ResNet-18 (ADD, LIF tau 2, ATan)", T=16, batch=32, classes=11, seq_len=None,
+        shape=lambda B: (16, B, 2, 128, 128),
+        draw=lambda torch, shape, device: (torch.poisson(torch.full(shape, 0.05, device=device)) > 0).float(),
+        metric="train samples/sec (SEW-ResNet-18, T=16, 2x128x128 event frames, bf16, data parallel, device-timed, max over ranks)",
+        data="synthetic Poisson(0.05) event frames clipped to {0,1}, random labels over 11 classes, random-init weights"),
+}
+
+
 def build_ours(device, backend="cuda"):
     from spikingjelly_b200 import ops
     from spikingjelly_b200.activation_based import functional
@@ -170,8 +199,61 @@ def build_reference(device, backend):
     return net, functional, chosen
 
 
+def run_delegated(args) -> None:
+    """``--config snn_llm`` / ``--config neuron``: run the configuration's own benchmark (same process, same launcher) and
+    restate its record in this script's JSON contract."""
+    import contextlib
+    import io
+    import runpy
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    if rank == 0:
+        sampler.start()
+    buf = io.StringIO()
+    if args.config == "snn_llm":
+        argv = ["benchmark_snn_llm.py", "--steps", str(args.steps), "--warmup", str(args.warmup), "--impl", args.impl]
+        if args.impl == "ours" and world > 1:
+            argv += ["--path", "fused"]
+        script = ROOT / "benchmark" / "benchmark_snn_llm.py"
+    else:
+        argv = ["benchmark_neuron_kernels.py", "--headline", "--iters", str(max(args.steps, 5)), "--impl", args.impl]
+        script = ROOT / "benchmark" / "benchmark_neuron_kernels.py"
+    old_argv = sys.argv
+    sys.argv = argv
+    try:
+        with contextlib.redirect_stdout(buf):
+            runpy.run_path(str(script), run_name="__main__")
+    finally:
+        sys.argv = old_argv
+    clocks = sampler.stop() if rank == 0 else {}
+    if rank != 0:
+        return
+    lines = [ln for ln in buf.getvalue().splitlines() if ln.startswith("{")]
+    src = json.loads(lines[-1]) if lines else {"unavailable": "the benchmark printed no record"}
+    if "unavailable" in src:
+        print(json.dumps({"impl": args.impl, "unavailable": src["unavailable"]}))
+        return
+    if args.config == "snn_llm":
+        rec = {"metric": "train tokens/sec (SNN-LLM 24L d2048 FFN5504 T=4, seq 2048, micro-batch 4, tensor parallel, device-timed, max over ranks)",
+               "value": src["tokens_per_s"], "unit": "tokens/s", "ms_per_step": src["ms_per_step"], "higher_is_better": True,
+               "scaling": "strong", "config": {"model": "SNN-LLM-24L-2048", "T": 4, "global_batch": 4, "seq_len": 2048,
+                                               "parallelism": f"tp{world}", "path": src.get("path"), "l2": "256 MB flush written between steps"}}
+    else:
+        rec = {"metric": "multi-step LIF forward+backward, T=4, N=2^24, bf16 (us, CUDA events, L2 flushed)", "value": src["fwd_bwd_us"],
+               "unit": "us", "ms_per_step": round(src["fwd_bwd_us"] / 1e3, 4), "higher_is_better": False, "scaling": "weak",
+               "config": {"model": "LIFNode tau=2 hard reset ATan", "T": 4, "N": 1 << 24, "seq_len": None, "global_batch": None,
+                          "parallelism": "1 GPU", "l2": "256 MB flush written between launches"}}
+    rec.update({"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic", "impl": args.impl, "clocks": clocks, "source_record": src})
+    print(json.dumps(rec))
+
+
 def main():
     args = parse()
+    if args.config in ("snn_llm", "neuron"):
+        return run_delegated(args)
+    wl = WORKLOADS[args.config]
     import torch
     import torch.distributed as dist
     import torch.nn.functional as F
@@ -198,7 +280,10 @@ def main():
     launches = None
     if args.impl == "reference":
         try:
-            net, functional, chosen = build_reference(device, args.ref_backend)
+            if args.config == "spikformer":
+                net, functional, chosen = build_reference(device, args.ref_backend)
+            else:
+                net, functional, chosen = _sew_build("reference", device, args.ref_backend)
         except Exception as exc:
             if rank == 0:
                 print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}))
@@ -209,7 +294,10 @@ def main():
             net = prepare_snn_data_parallel(net, device_ids=[local_rank])
         step_model = net
     else:
-        net, functional = build_ours(device)
+        if args.config == "spikformer":
+            net, functional = build_ours(device)
+        else:
+            net, functional, _ = _sew_build("ours", device, None)
         if world > 1:
             from spikingjelly_b200.parallel import data_parallel
             step_model = data_parallel.prepare_snn_data_parallel(net, device_ids=[local_rank])
@@ -219,11 +307,12 @@ def main():
         launches = counters
 
     opt = torch.optim.AdamW(step_model.parameters(), lr=1e-4, weight_decay=0.01, fused=True)
-    B = args.batch
-    dev_x = torch.randn(B, 3, 224, 224, device=device)
-    dev_y = torch.randint(0, 1000, (B,), device=device)
-    host_x = [torch.randn(B, 3, 224, 224).pin_memory() for _ in range(2)]
-    host_y = [torch.randint(0, 1000, (B,)).pin_memory() for _ in range(2)]
+    B = args.batch if args.batch != PER_GPU_BATCH or args.config == "spikformer" else wl["batch"]
+    shape = wl["shape"](B)
+    dev_x = wl["draw"](torch, shape, device)
+    dev_y = torch.randint(0, wl["classes"], (B,), device=device)
+    host_x = [wl["draw"](torch, shape, "cpu").pin_memory() for _ in range(2)]
+    host_y = [torch.randint(0, wl["classes"], (B,)).pin_memory() for _ in range(2)]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
 
     def train_step(x, y):
@@ -317,13 +406,13 @@ def main():
     if rank == 0:
         value = world * B * args.steps / (ms_total / 1e3)
         rec = {
-            "metric": "train samples/sec (Spikformer-8-512, T=4, bf16, data parallel, device-timed, max over ranks)",
+            "metric": wl["metric"],
             "value": round(value, 2), "unit": "samples/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_total / args.steps, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic N(0,1) 224x224x3 images, random labels, random-init weights",
-            "config": {"model": "Spikformer-8-512", "T": 4, "global_batch": world * B, "per_gpu_batch": B,
-                       "seq_len": 196, "parallelism": f"dp{world}", "optimizer": "AdamW(fused)",
+            "data": wl["data"],
+            "config": {"model": wl["model"], "T": wl["T"], "global_batch": world * B, "per_gpu_batch": B,
+                       "seq_len": wl["seq_len"], "parallelism": f"dp{world}", "optimizer": "AdamW(fused)",
                        "l2": "256 MB flush written between steps (inside the timed region)"},
             "impl": args.impl, "clocks": clocks, "last_loss": round(float(loss.item()), 4),
         }

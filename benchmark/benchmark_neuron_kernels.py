@@ -50,6 +50,51 @@ def make(ns, kind, soft, backend):
     return ns.neuron.ParametricLIFNode(init_tau=2.0, **kw)
 
 
+def headline(args, dev):
+    T, N = 4, 1 << 24
+    x = (torch.randn(T, N, device=dev) + 0.5).to(torch.bfloat16).requires_grad_(True)
+    g = torch.randn(T, N, device=dev).to(torch.bfloat16)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    class NS:
+        pass
+    rec = {"neuron": "lif", "soft_reset": False, "dtype": "bf16", "T": T, "N": N, "impl": args.impl}
+    if args.impl == "ours":
+        from spikingjelly_b200 import ops
+        from spikingjelly_b200.activation_based import functional, neuron, surrogate
+        ops.require()
+        NS.neuron, NS.surrogate, NS.functional = neuron, surrogate, functional
+        backends = ["cuda"]
+    else:
+        try:
+            sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
+            from spikingjelly.activation_based import functional as rf, neuron as rn, surrogate as rs
+        except Exception as exc:
+            print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}))
+            return
+        NS.neuron, NS.surrogate, NS.functional = rn, rs, rf
+        backends = args.ref_backends.split(",")
+    times = {}
+    for be in backends:
+        try:
+            net = make(NS, "lif", False, be).to(dev)
+
+            def f():
+                x.grad = None
+                net(x).backward(g)
+                NS.functional.reset_net(net)
+            times[be] = round(time_fn(f, flush, iters=args.iters), 2)
+        except Exception as exc:
+            rec[f"{be}_err"] = f"{type(exc).__name__}: {exc}"[:120]
+    if not times:
+        print(json.dumps({"impl": args.impl, "unavailable": "no neuron backend ran: " + "; ".join(str(v) for k, v in rec.items() if k.endswith("_err"))}))
+        return
+    best = min(times, key=times.get)
+    rec.update(fwd_bwd_us=times[best], backend=best, all_backends_us=times,
+               GBps=round(5 * T * N * 2 / times[best] / 1e3, 1))
+    print(json.dumps(rec))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default="")
@@ -59,8 +104,14 @@ def main():
     ap.add_argument("--neurons", default="if,lif,lif_ndi,plif")
     ap.add_argument("--no-reference", action="store_true")
     ap.add_argument("--ref-backends", default="torch,triton")
+    ap.add_argument("--headline", action="store_true",
+                    help="one record only: LIF (tau 2, hard reset, ATan) forward + backward, bf16, T = 4, N = 2^24, for --impl")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
     dev = torch.device("cuda")
+    if args.headline:
+        return headline(args, dev)
     from spikingjelly_b200.activation_based import functional, neuron, surrogate
 
     class Ours:

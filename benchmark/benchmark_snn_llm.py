@@ -32,6 +32,10 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--fp8", action="store_true", help="run the four linear layers of every block through the fp8 linear (TP = 1)")
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours",
+                    help="reference: the same architecture assembled from the reference package's parts (benchmark/snn_llm_reference_parts.py)")
+    ap.add_argument("--path", choices=["megatron", "fused"], default="megatron",
+                    help="ours, several GPUs: NCCL all-reduce tensor parallelism, or the fused token-sharded path (parallel/fused_tp_train.py)")
     ap.add_argument("--out", default="")
     a = ap.parse_args()
     world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
@@ -39,12 +43,39 @@ def main():
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    ops.require()
     torch.manual_seed(0)                                   # identical replicated parameters on every rank
-    model = snn_llm.snn_llm_1b(n_layers=a.layers, backend="cuda", max_seq_len=a.seq)
-    if world > 1:
-        model = snn_llm.parallelize_snn_llm(model)
-    model.to(device)
+    extra = {}
+    sync_replicated = None
+    if a.impl == "reference":
+        try:
+            sys.path.insert(0, str(ROOT / "benchmark"))
+            import snn_llm_reference_parts as ref
+            backend = ref.pick_backend(device)
+            model = ref.build(a.layers, a.seq, backend).to(device)
+            if world > 1:
+                model = ref.tensor_parallel(model, world)
+            extra["reference_backend"] = backend
+        except Exception as exc:
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}))
+            if world > 1:
+                dist.destroy_process_group()
+            return
+    else:
+        ops.require()
+        model = snn_llm.snn_llm_1b(n_layers=a.layers, backend="cuda", max_seq_len=a.seq)
+        if world > 1 and a.path == "megatron":
+            model = snn_llm.parallelize_snn_llm(model)
+        model.to(device)
+        if a.path == "fused":
+            from spikingjelly_b200.parallel.data_parallel import SNNDataParallel
+            from spikingjelly_b200.parallel.fused_tp_train import FusedTPSNNLLM
+            model = FusedTPSNNLLM(model, a.micro_batch, a.seq)
+            if world > 1:
+                # replicated parameters (embedding, norms, LM head) see this rank's tokens only: sum their gradients
+                holder = torch.nn.Module()
+                holder.params = torch.nn.ParameterList(model.replicated_parameters())
+                sync_replicated = SNNDataParallel(holder, reduce="sum", timeout_s=120.0)
     if a.fp8:
         # per-tensor scaled e4m3 operands on the tcgen05 kind::f8f6f4 GEMM (spikes are exact in e4m3); the LM head stays bf16
         from spikingjelly_b200.ops import fp8
@@ -54,11 +85,11 @@ def main():
             for lin in (blk.attn.qkv, blk.attn.proj, blk.ffn.up, blk.ffn.down):
                 lin.forward = (lambda x, m=lin: fp8.linear(x, m.weight, m.bias))
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
-    tok = torch.randint(0, model.cfg.vocab_size, (a.micro_batch, a.seq), device=device, generator=torch.Generator(device).manual_seed(1))
+    tok = torch.randint(0, 32000, (a.micro_batch, a.seq), device=device, generator=torch.Generator(device).manual_seed(1))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
 
     def step():
-        with torch.autocast("cuda", dtype=torch.bfloat16):
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=a.path != "fused" or a.impl == "reference"):
             _, loss = model(tok, labels=tok)
         opt.zero_grad(set_to_none=True)
         loss.backward()
@@ -86,20 +117,25 @@ def main():
     if rank == 0:
         ms = t.item() / a.steps
         tokens = a.micro_batch * a.seq
-        fwd_flops = tokens * model.flops_per_token(a.seq)
+        fwd_flops = tokens * (model.flops_per_token(a.seq) if hasattr(model, "flops_per_token") else snn_llm.SNNLLM.flops_per_token(model, a.seq))
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
         peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
         tflops = 3.0 * fwd_flops / (ms / 1e3) / 1e12 / world
         rec = {"config": f"SNN-LLM {a.layers}L d2048 ffn5504 T4 seq{a.seq} mb{a.micro_batch} {"fp8" if a.fp8 else "bf16"} tp{world}", "n_gpus": world,
+               "impl": a.impl, "path": a.path if a.impl == "ours" else "reference DTensor TP",
                "ms_per_step": round(ms, 2), "tokens_per_s": round(tokens / ms * 1e3, 1), "model_tflops_per_gpu": round(tflops, 1),
                "of_measured_sustained_bf16_peak": round(tflops / peak, 3), "peak_source": "measured" if peaks else "fallback",
                "last_loss": round(float(loss), 4), "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
                "parameters": sum(p.numel() for p in model.parameters())}
+        rec.update(extra)
         line = json.dumps(rec)
         print(line)
         if a.out:
             with open(a.out, "a") as f:
                 f.write(line + "\n")
+    if sync_replicated is not None:
+        sync_replicated.check_communication()
+        model.check()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

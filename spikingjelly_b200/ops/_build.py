@@ -27,6 +27,10 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "--e
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-diag-suppress", "177,550"]
 
 
+#: ptxas resource reports (registers, spills, shared memory) of the translation units compiled by the last verbose build
+LAST_PTXAS_LOG: List[str] = []
+
+
 def _nvcc() -> str:
     cand = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not Path(cand).exists():
@@ -108,8 +112,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
         stamp.write_text(want)
     if verbose:
+        from ..logger import logger
+        LAST_PTXAS_LOG[:] = logs
         for lg in logs:
-            sys.stderr.write(lg)
+            logger.info("nvcc -Xptxas -v:\n%s", lg)
     return LIB
 
 
@@ -123,3 +129,5 @@ def is_current() -> bool:
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    for report in LAST_PTXAS_LOG:
+        print(report, file=sys.stderr)

@@ -87,8 +87,11 @@ class SNNDataParallel(nn.Module):
     def __init__(self, module: nn.Module, process_group: Optional[dist.ProcessGroup] = None,
                  bucket_cap_mb: float = 25.0, broadcast_buffers: bool = False, use_multimem: Optional[bool] = None,
                  timeout_s: float = 300.0, wire: str = "fp32", blocks: Optional[int] = None,
-                 tail_bucket_mb: float = 1.0):
+                 tail_bucket_mb: float = 1.0, reduce: str = "mean"):
         super().__init__()
+        if reduce not in ("mean", "sum"):
+            raise ValueError(f"reduce must be 'mean' (data parallel) or 'sum' (replicated parameters of a token-sharded model), got {reduce!r}")
+        self.reduce = reduce
         self.module = module
         self.group = process_group if process_group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
@@ -155,7 +158,7 @@ class SNNDataParallel(nn.Module):
                 p.grad = v
 
     def _launch(self, b: _Bucket) -> None:
-        scale = 1.0 / self.world
+        scale = 1.0 / self.world if self.reduce == "mean" else 1.0
         self._gather(b)
         if self._cuda:
             ready = torch.cuda.Event()
