@@ -84,16 +84,23 @@ def main():
         for blk in model.blocks:
             for lin in (blk.attn.qkv, blk.attn.proj, blk.ffn.up, blk.ffn.down):
                 lin.forward = (lambda x, m=lin: fp8.linear(x, m.weight, m.bias))
-    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
+    # the fused AdamW kernel takes one kind of tensor per call: sharded (DTensor) and plain parameters get an optimiser each
+    from torch.distributed.tensor import DTensor
+    kinds = {}
+    for p in model.parameters():
+        kinds.setdefault(isinstance(p, DTensor) or isinstance(p.data, DTensor), []).append(p)
+    opts = [torch.optim.AdamW(ps, lr=1e-4, fused=True) for ps in kinds.values()]
     tok = torch.randint(0, 32000, (a.micro_batch, a.seq), device=device, generator=torch.Generator(device).manual_seed(1))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
 
     def step():
         with torch.autocast("cuda", dtype=torch.bfloat16, enabled=a.path != "fused" or a.impl == "reference"):
             _, loss = model(tok, labels=tok)
-        opt.zero_grad(set_to_none=True)
+        for opt in opts:
+            opt.zero_grad(set_to_none=True)
         loss.backward()
-        opt.step()
+        for opt in opts:
+            opt.step()
         flush.zero_()
         return loss
 

@@ -7,9 +7,9 @@ from .factories import NeuronFactory
 from .modules import ChannelVoltageScaler, VoltageHook, VoltageScaler
 from .qcfs import SignedQCFSSequenceEncoder
 from .recipes import (ConversionRecipe, FXConversionRecipe, LocalThresholdBalancingRecipe, ModuleConversionRecipe, RateCodingRecipe,
-                      TransformerTDEquivalentRecipe)
+                      STATransformerRecipe, TransformerTDEquivalentRecipe)
 from .utils import download_url
 
 __all__ = ["Converter", "FXConverter", "ModuleConverter", "ConversionRecipe", "FXConversionRecipe", "ModuleConversionRecipe",
-           "RateCodingRecipe", "LocalThresholdBalancingRecipe", "TransformerTDEquivalentRecipe", "ChannelVoltageScaler", "VoltageHook",
+           "RateCodingRecipe", "LocalThresholdBalancingRecipe", "TransformerTDEquivalentRecipe", "STATransformerRecipe", "ChannelVoltageScaler", "VoltageHook",
            "VoltageScaler", "download_url", "NeuronFactory", "operators", "SignedQCFSSequenceEncoder", "estimate_delay_start"]

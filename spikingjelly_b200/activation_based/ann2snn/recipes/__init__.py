@@ -2,7 +2,8 @@ from .base import ConversionRecipe, FXConversionRecipe, ModuleConversionRecipe
 from .local_threshold_balancing import LocalThresholdBalancingRecipe
 from .rate_coding import RateCodingRecipe
 from .spikezip_qann import SpikeZIPTFQANNRecipe
+from .sta_transformer import STATransformerRecipe
 from .transformer_td_equivalent import TransformerTDEquivalentRecipe
 
 __all__ = ["ConversionRecipe", "FXConversionRecipe", "ModuleConversionRecipe", "LocalThresholdBalancingRecipe", "RateCodingRecipe", "SpikeZIPTFQANNRecipe",
-           "TransformerTDEquivalentRecipe"]
+           "STATransformerRecipe", "TransformerTDEquivalentRecipe"]

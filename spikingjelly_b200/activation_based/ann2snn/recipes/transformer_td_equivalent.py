@@ -11,12 +11,20 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch import fx
 
+from ... import base
+
 from ..operators import (SNNElementWiseProduct, SNNMatrixOperator, TDGELU, TDModule, TDSiLU, TDSoftmax, _td_module_from_ann)
 from .base import FXConversionRecipe
+from .step_mode_adapters import adapt_step_mode_graph, lift_tensor_functions
 
 __all__ = ["TransformerTDEquivalentRecipe"]
 
 _LINEAR_SAFE = (nn.Dropout, nn.Identity, nn.Flatten)
+#: placeholder names that carry no time axis in multi-step mode
+STATIC_INPUT_NAMES = frozenset({"attention_mask", "attn_mask", "causal_mask", "decoder_attention_mask", "encoder_attention_mask",
+                                "key_padding_mask", "mask", "padding_mask"})
+_METHOD_MODULES = {"softmax": lambda node: TDSoftmax(node.kwargs.get("dim", node.args[1] if len(node.args) > 1 else -1)),
+                   "matmul": lambda node: SNNMatrixOperator()}
 _FUNCTION_MODULES = {F.gelu: lambda node: TDGELU(node.kwargs.get("approximate", "none")), F.silu: lambda node: TDSiLU(),
                      torch.nn.functional.softmax: lambda node: TDSoftmax(node.kwargs.get("dim", node.args[1] if len(node.args) > 1 else -1)),
                      torch.softmax: lambda node: TDSoftmax(node.kwargs.get("dim", node.args[1] if len(node.args) > 1 else -1))}
@@ -33,13 +41,29 @@ class TransformerTDEquivalentRecipe(FXConversionRecipe):
         ann.eval()
         return ann
 
+    def _operator_for(self, node: fx.Node):
+        """``(operator module, its inputs)`` for a function or method node that has a temporal-difference form, else None."""
+        is_node = lambda *xs: all(isinstance(x, fx.Node) for x in xs)
+        if node.op == "call_function":
+            if node.target in _FUNCTION_MODULES and is_node(node.args[0]):
+                return _FUNCTION_MODULES[node.target](node), (node.args[0],)
+            if node.target in (torch.matmul, operator.matmul) and len(node.args) >= 2 and is_node(*node.args[:2]):
+                return SNNMatrixOperator(), tuple(node.args[:2])
+            if node.target in (operator.mul, torch.mul) and len(node.args) >= 2 and is_node(*node.args[:2]):
+                return SNNElementWiseProduct(), tuple(node.args[:2])
+        elif node.op == "call_method" and node.target in _METHOD_MODULES and node.args and is_node(node.args[0]):
+            if node.target == "matmul":
+                return (SNNMatrixOperator(), tuple(node.args[:2])) if len(node.args) >= 2 and is_node(node.args[1]) else None
+            return _METHOD_MODULES[node.target](node), (node.args[0],)
+        return None
+
     def replace(self, converter, fx_model: fx.GraphModule) -> fx.GraphModule:
         modules = dict(fx_model.named_modules())
         n_new = 0
         for node in list(fx_model.graph.nodes):
             if node.op == "call_module":
                 m = modules.get(node.target)
-                if isinstance(m, TDModule) or isinstance(m, _LINEAR_SAFE):
+                if isinstance(m, (TDModule, base.MemoryModule)) or isinstance(m, _LINEAR_SAFE):
                     continue
                 td = _td_module_from_ann(m, self.step_mode)
                 if td is None:
@@ -49,24 +73,22 @@ class TransformerTDEquivalentRecipe(FXConversionRecipe):
                     continue
                 parent, _, child = node.target.rpartition(".")
                 setattr(fx_model.get_submodule(parent) if parent else fx_model, child, td)
-            elif node.op == "call_function":
-                new = None
-                if node.target in _FUNCTION_MODULES:
-                    new, args = _FUNCTION_MODULES[node.target](node), (node.args[0],)
-                elif node.target in (torch.matmul, operator.matmul) and all(isinstance(a, fx.Node) for a in node.args[:2]):
-                    new, args = SNNMatrixOperator(), tuple(node.args[:2])
-                elif node.target in (operator.mul, torch.mul) and all(isinstance(a, fx.Node) for a in node.args[:2]):
-                    new, args = SNNElementWiseProduct(), tuple(node.args[:2])
-                if new is None:
-                    continue
-                new.step_mode = self.step_mode
-                target = f"td_function_{n_new}"
-                n_new += 1
-                fx_model.add_submodule(target, new)
-                with fx_model.graph.inserting_after(node):
-                    repl = fx_model.graph.call_module(target, args=args)
-                node.replace_all_uses_with(repl)
-                fx_model.graph.erase_node(node)
+                continue
+            found = self._operator_for(node)
+            if found is None:
+                continue
+            new, args = found
+            new.step_mode = self.step_mode
+            target = f"td_function_{n_new}"
+            n_new += 1
+            fx_model.add_submodule(target, new)
+            with fx_model.graph.inserting_after(node):
+                repl = fx_model.graph.call_module(target, args=args)
+            node.replace_all_uses_with(repl)
+            fx_model.graph.erase_node(node)
         fx_model.graph.lint()
         fx_model.recompile()
-        return fx_model
+        # what is left (stateless layers, tensor functions) follows the step mode of the network
+        adapt_step_mode_graph(fx_model, context=type(self).__name__)
+        static = [n.target for n in fx_model.graph.nodes if n.op == "placeholder" and n.target in STATIC_INPUT_NAMES]
+        return lift_tensor_functions(fx_model, static_inputs=static)

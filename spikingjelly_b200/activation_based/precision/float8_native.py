@@ -1,7 +1,10 @@
 """The fp8 policy of this package: every convertible linear map (step-mode ``Linear``, ``nn.Linear``,
 1x1 ``Conv1d``; optionally ``LayerNorm -> Linear`` and ``LayerNorm -> Linear -> GELU -> Linear``
-blocks as one module) runs its matrix products on the e4m3 / e5m2 tensor-core kernel of
-``ops/fp8.py`` with per-tensor dynamic ("current") scaling; everything else runs under bf16 autocast.
+blocks as one module) runs its three matrix products on the e4m3 / e5m2 tensor-core kernel of
+``ops/fp8.py``; everything else runs under bf16 autocast.  Two per-tensor scaling recipes: ``"delayed"`` (the
+default behind ``"auto"``: each tensor is scaled by the maximum its role showed in the previous call and read once)
+and ``"current"`` (scaled by its own maximum, read twice).  ``"block"`` and ``"mxfp8"`` are accepted names that
+resolve to ``"delayed"``: block-scaled operands are not implemented, and the capability report says so.
 
 Parameters stay in their original dtype and under their original names, so optimisers and
 checkpoints are unaffected by the conversion.
@@ -30,12 +33,29 @@ __all__ = ["Float8Linear", "Float8LayerNormLinear", "Float8LayerNormMLP", "Float
 _SUPPORTED_RECIPES = {"auto", "delayed", "current", "block", "mxfp8"}
 
 
-def _fp8_linear(x, weight, bias):
+def _fp8_linear(x, weight, bias, scaling=None):
     from ...ops import fp8
-    return fp8.linear(x, weight, bias)
+    return fp8.linear(x, weight, bias, scaling)
 
 
-class Float8Linear(nn.Linear):
+class _RecipeMixin:
+    """Scaling recipe of a converted module: ``n`` products, each with its own delayed-scaling state (kept outside
+    the state dict: it is rebuilt from the first call after a resume)."""
+    _n_products = 1
+
+    def set_recipe(self, recipe: str) -> None:
+        from ...ops import fp8
+        if recipe not in ("current", "delayed"):
+            raise ValueError(f"recipe must be 'current' or 'delayed', got {recipe!r}")
+        self.__dict__["fp8_recipe"] = recipe
+        self.__dict__["_scalings"] = [fp8.LinearScaling() for _ in range(self._n_products)] if recipe == "delayed" else None
+
+    def _scaling(self, i: int = 0):
+        sc = self.__dict__.get("_scalings")
+        return None if sc is None else sc[i]
+
+
+class Float8Linear(_RecipeMixin, nn.Linear):
     """``nn.Linear`` whose products run in fp8 (same parameters, same state dict)."""
 
     @classmethod
@@ -48,10 +68,10 @@ class Float8Linear(nn.Linear):
         return new
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return _fp8_linear(x, self.weight, self.bias)
+        return _fp8_linear(x, self.weight, self.bias, self._scaling())
 
 
-class Float8LayerNormLinear(nn.Module):
+class Float8LayerNormLinear(_RecipeMixin, nn.Module):
     """``Linear(LayerNorm(x))`` with the product in fp8."""
 
     def __init__(self, norm: nn.LayerNorm, linear: nn.Linear):
@@ -62,11 +82,12 @@ class Float8LayerNormLinear(nn.Module):
 
     def forward(self, x):
         return _fp8_linear(F.layer_norm(x, self.normalized_shape, self.layer_norm_weight, self.layer_norm_bias, self.eps),
-                           self.weight, self.bias)
+                           self.weight, self.bias, self._scaling())
 
 
-class Float8LayerNormMLP(nn.Module):
+class Float8LayerNormMLP(_RecipeMixin, nn.Module):
     """``fc2(GELU(fc1(LayerNorm(x))))`` with both products in fp8."""
+    _n_products = 2
 
     def __init__(self, norm: nn.LayerNorm, fc1: nn.Linear, fc2: nn.Linear):
         super().__init__()
@@ -77,7 +98,8 @@ class Float8LayerNormMLP(nn.Module):
 
     def forward(self, x):
         h = F.layer_norm(x, self.normalized_shape, self.layer_norm_weight, self.layer_norm_bias, self.eps)
-        return _fp8_linear(F.gelu(_fp8_linear(h, self.fc1_weight, self.fc1_bias)), self.fc2_weight, self.fc2_bias)
+        return _fp8_linear(F.gelu(_fp8_linear(h, self.fc1_weight, self.fc1_bias, self._scaling(0))), self.fc2_weight, self.fc2_bias,
+                           self._scaling(1))
 
 
 class _PatternModule(_Float8StepModule):
@@ -185,11 +207,12 @@ class Float8NativePolicy(PrecisionPolicy):
         if self.fp8_recipe not in _SUPPORTED_RECIPES:
             report["te_recipe_fallback_reason"] = f"unsupported fp8 recipe {self.fp8_recipe!r}"
             raise RuntimeError(f"Failed to resolve FP8 recipe: unsupported fp8 recipe {self.fp8_recipe!r}")
-        # one scaling scheme is implemented: the scale of every tensor is recomputed from its current amax
-        self._resolved_recipe_name = "current"
-        report["te_recipe_resolved"] = "current"
-        if self.fp8_recipe not in ("auto", "current"):
-            report["te_recipe_fallback_reason"] = f"recipe {self.fp8_recipe!r} is served by per-tensor current scaling"
+        # two per-tensor schemes: "current" recomputes every scale from the tensor itself, "delayed" takes it from
+        # the previous call of the same role; the block-scaled names resolve to "delayed"
+        self._resolved_recipe_name = "current" if self.fp8_recipe == "current" else "delayed"
+        report["te_recipe_resolved"] = self._resolved_recipe_name
+        if self.fp8_recipe in ("block", "mxfp8"):
+            report["te_recipe_fallback_reason"] = f"recipe {self.fp8_recipe!r} is served by per-tensor delayed scaling"
         target = torch.device(device)
         if target.type == "cuda" and target.index is None and torch.cuda.is_available():
             target = torch.device("cuda", torch.cuda.current_device())
@@ -202,6 +225,14 @@ class Float8NativePolicy(PrecisionPolicy):
         return torch.amp.autocast(self.device_type, dtype=torch.bfloat16)
 
     def _convert_modules(self, model, report):
+        out = self._convert_tree(model, report)
+        recipe = self._resolved_recipe_name or ("current" if self.fp8_recipe == "current" else "delayed")
+        for m in out.modules():
+            if isinstance(m, _RecipeMixin):
+                m.set_recipe(recipe)
+        return out
+
+    def _convert_tree(self, model, report):
         root = _convert_leaf(model)
         if root is not None:
             report.converted_modules.append("<root>")

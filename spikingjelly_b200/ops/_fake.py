@@ -58,12 +58,21 @@ def register() -> None:
         return gq.new_empty((n, s_, h, 3, d))
 
     @reg("sjb200::gemm_fp8")
-    def _(a, b, alpha, out_f32, split_k):
+    def _(a, b, alpha, out_f32, split_k, alpha2=None):
         return a.new_empty((a.shape[0], b.shape[0]), dtype=torch.float32 if out_f32 else torch.bfloat16)
 
     @reg("sjb200::fp8_quantize")
     def _(x, e5m2):
         return x.new_empty(x.shape, dtype=torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn), x.new_empty((1,), dtype=torch.float32)
+
+    @reg("sjb200::fp8_quantize_delayed")
+    def _(x, amax3, slot, e5m2):
+        return x.new_empty(x.shape, dtype=torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn), x.new_empty((1,), dtype=torch.float32)
+
+    @reg("sjb200::fp8_quantize_transpose")
+    def _(x, amax3, slot, e5m2):
+        f8 = torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn
+        return x.new_empty(x.shape, dtype=f8), x.new_empty((x.shape[1], x.shape[0]), dtype=f8), x.new_empty((1,), dtype=torch.float32)
 
     @reg("sjb200::bit_pack")
     def _(x):

@@ -157,14 +157,15 @@ std::tuple<at::Tensor, at::Tensor> gemm_16bit_stats(const at::Tensor& a, const a
     return {out, stats};
 }
 
-// D[M, N] (bf16) = alpha * A[M, K] (.) B[N, K]^T with fp8 operands (both e4m3 or both e5m2, K contiguous) and fp32
-// accumulation on the tensor cores.  `alpha`: optional fp32 device scalar (the product of the two
-// de-quantisation scales), multiplied in the epilogue so that no host synchronisation is needed.
+// D[M, N] (bf16) = alpha * alpha2 * A[M, K] (.) B[N, K]^T with fp8 operands (each e4m3 or e5m2, K contiguous) and fp32
+// accumulation on the tensor cores.  `alpha`, `alpha2`: optional fp32 device scalars (the two de-quantisation
+// scales), multiplied in the epilogue so that neither a host synchronisation nor a scalar-product kernel is needed.
 at::Tensor gemm_fp8(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& alpha, bool out_f32,
-                    int64_t split_k) {
+                    int64_t split_k, const c10::optional<at::Tensor>& alpha2) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2, "gemm_fp8: 2-D CUDA operands required");
-    const bool e4m3 = a.scalar_type() == at::kFloat8_e4m3fn, e5m2 = a.scalar_type() == at::kFloat8_e5m2;
-    TORCH_CHECK((e4m3 || e5m2) && a.scalar_type() == b.scalar_type(), "gemm_fp8: both operands must be float8_e4m3fn or both float8_e5m2");
+    auto fmt = [](const at::Tensor& t) { return t.scalar_type() == at::kFloat8_e4m3fn ? 0 : t.scalar_type() == at::kFloat8_e5m2 ? 1 : -1; };
+    const int fa = fmt(a), fb = fmt(b);
+    TORCH_CHECK(fa >= 0 && fb >= 0, "gemm_fp8: operands must be float8_e4m3fn or float8_e5m2");
     const c10::cuda::CUDAGuard guard(a.device());
     C10_CUDA_CHECK(cudaFree(nullptr));
     at::Tensor A = a.stride(1) == 1 ? a : a.contiguous();
@@ -194,9 +195,15 @@ at::Tensor gemm_fp8(const at::Tensor& a, const at::Tensor& b, const c10::optiona
     g.M = (int)M; g.N = (int)N; g.K = (int)K; g.ldd = (int)N;
     g.split_k = splits; g.kb_per_split = kb_per;
     g.out_f32 = (out_f32 || splits > 1) ? 1 : 0;
-    g.ab_format = e4m3 ? 0 : 1;
+    g.ab_format = fa | (fb << 4) | 0x80;
     g.out_bf16 = 1;
     g.alpha = nullptr;
+    g.alpha2 = nullptr;
+    if (alpha2.has_value() && alpha2->defined()) {
+        TORCH_CHECK(alpha.has_value() && alpha->defined(), "gemm_fp8: alpha2 needs alpha");
+        TORCH_CHECK(alpha2->is_cuda() && alpha2->scalar_type() == at::kFloat && alpha2->numel() == 1, "gemm_fp8: alpha2 must be one fp32 value on the device");
+        g.alpha2 = alpha2->data_ptr<float>();
+    }
     if (alpha.has_value() && alpha->defined()) {
         TORCH_CHECK(alpha->is_cuda() && alpha->scalar_type() == at::kFloat && alpha->numel() == 1, "gemm_fp8: alpha must be one fp32 value on the device");
         g.alpha = alpha->data_ptr<float>();
@@ -251,7 +258,7 @@ TORCH_LIBRARY_FRAGMENT(sjb200, m) {
     m.def("gemm_16bit(Tensor a, Tensor b, bool a_mn, bool b_mn, bool out_f32, int split_k) -> Tensor");
     m.def("gemm_16bit_stats(Tensor a, Tensor b, bool a_mn, bool b_mn) -> (Tensor, Tensor)");
     m.def("gemm_16bit_into(Tensor a, Tensor b, bool a_mn, bool b_mn, Tensor(a!) out) -> Tensor(a!)");
-    m.def("gemm_fp8(Tensor a, Tensor b, Tensor? alpha, bool out_f32, int split_k) -> Tensor");
+    m.def("gemm_fp8(Tensor a, Tensor b, Tensor? alpha, bool out_f32, int split_k, Tensor? alpha2=None) -> Tensor");
     m.def("gemm_status(Tensor like) -> int[]");
     m.def("gemm_set_pair_mode(int mode) -> int");
 }

@@ -73,7 +73,8 @@ struct GemmArgs {
     int out_f32;            // D is fp32 (always when split_k > 1)
     int ab_format;          // kind::f16: 0 = fp16, 1 = bf16;  kind::f8f6f4: 0 = e4m3, 1 = e5m2 (A and B alike)
     int out_bf16;           // 16-bit results are bf16 (else fp16)
-    const float* alpha;     // optional device scalar multiplied into the result (product of the fp8 scales)
+    const float* alpha;     // optional device scalar multiplied into the result (an fp8 de-quantisation scale, or the product of two)
+    const float* alpha2;    // optional second device scalar (used only together with `alpha`)
     float* stats;           // optional [ceil(M / 128) * 4][2][N]: per-column sum and sum of squares of the rounded
                             // 16-bit result over each 32-row slice (batch-norm statistics without re-reading D)
 };
@@ -239,7 +240,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     constexpr int BKE = 128 / ES;              // elements per k-block
     static_assert(ES == 2 || (!A_MN && !B_MN), "8-bit operands are K-major only");
     const int kb_total = (g.K + BKE - 1) / BKE;
-    const float alpha = g.alpha != nullptr ? __ldg(g.alpha) : 1.0f;
+    const float alpha = g.alpha != nullptr ? __ldg(g.alpha) * (g.alpha2 != nullptr ? __ldg(g.alpha2) : 1.0f) : 1.0f;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
@@ -489,7 +490,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int total_tiles = tiles_mn * g.split_k;
     const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
     const int kb_total = (g.K + BKE - 1) / BKE;
-    const float alpha = g.alpha != nullptr ? __ldg(g.alpha) : 1.0f;
+    const float alpha = g.alpha != nullptr ? __ldg(g.alpha) * (g.alpha2 != nullptr ? __ldg(g.alpha2) : 1.0f) : 1.0f;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }

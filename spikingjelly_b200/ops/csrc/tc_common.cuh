@@ -284,8 +284,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
 // Instruction descriptor, kind::f16, fp32 accumulation.
 //   [4,6) D format (1 = f32)  [7,10) A format  [10,13) B format (0 = f16, 1 = bf16)
 //   [15] A major  [16] B major (0 = K, 1 = MN)  [17,23) N >> 3  [24,29) M >> 4
+// `ab_format`: bits [0,3) the A format; with bit 7 set, bits [4,7) the B format, otherwise B has A's format.
 __host__ __device__ constexpr uint32_t make_idesc_f16(int ab_format, int a_mn, int b_mn, int M, int N) {
-    return (1u << 4) | ((uint32_t)ab_format << 7) | ((uint32_t)ab_format << 10) | ((uint32_t)a_mn << 15) |
+    const uint32_t fa = (uint32_t)ab_format & 7u;
+    const uint32_t fb = (ab_format & 0x80) ? (((uint32_t)ab_format >> 4) & 7u) : fa;
+    return (1u << 4) | (fa << 7) | (fb << 10) | ((uint32_t)a_mn << 15) |
            ((uint32_t)b_mn << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 

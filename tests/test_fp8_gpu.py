@@ -94,3 +94,64 @@ def test_fp8_policy_trains_a_spiking_mlp():
         functional.reset_net(art.model)
         losses.append(float(loss))
     assert all(l == l for l in losses) and min(losses[-5:]) < losses[0], losses
+
+
+def _cpu_copy(state):
+    st = fp8.ScalingState()
+    st.amax3, st.calls = state.amax3.cpu().clone(), state.calls
+    return st
+
+
+@pytest.mark.parametrize("e5m2", [False, True])
+@pytest.mark.parametrize("shape,transpose", [((1000, 40), False), ((128, 256), True), ((192, 128), True), ((64, 384), True)])
+def test_delayed_and_transposing_kernels_follow_the_cpu_formulation(e5m2, shape, transpose):
+    torch.manual_seed(3)
+    dev_state = fp8.ScalingState()
+    cpu_state = fp8.ScalingState()
+    for k, s in enumerate((1.0, 2.5, 0.3, 4.0, 1.0)):
+        x = (torch.randn(*shape, device="cuda") * s).to(torch.bfloat16)
+        q, qt, inv = fp8.quantize_with(x, dev_state, e5m2=e5m2, transpose=transpose)
+        rq, rqt, rinv = fp8.quantize_with(x.cpu(), cpu_state, e5m2=e5m2, transpose=transpose)
+        assert torch.allclose(inv.cpu(), rinv, rtol=1e-6), k
+        assert torch.equal(q.cpu().view(torch.uint8), rq.view(torch.uint8)), k
+        if transpose:
+            assert qt.is_contiguous() and torch.equal(qt.cpu().view(torch.uint8), rqt.view(torch.uint8)), k
+        assert torch.allclose(dev_state.amax3.cpu(), cpu_state.amax3), k
+    # current scaling through the transposing kernel
+    x = torch.randn(*shape, device="cuda").to(torch.bfloat16)
+    q, qt, inv = fp8.quantize_with(x, None, e5m2=e5m2, transpose=transpose)
+    q2, inv2 = fp8.quantize(x, e5m2)
+    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(inv, inv2)
+    if transpose:
+        assert torch.equal(qt.view(torch.uint8), q2.t().contiguous().view(torch.uint8))
+
+
+def test_gemm_fp8_mixes_formats_and_takes_two_scales():
+    torch.manual_seed(4)
+    a = torch.randn(256, 512, device="cuda").to(torch.float8_e5m2)
+    b = torch.randn(384, 512, device="cuda").to(torch.float8_e4m3fn)
+    s1, s2 = torch.tensor([0.5], device="cuda"), torch.tensor([0.25], device="cuda")
+    got = torch.ops.sjb200.gemm_fp8(a, b, s1, True, 0, s2)
+    ref = (a.float() @ b.float().t()) * 0.125
+    assert torch.allclose(got, ref, rtol=1e-4, atol=1e-2)
+    got = torch.ops.sjb200.gemm_fp8(b, a, s1, True, 0, None)
+    assert torch.allclose(got, (b.float() @ a.float().t()) * 0.5, rtol=1e-4, atol=1e-2)
+
+
+@pytest.mark.parametrize("delayed", [False, True])
+def test_fp8_linear_all_three_products_close_to_fp32(delayed):
+    torch.manual_seed(5)
+    x = (torch.rand(4, 256, 512, device="cuda") < 0.25).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(768, 512, device="cuda") * 0.03).requires_grad_(True)
+    sc = fp8.LinearScaling() if delayed else None
+    g = torch.randn(4, 256, 768, device="cuda", dtype=torch.bfloat16)
+    from spikingjelly_b200.ops import counters
+    for _ in range(3):
+        x.grad = w.grad = None
+        before = counters.by_name().get("gemm_fp8", 0)
+        fp8.linear(x, w, None, sc).backward(g)
+    assert counters.by_name().get("gemm_fp8", 0) - before == 3          # forward, data gradient, weight gradient
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().clone().requires_grad_(True)
+    torch.nn.functional.linear(xr, wr).backward(g.float())
+    cos = lambda a, b_: torch.nn.functional.cosine_similarity(a.flatten().float(), b_.flatten().float(), dim=0).item()
+    assert cos(x.grad, xr.grad) > 0.99 and cos(w.grad, wr.grad) > 0.99, (cos(x.grad, xr.grad), cos(w.grad, wr.grad))
