@@ -32,6 +32,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--fp8", action="store_true", help="run the four linear layers of every block through the fp8 linear (TP = 1)")
+    ap.add_argument("--fp8-recipe", choices=["delayed", "current"], default="delayed")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours",
                     help="reference: the same architecture assembled from the reference package's parts (benchmark/snn_llm_reference_parts.py)")
     ap.add_argument("--path", choices=["megatron", "fused"], default="megatron",
@@ -77,13 +78,15 @@ def main():
                 holder.params = torch.nn.ParameterList(model.replicated_parameters())
                 sync_replicated = SNNDataParallel(holder, reduce="sum", timeout_s=120.0)
     if a.fp8:
-        # per-tensor scaled e4m3 operands on the tcgen05 kind::f8f6f4 GEMM (spikes are exact in e4m3); the LM head stays bf16
+        # per-tensor scaled e4m3 / e5m2 operands on the tcgen05 kind::f8f6f4 GEMM in all three products (spikes are exact in
+        # e4m3); the LM head stays bf16
         from spikingjelly_b200.ops import fp8
         if world > 1:
             raise SystemExit("--fp8 is wired for TP = 1 in this script")
         for blk in model.blocks:
             for lin in (blk.attn.qkv, blk.attn.proj, blk.ffn.up, blk.ffn.down):
-                lin.forward = (lambda x, m=lin: fp8.linear(x, m.weight, m.bias))
+                sc = fp8.LinearScaling() if a.fp8_recipe == "delayed" else None
+                lin.forward = (lambda x, m=lin, sc=sc: fp8.linear(x, m.weight, m.bias, sc))
     # the fused AdamW kernel takes one kind of tensor per call: sharded (DTensor) and plain parameters get an optimiser each
     from torch.distributed.tensor import DTensor
     kinds = {}
@@ -128,7 +131,7 @@ def main():
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
         peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
         tflops = 3.0 * fwd_flops / (ms / 1e3) / 1e12 / world
-        rec = {"config": f"SNN-LLM {a.layers}L d2048 ffn5504 T4 seq{a.seq} mb{a.micro_batch} {"fp8" if a.fp8 else "bf16"} tp{world}", "n_gpus": world,
+        rec = {"config": f"SNN-LLM {a.layers}L d2048 ffn5504 T4 seq{a.seq} mb{a.micro_batch} {("fp8-" + a.fp8_recipe) if a.fp8 else "bf16"} tp{world}", "n_gpus": world,
                "impl": a.impl, "path": a.path if a.impl == "ours" else "reference DTensor TP",
                "ms_per_step": round(ms, 2), "tokens_per_s": round(tokens / ms * 1e3, 1), "model_tflops_per_gpu": round(tflops, 1),
                "of_measured_sustained_bf16_peak": round(tflops / peak, 3), "peak_source": "measured" if peaks else "fallback",

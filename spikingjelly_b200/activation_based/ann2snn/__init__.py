@@ -6,10 +6,11 @@ from .delay import estimate_delay_start
 from .factories import NeuronFactory
 from .modules import ChannelVoltageScaler, VoltageHook, VoltageScaler
 from .qcfs import SignedQCFSSequenceEncoder
-from .recipes import (ConversionRecipe, FXConversionRecipe, LocalThresholdBalancingRecipe, ModuleConversionRecipe, RateCodingRecipe,
+from .recipes import (Qwen2SNNCalibration, Qwen2SNNConfig, Qwen2SNNModel, Qwen2SNNRecipe, calibrate_qwen2_snn, ConversionRecipe, FXConversionRecipe, LocalThresholdBalancingRecipe, ModuleConversionRecipe, RateCodingRecipe,
                       STATransformerRecipe, TransformerTDEquivalentRecipe)
 from .utils import download_url
 
 __all__ = ["Converter", "FXConverter", "ModuleConverter", "ConversionRecipe", "FXConversionRecipe", "ModuleConversionRecipe",
            "RateCodingRecipe", "LocalThresholdBalancingRecipe", "TransformerTDEquivalentRecipe", "STATransformerRecipe", "ChannelVoltageScaler", "VoltageHook",
-           "VoltageScaler", "download_url", "NeuronFactory", "operators", "SignedQCFSSequenceEncoder", "estimate_delay_start"]
+           "VoltageScaler", "download_url", "NeuronFactory", "operators", "SignedQCFSSequenceEncoder", "estimate_delay_start", "Qwen2SNNCalibration",
+           "Qwen2SNNConfig", "Qwen2SNNModel", "Qwen2SNNRecipe", "calibrate_qwen2_snn"]

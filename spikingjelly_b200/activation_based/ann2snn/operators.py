@@ -276,6 +276,9 @@ class TDScaledDotProductAttention(TDModule):
 
     def ann_forward(self, q, k, v):
         mask = self.attn_mask
+        if mask is not None and mask.dim() == q.dim() and mask.shape[0] not in (1, q.shape[0]) and q.shape[0] % mask.shape[0] == 0:
+            # a whole sequence is evaluated with time folded into the batch (time-major): the per-sample mask repeats
+            mask = mask.repeat(q.shape[0] // mask.shape[0], *([1] * (mask.dim() - 1)))
         return F.scaled_dot_product_attention(q, k, v, attn_mask=mask, is_causal=self.is_causal and mask is None, scale=self.scale)
 
     def forward(self, q, k, v, attn_mask: Optional[torch.Tensor] = None):

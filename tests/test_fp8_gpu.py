@@ -96,12 +96,6 @@ def test_fp8_policy_trains_a_spiking_mlp():
     assert all(l == l for l in losses) and min(losses[-5:]) < losses[0], losses
 
 
-def _cpu_copy(state):
-    st = fp8.ScalingState()
-    st.amax3, st.calls = state.amax3.cpu().clone(), state.calls
-    return st
-
-
 @pytest.mark.parametrize("e5m2", [False, True])
 @pytest.mark.parametrize("shape,transpose", [((1000, 40), False), ((128, 256), True), ((192, 128), True), ((64, 384), True)])
 def test_delayed_and_transposing_kernels_follow_the_cpu_formulation(e5m2, shape, transpose):
@@ -110,12 +104,17 @@ def test_delayed_and_transposing_kernels_follow_the_cpu_formulation(e5m2, shape,
     cpu_state = fp8.ScalingState()
     for k, s in enumerate((1.0, 2.5, 0.3, 4.0, 1.0)):
         x = (torch.randn(*shape, device="cuda") * s).to(torch.bfloat16)
+        used = None if dev_state.calls == 0 else dev_state.amax3[(dev_state.calls + 2) % 3].clone()
         q, qt, inv = fp8.quantize_with(x, dev_state, e5m2=e5m2, transpose=transpose)
-        rq, rqt, rinv = fp8.quantize_with(x.cpu(), cpu_state, e5m2=e5m2, transpose=transpose)
+        # scale and history follow the CPU formulation; the bytes equal the same formula evaluated by PyTorch on the device
+        _, _, rinv = fp8.quantize_with(x.cpu(), cpu_state, e5m2=e5m2, transpose=transpose)
         assert torch.allclose(inv.cpu(), rinv, rtol=1e-6), k
-        assert torch.equal(q.cpu().view(torch.uint8), rq.view(torch.uint8)), k
+        fmax = fp8.E5M2_MAX if e5m2 else fp8.E4M3_MAX
+        amax_used = x.float().abs().max() if used is None else used
+        ref = (x.float() * (fmax / amax_used)).clamp(-fmax, fmax).to(q.dtype)
+        assert torch.equal(q.view(torch.uint8), ref.view(torch.uint8)), k
         if transpose:
-            assert qt.is_contiguous() and torch.equal(qt.cpu().view(torch.uint8), rqt.view(torch.uint8)), k
+            assert qt.is_contiguous() and torch.equal(qt.view(torch.uint8), ref.t().contiguous().view(torch.uint8)), k
         assert torch.allclose(dev_state.amax3.cpu(), cpu_state.amax3), k
     # current scaling through the transposing kernel
     x = torch.randn(*shape, device="cuda").to(torch.bfloat16)
