@@ -44,6 +44,9 @@ def parse():
     p.add_argument("--impl", choices=["ours", "reference"], default="ours")
     p.add_argument("--batch", type=int, default=PER_GPU_BATCH, help="per-GPU batch")
     p.add_argument("--ref-backend", default="auto", help="reference neuron backend: auto|triton|torch")
+    p.add_argument("--ref-compile", action="store_true",
+                   help="reference arm: wrap the model in torch.compile (the reference's stock modules are compile-friendly; its "
+                        "\"inductor\" backend name exists for FlexSN only, LIFNode offers torch / cupy / triton)")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--config", choices=["spikformer", "sew_resnet", "snn_llm", "neuron"], default="spikformer",
                    help="spikformer (default, the headline): Spikformer-8-512 data parallel; sew_resnet: SEW-ResNet-18 on event frames, "
@@ -289,6 +292,9 @@ def main():
                 print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}))
             return
         extra["reference_backend"] = chosen
+        if args.ref_compile:
+            net = torch.compile(net)
+            extra["reference_compiled"] = True
         if world > 1:
             from spikingjelly.activation_based.distributed.data_parallel import prepare_snn_data_parallel
             net = prepare_snn_data_parallel(net, device_ids=[local_rank])

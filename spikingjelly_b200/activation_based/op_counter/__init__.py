@@ -8,4 +8,6 @@ from .lemaire_addressing import *  # noqa: F401,F403
 from .analytical_energy import *  # noqa: F401,F403
 from .memory_residency import *  # noqa: F401,F403
 from . import spikesim  # noqa: F401
+from . import neuromc  # noqa: F401
+from .neuromc import *  # noqa: F401,F403
 from .spikesim import *  # noqa: F401,F403

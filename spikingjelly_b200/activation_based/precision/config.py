@@ -13,7 +13,7 @@ __all__ = ["PrecisionConfig"]
 class PrecisionConfig:
     mode: str = "fp32"          # fp32 | fp16 | bf16 | fp8 (aliases: fp8-torchao, fp8-te)
     strictness: str = "warn"    # strict: raise if unavailable; warn / silent: fall back to fp32
-    fp8_recipe: str = "auto"    # auto | current | delayed | block | mxfp8 (the native backend implements "current")
+    fp8_recipe: str = "auto"    # auto | current | delayed | block | mxfp8 (native backend: "delayed" and "current"; the other names resolve to "delayed")
     device: Optional[str] = None
 
     def __post_init__(self):

@@ -48,7 +48,7 @@ class _RecipeMixin:
         if recipe not in ("current", "delayed"):
             raise ValueError(f"recipe must be 'current' or 'delayed', got {recipe!r}")
         self.__dict__["fp8_recipe"] = recipe
-        self.__dict__["_scalings"] = [fp8.LinearScaling() for _ in range(self._n_products)] if recipe == "delayed" else None
+        self.__dict__["_scalings"] = [fp8.LinearScaling(delayed=recipe == "delayed") for _ in range(self._n_products)]
 
     def _scaling(self, i: int = 0):
         sc = self.__dict__.get("_scalings")

@@ -132,10 +132,25 @@ def quantize_with(x: torch.Tensor, state: Optional[ScalingState], e5m2: bool = F
 
 
 class LinearScaling:
-    """The three tensor roles of one fp8 linear layer under delayed scaling."""
+    """Per-layer state of an fp8 linear: the three tensor roles under delayed scaling (``delayed=False``: every tensor
+    is scaled by its own maximum and only the weight cache below is used), and the quantised weight of the last
+    gradient-free call, reused while the parameter has not been written (inference quantises the weight once)."""
 
-    def __init__(self):
+    def __init__(self, delayed: bool = True):
+        self.delayed = bool(delayed)
         self.x, self.w, self.g = ScalingState(), ScalingState(), ScalingState()
+        self._frozen = None                 # (data_ptr, version, wq, inv_scale)
+
+    def role(self, name: str) -> Optional[ScalingState]:
+        return getattr(self, name) if self.delayed else None
+
+    def frozen_weight(self, weight: torch.Tensor):
+        key = (weight.data_ptr(), weight._version)
+        if self._frozen is None or self._frozen[0] != key:
+            w16 = weight.detach() if weight.dtype in (torch.bfloat16, torch.float16) else weight.detach().to(torch.bfloat16)
+            wq, _, sw = quantize_with(w16, None)
+            self._frozen = (key, wq, sw)
+        return self._frozen[1], self._frozen[2]
 
 
 def _mm(a_q, b_q, sa, sb, out_f32=False):
@@ -158,8 +173,8 @@ class _Fp8Linear(torch.autograd.Function):
         need_gw, need_gx = weight.requires_grad, x2d.requires_grad
         x16 = x2d if x2d.dtype in (torch.bfloat16, torch.float16) else x2d.to(torch.bfloat16)
         w16 = weight.detach() if weight.dtype in (torch.bfloat16, torch.float16) else weight.detach().to(torch.bfloat16)
-        xq, xqt, sx = quantize_with(x16, scaling.x if scaling else None, transpose=need_gw)
-        wq, wqt, sw = quantize_with(w16, scaling.w if scaling else None, transpose=need_gx)
+        xq, xqt, sx = quantize_with(x16, scaling.role("x") if scaling else None, transpose=need_gw)
+        wq, wqt, sw = quantize_with(w16, scaling.role("w") if scaling else None, transpose=need_gx)
         y = _mm(xq, wq, sx, sw)
         if bias is not None:
             y = y + bias.to(y.dtype)
@@ -175,7 +190,7 @@ class _Fp8Linear(torch.autograd.Function):
         if g16.dtype not in (torch.bfloat16, torch.float16):
             g16 = g16.to(torch.bfloat16)
         need_gx, need_gw = ctx.needs_input_grad[0] and wqt is not None, ctx.needs_input_grad[1] and xqt is not None
-        gq, gqt, sg = quantize_with(g16, ctx.scaling.g if ctx.scaling else None, e5m2=True, transpose=need_gw)
+        gq, gqt, sg = quantize_with(g16, ctx.scaling.role("g") if ctx.scaling else None, e5m2=True, transpose=need_gw)
         if need_gx:
             gx = _mm(gq, wqt, sg, sw).to(ctx.in_dtype)                 # [M, N] x [K, N]^T
         if need_gw:
@@ -194,5 +209,16 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     m = x.numel() // max(k, 1)
     if k % 16 or n % 16 or m % 16:
         return torch.nn.functional.linear(x, weight, bias)
-    y = _Fp8Linear.apply(x.reshape(-1, k), weight, bias, scaling)
+    x2d = x.reshape(-1, k)
+    if scaling is not None and not (torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad or (bias is not None and bias.requires_grad))):
+        # nothing to differentiate: quantise the activation only, the weight's bytes are kept between calls
+        x16 = x2d if x2d.dtype in (torch.bfloat16, torch.float16) else x2d.to(torch.bfloat16)
+        xq, _, sx = quantize_with(x16, scaling.role("x"))
+        wq, sw = scaling.frozen_weight(weight)
+        y = _mm(xq, wq, sx, sw)
+        if bias is not None:
+            y = y + bias.to(y.dtype)
+        y = y.to(x.dtype) if x.dtype != torch.float32 else y.float()
+    else:
+        y = _Fp8Linear.apply(x2d, weight, bias, scaling)
     return y.reshape(*x.shape[:-1], n)

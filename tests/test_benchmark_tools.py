@@ -1,0 +1,45 @@
+"""The benchmark folder's host-side tools: the record analyser and the deterministic SNN-LLM smoke run."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT / "benchmark"))
+
+
+def _records(tmp_path):
+    rows = []
+    for impl, base in (("ours", 1000.0), ("reference", 250.0)):
+        for n in (1, 2, 8):
+            for trial in range(3):
+                rows.append({"impl": impl, "model": "m", "n_gpus": n, "samples_per_s": base * n * (0.95 if n > 1 else 1.0) + trial, "step_ms": 1.0})
+    path = tmp_path / "r.jsonl"
+    path.write_text("header line that is not json\n" + "\n".join(json.dumps(r) for r in rows))
+    return path
+
+
+def test_group_compare_and_scaling(tmp_path, capsys):
+    import analyze_distributed_benchmark as A
+    path = _records(tmp_path)
+    rows = A.load_records(str(path))
+    assert len(rows) == 18
+    table = A.group_and_aggregate(rows, ["impl", "n_gpus"], ["samples_per_s"])
+    assert len(table) == 6 and table[0]["count"] == 3 and table[0]["samples_per_s.median"] == 1001.0
+    cmp_rows = A.compare(rows, ["model", "n_gpus"], "impl", "ours", "reference", "samples_per_s")
+    assert len(cmp_rows) == 3 and all(3.9 < r["ratio"] < 4.1 for r in cmp_rows)
+    sc = A.scaling(A.filter_records(rows, {"impl": "ours"}), ["model"], "n_gpus", "samples_per_s")
+    assert [r["n_gpus"] for r in sc] == [1, 2, 8] and sc[0]["efficiency"] == 1.0 and 0.94 < sc[2]["efficiency"] < 0.96
+    assert A.main([str(path), "--group-by", "impl,n_gpus", "--metric", "samples_per_s", "--format", "csv"]) == 0
+    out = capsys.readouterr().out
+    assert out.splitlines()[0].startswith("impl,n_gpus,count") and len(out.strip().splitlines()) == 7
+    assert A.main([str(path), "--group-by", "model,n_gpus", "--compare", "impl=ours:reference", "--metric", "samples_per_s"]) == 0
+    assert "ratio" in capsys.readouterr().out
+
+
+def test_snn_llm_smoke_is_reproducible(tmp_path):
+    r = subprocess.run([sys.executable, str(ROOT / "benchmark" / "snn_llm_smoke.py"), "--device", "cpu", "--output-dir", str(tmp_path), "--repeat", "2"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    rec = json.loads((tmp_path / "snn_llm_smoke.json").read_text())
+    assert rec["reproducible"] and rec["result"]["loss_decreased"] and len(rec["result"]["parameter_sha256"]) == 64

@@ -65,4 +65,22 @@ def test_policy_resolves_recipes():
         out = pol._convert_modules(net, R)
         lins = [m for m in out.modules() if isinstance(m, Float8Linear)]
         assert len(lins) == 2 and all(m.fp8_recipe == resolved for m in lins)
-        assert (lins[0]._scaling() is None) == (resolved == "current")
+        assert lins[0]._scaling().delayed == (resolved == "delayed")
+
+
+def test_gradient_free_calls_reuse_the_quantised_weight():
+    torch.manual_seed(0)
+    w = torch.nn.Parameter(torch.randn(32, 64) * 0.1)
+    x = torch.randn(16, 64)
+    sc = fp8.LinearScaling()
+    with torch.no_grad():
+        y1 = fp8.linear(x, w, None, sc)
+        first = sc._frozen
+        y2 = fp8.linear(x, w, None, sc)
+        assert sc._frozen is first
+        w.mul_(2.0)                                   # an in-place update invalidates the cached bytes
+        y3 = fp8.linear(x, w, None, sc)
+        assert sc._frozen is not first
+    ref = x @ w.detach().t()
+    assert torch.nn.functional.cosine_similarity(y3.flatten(), ref.flatten(), dim=0) > 0.998
+    assert torch.allclose(y3, 2 * y1, rtol=0.1, atol=0.05)
