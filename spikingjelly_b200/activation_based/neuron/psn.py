@@ -24,6 +24,19 @@ def _psn_params(T: int):
     return weight, bias
 
 
+def _fused_spikes(x_seq, weight, bias, sg):
+    """The one-kernel path (``ops/psn.py``) when the input qualifies, else None."""
+    if not (torch.is_tensor(x_seq) and x_seq.is_cuda):
+        return None
+    from ...ops import psn as psn_op
+    spec = surrogate.surrogate_spec(sg)
+    if not psn_op.supported(x_seq, spec) or x_seq.shape[0] != weight.shape[0]:
+        return None
+    if torch.is_autocast_enabled("cuda") and x_seq.dtype == torch.float32:
+        x_seq = x_seq.to(torch.get_autocast_dtype("cuda"))
+    return psn_op.psn_spikes(x_seq, weight, bias, spec)
+
+
 class PSN(nn.Module, base.MultiStepModule):
     def __init__(self, T: int, surrogate_function=surrogate.ATan()):
         super().__init__()
@@ -33,6 +46,9 @@ class PSN(nn.Module, base.MultiStepModule):
         self.weight, self.bias = _psn_params(T)
 
     def forward(self, x_seq: torch.Tensor):
+        fused = _fused_spikes(x_seq, self.weight, self.bias, self.surrogate_function)
+        if fused is not None:
+            return fused
         h = torch.addmm(self.bias, self.weight, x_seq.flatten(1))
         return self.surrogate_function(h).view(x_seq.shape)
 
@@ -88,6 +104,9 @@ class MaskedPSN(base.MemoryModule):
     def multi_step_functional_forward(self, inputs, states, **kwargs):
         x_seq = inputs[0]
         assert x_seq.shape[0] == self.T
+        fused = _fused_spikes(x_seq, self.masked_weight(), self.bias, self.surrogate_function)
+        if fused is not None:
+            return (fused,), states
         h = torch.addmm(self.bias, self.masked_weight(), x_seq.flatten(1))
         return (self.surrogate_function(h).view(x_seq.shape),), states
 
@@ -137,6 +156,9 @@ class SlidingPSN(base.MemoryModule):
         x_seq = inputs[0]
         if self.backend == "gemm":
             w = self.gen_gemm_weight(x_seq.shape[0])
+            fused = _fused_spikes(x_seq, w, self.bias.reshape(-1).expand(x_seq.shape[0]), self.surrogate_function)
+            if fused is not None:
+                return (fused,), states
             h = torch.addmm(self.bias, w, x_seq.flatten(1)).view(x_seq.shape)
             return (self.surrogate_function(h),), states
         if self.backend == "conv":

@@ -58,7 +58,7 @@ def register() -> None:
         return gq.new_empty((n, s_, h, 3, d))
 
     @reg("sjb200::gemm_fp8")
-    def _(a, b, alpha, out_f32, split_k, alpha2=None):
+    def _(a, b, alpha, out_f32, split_k, alpha2=None, bias=None):
         return a.new_empty((a.shape[0], b.shape[0]), dtype=torch.float32 if out_f32 else torch.bfloat16)
 
     @reg("sjb200::fp8_quantize")
@@ -73,6 +73,19 @@ def register() -> None:
     def _(x, amax3, slot, e5m2):
         f8 = torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn
         return x.new_empty(x.shape, dtype=f8), x.new_empty((x.shape[1], x.shape[0]), dtype=f8), x.new_empty((1,), dtype=torch.float32)
+
+    @reg("sjb200::psn_forward")
+    def _(x, w, b):
+        return torch.empty_like(x)
+
+    @reg("sjb200::psn_backward")
+    def _(x, grad_s, w, b, surrogate_id, p0, p1):
+        return torch.empty_like(x), torch.empty_like(x)
+
+    @reg("sjb200::psn_backward_small")
+    def _(x, grad_s, w, b, surrogate_id, p0, p1):
+        T = x.shape[0]
+        return torch.empty_like(x), x.new_empty((T, T), dtype=torch.float32), x.new_empty((T,), dtype=torch.float32)
 
     @reg("sjb200::bit_pack")
     def _(x):

@@ -161,7 +161,7 @@ std::tuple<at::Tensor, at::Tensor> gemm_16bit_stats(const at::Tensor& a, const a
 // accumulation on the tensor cores.  `alpha`, `alpha2`: optional fp32 device scalars (the two de-quantisation
 // scales), multiplied in the epilogue so that neither a host synchronisation nor a scalar-product kernel is needed.
 at::Tensor gemm_fp8(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& alpha, bool out_f32,
-                    int64_t split_k, const c10::optional<at::Tensor>& alpha2) {
+                    int64_t split_k, const c10::optional<at::Tensor>& alpha2, const c10::optional<at::Tensor>& bias) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2, "gemm_fp8: 2-D CUDA operands required");
     auto fmt = [](const at::Tensor& t) { return t.scalar_type() == at::kFloat8_e4m3fn ? 0 : t.scalar_type() == at::kFloat8_e5m2 ? 1 : -1; };
     const int fa = fmt(a), fb = fmt(b);
@@ -199,6 +199,13 @@ at::Tensor gemm_fp8(const at::Tensor& a, const at::Tensor& b, const c10::optiona
     g.out_bf16 = 1;
     g.alpha = nullptr;
     g.alpha2 = nullptr;
+    g.bias = nullptr;
+    at::Tensor bias_f32;
+    if (bias.has_value() && bias->defined()) {
+        TORCH_CHECK(bias->is_cuda() && bias->numel() == N, "gemm_fp8: bias must hold one value per output column");
+        bias_f32 = bias->to(at::kFloat).contiguous();
+        g.bias = bias_f32.data_ptr<float>();
+    }
     if (alpha2.has_value() && alpha2->defined()) {
         TORCH_CHECK(alpha.has_value() && alpha->defined(), "gemm_fp8: alpha2 needs alpha");
         TORCH_CHECK(alpha2->is_cuda() && alpha2->scalar_type() == at::kFloat && alpha2->numel() == 1, "gemm_fp8: alpha2 must be one fp32 value on the device");
@@ -258,7 +265,7 @@ TORCH_LIBRARY_FRAGMENT(sjb200, m) {
     m.def("gemm_16bit(Tensor a, Tensor b, bool a_mn, bool b_mn, bool out_f32, int split_k) -> Tensor");
     m.def("gemm_16bit_stats(Tensor a, Tensor b, bool a_mn, bool b_mn) -> (Tensor, Tensor)");
     m.def("gemm_16bit_into(Tensor a, Tensor b, bool a_mn, bool b_mn, Tensor(a!) out) -> Tensor(a!)");
-    m.def("gemm_fp8(Tensor a, Tensor b, Tensor? alpha, bool out_f32, int split_k, Tensor? alpha2=None) -> Tensor");
+    m.def("gemm_fp8(Tensor a, Tensor b, Tensor? alpha, bool out_f32, int split_k, Tensor? alpha2=None, Tensor? bias=None) -> Tensor");
     m.def("gemm_status(Tensor like) -> int[]");
     m.def("gemm_set_pair_mode(int mode) -> int");
 }

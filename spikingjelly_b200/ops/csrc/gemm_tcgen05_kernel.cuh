@@ -75,6 +75,7 @@ struct GemmArgs {
     int out_bf16;           // 16-bit results are bf16 (else fp16)
     const float* alpha;     // optional device scalar multiplied into the result (an fp8 de-quantisation scale, or the product of two)
     const float* alpha2;    // optional second device scalar (used only together with `alpha`)
+    const float* bias;      // optional fp32 vector [N] added to every row (by split 0 when the contraction is split)
     float* stats;           // optional [ceil(M / 128) * 4][2][N]: per-column sum and sum of squares of the rounded
                             // 16-bit result over each 32-row slice (batch-norm statistics without re-reading D)
 };
@@ -127,6 +128,11 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int c_begin, i
             for (int q = 0; q < 32; ++q) cur[q] = __float_as_uint(__uint_as_float(cur[q]) * alpha);
         }
         const int col0 = n0 + c * 32;
+        if (g.bias != nullptr && split == 0) {
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+                if (col0 + q < g.N) cur[q] = __float_as_uint(__uint_as_float(cur[q]) + __ldg(g.bias + col0 + q));
+        }
         if (g.out_f32) {
             // split-K partial sums / fp32 results: straight from registers, one 128-byte run per row
             if (row < g.M && col0 < g.N) {

@@ -39,7 +39,7 @@ def quantize(x: torch.Tensor, e5m2: bool = False) -> Tuple[torch.Tensor, torch.T
         return torch.ops.sjb200.fp8_quantize(x, e5m2)
     fmax = E5M2_MAX if e5m2 else E4M3_MAX
     amax = x.detach().abs().amax().float()
-    scale = torch.where(amax > 0, fmax / amax, torch.ones_like(amax))
+    scale = torch.where(amax > 0, torch.full_like(amax, fmax) / amax, torch.ones_like(amax))
     q = (x.float() * scale).clamp(-fmax, fmax).to(torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn)
     return q, (1.0 / scale).reshape(1)
 
@@ -84,7 +84,8 @@ class ScalingState:
 
 
 def _quantize_reference(x, fmax, f8, amax):
-    scale = torch.where(amax > 0, fmax / amax, torch.ones_like(amax))
+    # tensor / tensor is a true division like the kernel's; ``float / tensor`` would be reciprocal-times-scalar, one ulp off
+    scale = torch.where(amax > 0, torch.full_like(amax, fmax) / amax, torch.ones_like(amax))
     return (x.float() * scale).clamp(-fmax, fmax).to(f8), (1.0 / scale).reshape(1)
 
 
@@ -153,14 +154,28 @@ class LinearScaling:
         return self._frozen[1], self._frozen[2]
 
 
-def _mm(a_q, b_q, sa, sb, out_f32=False):
+def _mm(a_q, b_q, sa, sb, out_f32=False, bias=None):
+    """``sa * sb * a_q @ b_q.T (+ bias)``; scales and bias are applied in the GEMM epilogue."""
     if _native(a_q):
         from . import counters, require
         require()
         counters.bump("gemm_fp8")
-        return torch.ops.sjb200.gemm_fp8(a_q, b_q, sa, out_f32, 0, sb)
+        return torch.ops.sjb200.gemm_fp8(a_q, b_q, sa, out_f32, 0, sb, bias)
     y = (a_q.float() @ b_q.float().t()) * (sa * sb)
+    if bias is not None:
+        y = y + bias.float()
     return y if out_f32 else y.to(torch.bfloat16)
+
+
+def _result_dtype(x: torch.Tensor) -> torch.dtype:
+    """What ``F.linear`` would return for this input: the autocast dtype inside an autocast region, else the input's."""
+    if torch.is_autocast_enabled(x.device.type):
+        return torch.get_autocast_dtype(x.device.type)
+    return x.dtype
+
+
+def _as(y: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    return y if y.dtype == dtype else y.to(dtype)
 
 
 class _Fp8Linear(torch.autograd.Function):
@@ -175,12 +190,10 @@ class _Fp8Linear(torch.autograd.Function):
         w16 = weight.detach() if weight.dtype in (torch.bfloat16, torch.float16) else weight.detach().to(torch.bfloat16)
         xq, xqt, sx = quantize_with(x16, scaling.role("x") if scaling else None, transpose=need_gw)
         wq, wqt, sw = quantize_with(w16, scaling.role("w") if scaling else None, transpose=need_gx)
-        y = _mm(xq, wq, sx, sw)
-        if bias is not None:
-            y = y + bias.to(y.dtype)
+        y = _mm(xq, wq, sx, sw, bias=None if bias is None else bias.detach())
         ctx.save_for_backward(xqt, sx, wqt, sw)
         ctx.scaling, ctx.has_bias, ctx.in_dtype, ctx.w_dtype = scaling, bias is not None, x2d.dtype, weight.dtype
-        return y.to(x2d.dtype) if x2d.dtype != torch.float32 else y.float()
+        return _as(y, _result_dtype(x2d))
 
     @staticmethod
     def backward(ctx, gy):
@@ -196,7 +209,7 @@ class _Fp8Linear(torch.autograd.Function):
         if need_gw:
             gw = _mm(gqt, xqt, sg, sx, out_f32=True).to(ctx.w_dtype)   # [N, M] x [K, M]^T
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            gb = gy.float().sum(0)
+            gb = gy.sum(0, dtype=torch.float32)
         return gx, gw, gb, None
 
 
@@ -215,10 +228,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         x16 = x2d if x2d.dtype in (torch.bfloat16, torch.float16) else x2d.to(torch.bfloat16)
         xq, _, sx = quantize_with(x16, scaling.role("x"))
         wq, sw = scaling.frozen_weight(weight)
-        y = _mm(xq, wq, sx, sw)
-        if bias is not None:
-            y = y + bias.to(y.dtype)
-        y = y.to(x.dtype) if x.dtype != torch.float32 else y.float()
+        y = _as(_mm(xq, wq, sx, sw, bias=bias), _result_dtype(x))
     else:
         y = _Fp8Linear.apply(x2d, weight, bias, scaling)
     return y.reshape(*x.shape[:-1], n)

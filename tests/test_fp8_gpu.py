@@ -111,7 +111,7 @@ def test_delayed_and_transposing_kernels_follow_the_cpu_formulation(e5m2, shape,
         assert torch.allclose(inv.cpu(), rinv, rtol=1e-6), k
         fmax = fp8.E5M2_MAX if e5m2 else fp8.E4M3_MAX
         amax_used = x.float().abs().max() if used is None else used
-        ref = (x.float() * (fmax / amax_used)).clamp(-fmax, fmax).to(q.dtype)
+        ref = (x.float() * (torch.full_like(amax_used, fmax) / amax_used)).clamp(-fmax, fmax).to(q.dtype)       # true division, as in the kernel
         assert torch.equal(q.view(torch.uint8), ref.view(torch.uint8)), k
         if transpose:
             assert qt.is_contiguous() and torch.equal(qt.view(torch.uint8), ref.t().contiguous().view(torch.uint8)), k
@@ -135,6 +135,29 @@ def test_gemm_fp8_mixes_formats_and_takes_two_scales():
     assert torch.allclose(got, ref, rtol=1e-4, atol=1e-2)
     got = torch.ops.sjb200.gemm_fp8(b, a, s1, True, 0, None)
     assert torch.allclose(got, (b.float() @ a.float().t()) * 0.5, rtol=1e-4, atol=1e-2)
+    # bias added in the epilogue, also when the contraction is split (only the first split adds it)
+    bias = torch.randn(384, device="cuda")
+    for split in (0, 1, 4):
+        got = torch.ops.sjb200.gemm_fp8(a, b, s1, True, split, s2, bias)
+        assert torch.allclose(got, ref + bias, rtol=1e-4, atol=1e-2), split
+    got16 = torch.ops.sjb200.gemm_fp8(a, b, s1, False, 0, s2, bias)
+    assert got16.dtype == torch.bfloat16 and torch.allclose(got16.float(), ref + bias, rtol=2e-2, atol=0.5)
+
+
+def test_fp8_linear_returns_the_autocast_dtype():
+    x = torch.randn(64, 128, device="cuda")
+    w = torch.randn(256, 128, device="cuda", requires_grad=True)
+    b = torch.randn(256, device="cuda", requires_grad=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = fp8.linear(x, w, b)
+        with torch.no_grad():
+            y2 = fp8.linear(x, w, b, fp8.LinearScaling())
+    assert y.dtype == torch.bfloat16 and y2.dtype == torch.bfloat16
+    assert fp8.linear(x, w, b).dtype == torch.float32
+    ref = torch.nn.functional.linear(x, w, b)
+    assert torch.nn.functional.cosine_similarity(y.float().flatten(), ref.flatten(), dim=0) > 0.995
+    y.float().sum().backward()
+    assert torch.allclose(b.grad, torch.full_like(b, 64.0))
 
 
 @pytest.mark.parametrize("delayed", [False, True])
