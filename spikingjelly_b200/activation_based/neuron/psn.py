@@ -34,7 +34,7 @@ def _fused_spikes(x_seq, weight, bias, sg):
         return None
     if torch.is_autocast_enabled("cuda") and x_seq.dtype == torch.float32:
         x_seq = x_seq.to(torch.get_autocast_dtype("cuda"))
-    return psn_op.psn_spikes(x_seq, weight, bias, spec)
+    return psn_op.psn_spikes(x_seq, weight, bias, spec, sg)
 
 
 class PSN(nn.Module, base.MultiStepModule):

@@ -15,14 +15,15 @@ def _eager(x, w, b, sg):
 
 @pytest.mark.parametrize("T", [1, 4, 7, 16, 32])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
-def test_matches_eager(T, dtype):
+@pytest.mark.parametrize("with_sg", [False, True])
+def test_matches_eager(T, dtype, with_sg):
     torch.manual_seed(T)
     sg = surrogate.ATan()
     x = (torch.randn(T, 6, 200, device="cuda") * 0.7).to(dtype).requires_grad_(True)
     w = (torch.randn(T, T, device="cuda") * 0.5).requires_grad_(True)
     b = (torch.randn(T, 1, device="cuda") * 0.1).requires_grad_(True)
     g = torch.randn(T, 6, 200, device="cuda").to(dtype)
-    s = psn_op.psn_spikes(x, w, b, surrogate.surrogate_spec(sg))
+    s = psn_op.psn_spikes(x, w, b, surrogate.surrogate_spec(sg), sg if with_sg else None)
     gx, gw, gb = torch.autograd.grad(s, (x, w, b), g)
     xr = x.detach().float().requires_grad_(True)
     wr, br = w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
