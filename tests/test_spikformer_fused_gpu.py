@@ -103,10 +103,10 @@ def test_fused_matches_same_schedule_oracle(dims, heads):
     from spikingjelly_b200.ops import gemm
     gemm.check_status(x)
     cos = F.cosine_similarity(out_f.float().flatten(), out_o.float().flatten(), dim=0).item()
-    assert cos > 0.995, cos
+    assert cos > 0.9999, cos                     # measured 0.9999998
     worst = min((F.cosine_similarity(g_f[n].flatten(), g_o[n].flatten(), dim=0).item(), n)
                 for n in g_o if g_o[n].norm() > 0)
-    assert worst[0] > 0.97, worst
+    assert worst[0] > 0.999, worst                # measured 0.99992 (batch-norm affine parameters of the stem)
 
 
 def test_fused_vs_modular_statistics():
@@ -143,3 +143,61 @@ def test_sequence_input_and_eval_mode():
         b = net(x).float()
     assert a.abs().sum() > 0
     assert F.cosine_similarity(a.flatten(), b.flatten(), dim=0) > 0.9
+
+
+def _reference_spikformer(**cfg):
+    """The unmodified reference package's Spikformer (installed under ``baseline/_ref``), or a skip."""
+    import sys
+    from pathlib import Path
+    ref = Path(__file__).resolve().parents[1] / "baseline" / "_ref"
+    if not (ref / "spikingjelly").is_dir():
+        pytest.skip("reference package is not installed under baseline/_ref")
+    if str(ref) not in sys.path:
+        sys.path.insert(0, str(ref))
+    from spikingjelly.activation_based import functional as ref_functional
+    from spikingjelly.activation_based.model import spikformer as ref_spikformer
+    return ref_spikformer.Spikformer(backend="torch", **cfg), ref_functional
+
+
+def test_against_the_reference_package_with_shared_weights():
+    cfg = dict(T=4, img_size_h=64, img_size_w=64, embed_dims=128, num_heads=4, depths=2, num_classes=16)
+    ref, ref_functional = _reference_spikformer(**cfg)
+    ref = ref.to(DEV)
+    torch.manual_seed(0)
+    net = spikformer.Spikformer(backend="cuda", **cfg).to(DEV)
+    missing = net.load_state_dict(ref.state_dict(), strict=True)          # same module tree, same keys
+    assert not missing.missing_keys and not missing.unexpected_keys
+    x = torch.randn(8, 3, 64, 64, device=DEV)
+    y = torch.randint(0, 16, (8,), device=DEV)
+    # 1. fp32, module by module: the same arithmetic as the reference's eager path
+    net.fused = False
+    out_r = ref(x)
+    F.cross_entropy(out_r.mean(0), y).backward()
+    ref_functional.reset_net(ref)
+    out_m = net(x)
+    F.cross_entropy(out_m.mean(0), y).backward()
+    functional.reset_net(net)
+    g_r = {n: p.grad.detach().clone() for n, p in ref.named_parameters() if p.grad is not None}
+    g_m = _grads(net)
+    assert torch.allclose(out_m, out_r, rtol=1e-3, atol=1e-4), (out_m - out_r).abs().max()
+    for n in g_r:
+        if g_r[n].norm() > 0:
+            assert F.cosine_similarity(g_m[n].flatten(), g_r[n].flatten(), dim=0) > 0.999, n
+    # 2. the fused bf16 schedule against the reference.  A randomly initialised spiking network amplifies rounding: the
+    #    reference's own bf16-autocast output has cosine 0.93 with its fp32 output.  The fused schedule must agree with
+    #    the fp32 reference at least as well as the reference's bf16 run does (gradients of this chaotic pair are not
+    #    comparable parameter by parameter; test_fused_matches_same_schedule_oracle checks them to 0.999).
+    net.zero_grad(set_to_none=True)
+    net.fused = True
+    with torch.autocast("cuda", dtype=BF):
+        out_f = net(x)
+        out_r16 = ref(x)
+    ref_functional.reset_net(ref)
+    loss_f = F.cross_entropy(out_f.float().mean(0), y)
+    loss_f.backward()
+    functional.reset_net(net)
+    agree = lambda a, b: F.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0).item()
+    assert agree(out_f, out_r) > agree(out_r16, out_r) - 0.03, (agree(out_f, out_r), agree(out_r16, out_r))
+    assert agree(out_f.float().mean(0), out_r.mean(0)) > 0.95
+    assert abs(float(loss_f) - float(F.cross_entropy(out_r.detach().mean(0), y))) < 0.05
+    assert all(torch.isfinite(g).all() for g in _grads(net).values())
