@@ -153,8 +153,9 @@ def main():
                             return f
                         row = {"neuron": kind, "soft_reset": soft, "dtype": dname, "T": T, "N": N}
                         if dname == "fp8":
-                            # x is stored as e4m3 (1 byte); spikes and gradients are bf16.  The reference has no fp8 path: its
-                            # columns are timed on the same values widened to bf16.
+                            # x is stored as e4m3 (1 byte); spikes and gradients are bf16.  The reference column is its
+                            # mixed-precision LIF (`multistep_lif_mp`: fp8 storage, fp32 compute, bf16 spikes), which exists for
+                            # LIF only; IF rows keep the reference's bf16 kernels on the widened values.
                             if kind not in kind_id:
                                 continue
                             x8 = x.detach().to(torch.float8_e4m3fn)
@@ -171,6 +172,21 @@ def main():
                             row["ours_us"] = round(time_fn(run(net, Ours), flush), 2)
                             bytes_moved = 5 * T * N * x.element_size()
                         row["ours_GBps"] = round(bytes_moved / row["ours_us"] / 1e3, 1)
+                        if Ref is not None and dname == "fp8" and kind in ("lif", "lif_ndi"):
+                            try:
+                                from spikingjelly.activation_based.triton_kernel.neuron_kernel.lif import multistep_lif_mp
+                                sgf = Ref.surrogate.ATan()
+                                v0 = torch.zeros(N, device=dev, dtype=torch.bfloat16)
+
+                                def ref_mp():
+                                    x.grad = None
+                                    out = multistep_lif_mp(x, v0, decay_input=(kind == "lif"), tau=2.0, v_threshold=1.0, v_reset=None if soft else 0.0,
+                                                           storage_dtype=torch.float8_e4m3fn, compute_dtype="fp32", backward_compute_dtype="fp32",
+                                                           spike_dtype=torch.bfloat16, surrogate_function=sgf)
+                                    out[0].backward(g)
+                                row["ref_triton_mp_fp8_us"] = round(time_fn(ref_mp, flush, iters=5, warmup=2), 2)
+                            except Exception as exc:
+                                row["ref_triton_mp_fp8_err"] = f"{type(exc).__name__}: {exc}"[:160]
                         if Ref is not None:
                             for be in args.ref_backends.split(","):
                                 if be == "torch" and T * N > (1 << 27):

@@ -105,7 +105,7 @@ def register() -> None:
 
     # ------------------------------------------------------------------ neuron scan
     def _state_dtype(x):
-        return torch.bfloat16 if x.dtype == torch.float8_e4m3fn else x.dtype
+        return torch.bfloat16 if x.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) else x.dtype
 
     @reg("sjb200::scan_forward")
     def _(x_seq, v_init, v_init_scalar, r, kind, tau, q0, q1, q2, v_th, v_reset, soft_reset, store_v_seq, pack_bits, save_ckpt):

@@ -8,6 +8,7 @@
 // The normalised tensor never exists in memory.  Per-channel reductions use per-block partial
 // sums in a scratch buffer that a finalize kernel adds in a fixed order (deterministic).
 #include <ATen/ATen.h>
+#include <cstdlib>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
@@ -584,7 +585,13 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> bn_lif_backward(
         long long gcd_a = C, gcd_b = (long long)kThreads * V1;
         while (gcd_b) { const long long t = gcd_a % gcd_b; gcd_a = gcd_b; gcd_b = t; }
         const long long m = C / gcd_a;
-        const long long want = std::max<long long>(1, std::min<long long>((n_vec + kThreads - 1) / kThreads, (long long)sms * 3));
+        // The grid is one wave of resident blocks (a grid-stride loop covers the rest): with more blocks than fit, the
+        // last partial wave ran on half-empty SMs (1.5 waves measured: 444 blocks on 148 x 2 slots).
+        // SJB200_BNLIF_OCC=3 selects the 80-register build (three CTAs per SM, 46 bytes of spills): measured equal or
+        // slower than the 114-register build with two CTAs, which stays the default.
+        static const int occ_choice = [] { const char* e = std::getenv("SJB200_BNLIF_OCC"); return e ? std::atoi(e) : 2; }();
+        const int occ = (T == TCB && occ_choice == 3) ? 3 : 2;
+        const long long want = std::max<long long>(1, std::min<long long>((n_vec + kThreads - 1) / kThreads, (long long)sms * occ));
         const int grid1 = (int)(std::max<long long>(1, want / m) * m);
         at::Tensor partial = at::empty({grid1, 2, C}, fopt);
         SJ_BN_KIND(kind, {
@@ -594,7 +601,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> bn_lif_backward(
                     scale.data_ptr<float>(), shift.data_ptr<float>(), ck,
                     reinterpret_cast<scalar_t*>(gx.data_ptr()), partial.data_ptr<float>());
             };
-            if (T == TCB) launch(bn_lif_backward1_kernel<scalar_t, V1, KIND, TCB>);
+            if (T == TCB && occ == 3) launch(bn_lif_backward1_kernel<scalar_t, V1, KIND, TCB, 3>);     // 80 registers, three CTAs per SM
+            else if (T == TCB) launch(bn_lif_backward1_kernel<scalar_t, V1, KIND, TCB, 2>);
             else launch(bn_lif_backward1_kernel<scalar_t, V1, KIND, 0>);
         });
         C10_CUDA_KERNEL_LAUNCH_CHECK();

@@ -44,17 +44,19 @@ ScanParams make_params(const Dims& d, int64_t kind, double tau, double q0, doubl
     return p;
 }
 
-// scalar_t: storage type of x_seq; state_t: type of spikes, potentials and gradients (bf16 when x is fp8-e4m3)
+// scalar_t: storage type of x_seq; state_t: type of spikes, potentials and gradients (bf16 when x is stored as fp8, e4m3 or
+// e5m2).  The recurrence itself always runs in fp32 registers, whatever the storage types.
 #define SJ_DISPATCH_FLOATING(DTYPE, ...)                                                                      \
     switch (DTYPE) {                                                                                           \
     case at::kFloat: { using scalar_t = float; using state_t = float; __VA_ARGS__; break; }                    \
     case at::kHalf: { using scalar_t = __half; using state_t = __half; __VA_ARGS__; break; }                   \
     case at::kBFloat16: { using scalar_t = __nv_bfloat16; using state_t = __nv_bfloat16; __VA_ARGS__; break; } \
     case at::kFloat8_e4m3fn: { using scalar_t = __nv_fp8_e4m3; using state_t = __nv_bfloat16; __VA_ARGS__; break; } \
+    case at::kFloat8_e5m2: { using scalar_t = __nv_fp8_e5m2; using state_t = __nv_bfloat16; __VA_ARGS__; break; }   \
     default: TORCH_CHECK(false, "neuron scan: unsupported dtype ", DTYPE);                                     \
     }
 
-at::ScalarType state_dtype(at::ScalarType x) { return x == at::kFloat8_e4m3fn ? at::kBFloat16 : x; }
+at::ScalarType state_dtype(at::ScalarType x) { return (x == at::kFloat8_e4m3fn || x == at::kFloat8_e5m2) ? at::kBFloat16 : x; }
 
 int chunk_for(int T) { return T <= 4 ? 4 : 8; }
 

@@ -156,14 +156,15 @@ def test_deterministic_twice():
 @pytest.mark.gpu
 @pytest.mark.parametrize("T,N", [(4, 4096), (8, 4096), (16, 1000), (5, 777)])
 @pytest.mark.parametrize("kind", ["if", "lif_di", "lif_ndi"])
-def test_fp8_e4m3_input_equals_bf16_kernel_on_the_same_values(T, N, kind):
-    """x stored as one byte per element: every e4m3 value is exact in bf16, so spikes, final potential and the input
-    gradient must be bit-identical to the bf16 kernel fed with the widened tensor."""
+@pytest.mark.parametrize("storage", [torch.float8_e4m3fn, torch.float8_e5m2])
+def test_fp8_input_equals_bf16_kernel_on_the_same_values(T, N, kind, storage):
+    """x stored as one byte per element (e4m3 or e5m2): every fp8 value is exact in bf16, so spikes, final potential and
+    the input gradient must be bit-identical to the bf16 kernel fed with the widened tensor."""
     from spikingjelly_b200 import ops
     from spikingjelly_b200.ops.neuron_scan import KIND
     ops.require()
     torch.manual_seed(0)
-    x8 = (torch.randn(T, N, device="cuda") + 0.5).to(torch.float8_e4m3fn)
+    x8 = (torch.randn(T, N, device="cuda") + 0.5).to(storage)
     x16 = x8.to(torch.bfloat16)
     g = torch.randn(T, N, device="cuda").to(torch.bfloat16)
     k = KIND[kind]
