@@ -65,6 +65,7 @@ class CKernel:
         self.reserved_cnames: list = []
         self.kernel_name = kernel_name
         self._core = ""
+        self.extra_headers = ""             # source text placed before the kernel (device helpers the fragments call)
         self._lib = None
         self._built_source: Optional[str] = None
 
@@ -109,7 +110,7 @@ class CKernel:
     @property
     def translation_unit(self) -> str:
         """:attr:`full_codes` with the includes and the host launcher."""
-        return (_PREAMBLE + self.full_codes +
+        return (_PREAMBLE + self.extra_headers + "\n" + self.full_codes +
                 f'\nextern "C" __attribute__((visibility("default"))) int launch_{self.kernel_name}(unsigned gx, unsigned gy, unsigned gz, '
                 f"unsigned bx, unsigned by, unsigned bz, void* stream, void** args) {{\n"
                 f"    return (int)cudaLaunchKernel((const void*){self.kernel_name}, dim3(gx, gy, gz), dim3(bx, by, bz), args, 0, (cudaStream_t)stream);\n}}\n")
