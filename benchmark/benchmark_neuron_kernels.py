@@ -108,6 +108,8 @@ def main():
                     help="one record only: LIF (tau 2, hard reset, ATan) forward + backward, bf16, T = 4, N = 2^24, for --impl")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--bits", action="store_true", help="also time the bit-only spike output (ours) and the reference's dense kernel + "
+                    "BitSpikeCompressor")
     args = ap.parse_args()
     dev = torch.device("cuda")
     if args.headline:
@@ -171,6 +173,33 @@ def main():
                             net = make(Ours, kind, soft, "cuda").to(dev)
                             row["ours_us"] = round(time_fn(run(net, Ours), flush), 2)
                             bytes_moved = 5 * T * N * x.element_size()
+                            if args.bits and kind in kind_id:
+                                # forward emits only bit-packed spikes (1/8 byte per element); backward is unchanged
+                                from spikingjelly_b200.ops import bitspike
+                                from spikingjelly_b200.ops.neuron_scan import NeuronSpec
+                                spec = NeuronSpec(kind=kind_id[kind], v_threshold=1.0, v_reset=None if soft else 0.0, tau=2.0, sg=(1, 2.0, 0.0))
+
+                                def ours_bits():
+                                    x.grad = None
+                                    bits, _ = bitspike.multistep_neuron_bits(x, 0.0, spec)
+                                    bits.handle.backward(g)
+                                row["ours_bits_us"] = round(time_fn(ours_bits, flush), 2)
+                                if Ref is not None:
+                                    try:
+                                        # the reference's way to keep spikes as bits: its memopt compressor after the dense kernel
+                                        from spikingjelly.activation_based.memopt.compress import BitSpikeCompressor
+                                        rnet = make(Ref, kind, soft, "triton").to(dev)
+                                        comp = BitSpikeCompressor()
+
+                                        def ref_bits():
+                                            x.grad = None
+                                            s = rnet(x)
+                                            comp.compress(s.detach())
+                                            s.backward(g)
+                                            Ref.functional.reset_net(rnet)
+                                        row["ref_triton_bitcompress_us"] = round(time_fn(ref_bits, flush, iters=5, warmup=2), 2)
+                                    except Exception as exc:
+                                        row["ref_triton_bitcompress_err"] = f"{type(exc).__name__}: {exc}"[:160]
                         row["ours_GBps"] = round(bytes_moved / row["ours_us"] / 1e3, 1)
                         if Ref is not None and dname == "fp8" and kind in ("lif", "lif_ndi"):
                             try:

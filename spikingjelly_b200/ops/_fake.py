@@ -108,14 +108,15 @@ def register() -> None:
         return torch.bfloat16 if x.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) else x.dtype
 
     @reg("sjb200::scan_forward")
-    def _(x_seq, v_init, v_init_scalar, r, kind, tau, q0, q1, q2, v_th, v_reset, soft_reset, store_v_seq, pack_bits, save_ckpt):
+    def _(x_seq, v_init, v_init_scalar, r, kind, tau, q0, q1, q2, v_th, v_reset, soft_reset, store_v_seq, pack_bits, save_ckpt,
+          bits_only=False):
         sd = _state_dtype(x_seq)
         T = x_seq.shape[0]
         N = x_seq.numel() // T if T else 0
         chunk = 4 if T <= 4 else 8
         n_ckpt = (T + chunk - 1) // chunk - 1
         none = lambda: x_seq.new_empty((0,))
-        return (x_seq.new_empty(x_seq.shape, dtype=sd), x_seq.new_empty(x_seq.shape[1:], dtype=sd),
+        return (x_seq.new_empty((0,) if bits_only else x_seq.shape, dtype=sd), x_seq.new_empty(x_seq.shape[1:], dtype=sd),
                 x_seq.new_empty(x_seq.shape, dtype=sd) if store_v_seq else none(),
                 x_seq.new_empty((T, (N + 31) // 32), dtype=torch.int32) if pack_bits else none(),
                 x_seq.new_empty((n_ckpt, N), dtype=torch.float32) if (save_ckpt and n_ckpt > 0) else none())

@@ -68,8 +68,9 @@ int64_t scan_chunk(int64_t T) { return chunk_for((int)T); }
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> scan_forward(
     const at::Tensor& x_seq, const c10::optional<at::Tensor>& v_init, double v_init_scalar,
     const c10::optional<at::Tensor>& r, int64_t kind, double tau, double q0, double q1, double q2, double v_th,
-    double v_reset, bool soft_reset, bool store_v_seq, bool pack_bits, bool save_ckpt) {
+    double v_reset, bool soft_reset, bool store_v_seq, bool pack_bits, bool save_ckpt, bool bits_only) {
     TORCH_CHECK(x_seq.is_cuda(), "scan_forward: x_seq must be a CUDA tensor");
+    TORCH_CHECK(!bits_only || pack_bits, "scan_forward: bits_only needs pack_bits");
     const c10::cuda::CUDAGuard guard(x_seq.device());
     at::Tensor x = x_seq.contiguous();
     const Dims d = seq_dims(x);
@@ -81,7 +82,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> scan_forw
     const ScanParams p = make_params(d, kind, tau, q0, q1, q2, r, v_th, v_reset, soft_reset, vi, v_init_scalar);
 
     const auto sopt = x.options().dtype(state_dtype(x.scalar_type()));
-    at::Tensor spike = at::empty(x.sizes(), sopt);
+    // bits_only: the spikes leave the kernel as 1 bit per neuron and nothing else (the dense tensor has no elements)
+    at::Tensor spike = bits_only ? at::empty({0}, sopt) : at::empty(x.sizes(), sopt);
     std::vector<int64_t> state_shape(x.sizes().begin() + 1, x.sizes().end());
     at::Tensor v_last = at::empty(state_shape, sopt);
     // a zero-element tensor stands for an absent optional output (each output gets its own)
@@ -98,14 +100,14 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> scan_forw
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
     SJ_DISPATCH_FLOATING(x.scalar_type(), {
         constexpr int VV = 16 / sizeof(state_t);
-        const bool vec = (d.N % VV == 0) && aligned<scalar_t>(x.data_ptr(), VV) && aligned<state_t>(spike.data_ptr(), VV) &&
+        const bool vec = (d.N % VV == 0) && aligned<scalar_t>(x.data_ptr(), VV) && (bits_only || aligned<state_t>(spike.data_ptr(), VV)) &&
                          aligned<state_t>(v_last.data_ptr(), VV) && aligned<state_t>(p.v_init, VV) &&
                          (!v_seq.has_value() || aligned<state_t>(v_seq->data_ptr(), VV)) &&
                          (!ckpt.has_value() || aligned<float>(ckpt->data_ptr(), VV));
         const int V = vec ? (TC == 8 ? 4 : VV) : 1;
         const long long threads_needed = (d.N + V - 1) / V;
         const unsigned grid = (unsigned)((threads_needed + kThreads - 1) / kThreads);
-        ScanFwdPtrs io{x.data_ptr(), spike.data_ptr(), v_last.data_ptr(),
+        ScanFwdPtrs io{x.data_ptr(), bits_only ? nullptr : spike.data_ptr(), v_last.data_ptr(),
                        v_seq.has_value() ? v_seq->data_ptr() : nullptr,
                        packed.has_value() ? reinterpret_cast<uint32_t*>(packed->data_ptr()) : nullptr,
                        ckpt.has_value() ? ckpt->data_ptr<float>() : nullptr};
@@ -192,7 +194,7 @@ TORCH_LIBRARY_FRAGMENT(sjb200, m) {
     m.def("scan_chunk(int T) -> int", &sjb200::scan_chunk);
     m.def("scan_forward(Tensor x_seq, Tensor? v_init, float v_init_scalar, Tensor? r, int kind, float tau, float q0, "
           "float q1, float q2, float v_th, float v_reset, bool soft_reset, bool store_v_seq, bool pack_bits, "
-          "bool save_ckpt) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
+          "bool save_ckpt, bool bits_only=False) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
     m.def("scan_backward(Tensor grad_spike_seq, Tensor? grad_v_last, Tensor? grad_v_seq, Tensor x_seq, Tensor? v_init, "
           "float v_init_scalar, Tensor? r, Tensor? ckpt, int kind, float tau, float q0, float q1, float q2, float v_th, "
           "float v_reset, bool soft_reset, int sg_id, float sg_p0, float sg_p1, bool detach_reset, "

@@ -149,7 +149,7 @@ scan_forward_kernel(ScanParams p, const TIN* __restrict__ x_seq, TO* __restrict_
                 }
                 const long long off = (long long)(t0 + i) * p.N + n0;
                 if (active) {
-                    store_vec<TO, V>(spike_seq + off, s);
+                    if (LEAN || spike_seq != nullptr) store_vec<TO, V>(spike_seq + off, s);      // null: bit-packed output only
                     if (v_seq != nullptr) store_vec<TO, V>(v_seq + off, v);
                 }
                 if (packed != nullptr) {  // uniform branch: every lane of the warp takes part
