@@ -1,4 +1,8 @@
 """The example scripts run end to end on generated data (CPU, a couple of steps each)."""
+import numpy as np
+import pytest
+import torch
+
 from spikingjelly_b200.activation_based.examples import classify_dvsg, conv_fashion_mnist, flexsn_custom_neuron, lif_fc_mnist
 from spikingjelly_b200.activation_based.examples.memopt import train_distributed
 
@@ -83,3 +87,41 @@ def test_spiking_lstm_text_example_learns_synthetic_languages():
     assert ex.to_ascii("Ślusàrski") == "Slusarski" and ex.word_to_tensor("ab").shape == (2, 1, len(ex.LETTERS))
     s = ex.main(["--synthetic", "--steps", "150", "--hidden", "32"])
     assert s["last_loss"] < s["first_loss"] and s["test_acc"] > 0.4
+
+
+def test_spiking_actor_td3_runs_with_both_actor_kinds():
+    from spikingjelly_b200.activation_based.examples import spiking_actor_td3 as ex
+    for kind in ("ilc", "noisy"):
+        agent, returns = ex.train(kind, steps=260, start_steps=100, update_after=100, batch_size=8, quiet=True)
+        assert agent.updates == 160 and len(returns) == 1 and returns[0] < 0
+        act = agent.act(np.zeros(3, np.float32))
+        assert act.shape == (1,) and abs(float(act[0])) <= 2.0
+    assert ex.SpikingActor(3, 1, 2.0, "noisy").noise_length() == 2 * 64 + 2 * 64 + 2 * 10 + 1
+    with pytest.raises(ValueError):
+        ex.SpikingActor(3, 1, 2.0, "plain")
+
+
+def test_dsqn_and_r11_examples_run():
+    from spikingjelly_b200.activation_based.examples import DSQN
+    from spikingjelly_b200.activation_based.examples import cifar10_r11_enabling_spikebased_backpropagation as r11
+    net, rewards = DSQN.train(frames=160, T=2, size=8, batch_size=8, start=40, sync=50, quiet=True)
+    assert len(rewards) == 160 // 7 and set(rewards) <= {1.0, -1.0}
+    q = net(torch.zeros(2, 1, 8, 8))
+    assert q.shape == (2, 3)
+    _, hist = r11.main(["--synthetic", "-T", "12", "--width", "4", "--image-size", "16", "--samples", "32", "-b", "16", "--epochs", "3", "--device", "cpu",
+                        "--lr", "0.05"])
+    assert len(hist) == 3 and hist[-1][0] < hist[0][0]
+
+
+def test_vector_environments():
+    from functools import partial
+    from spikingjelly_b200.activation_based.examples import _cartpole
+    from spikingjelly_b200.activation_based.examples.common.multiprocessing_env import SerialVecEnv, SubprocVecEnv
+    for cls in (SerialVecEnv, SubprocVecEnv):
+        envs = cls([partial(_cartpole.CartPole, seed=i) for i in range(3)])
+        obs = envs.reset()
+        assert obs.shape == (3, 4) and len(envs) == 3
+        for _ in range(30):
+            obs, rew, done, info = envs.step([1, 0, 1])
+        assert obs.shape == (3, 4) and rew.shape == (3,) and done.dtype == bool and len(info) == 3
+        envs.close()
