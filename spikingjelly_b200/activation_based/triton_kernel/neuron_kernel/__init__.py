@@ -1,0 +1,136 @@
+"""Functional multi-step neurons under the reference's names (``triton_kernel/neuron_kernel/{integrate_and_fire,lif,plif,
+utils}.py``): ``multistep_if``, ``multistep_lif``, ``multistep_plif`` return ``(spike_seq, v_seq)``; the ``*_mp`` forms take
+a storage dtype (fp32 / fp16 / bf16 / fp8 e4m3 / fp8 e5m2), compute dtypes and a spike dtype.  All of them run the CUDA scan
+kernels of this package (``ops/neuron_scan.py``): one kernel per direction, only the input kept for backward.
+
+Differences a caller can see: arithmetic is always fp32 in registers (the compute-dtype arguments are validated and kept in
+the plan, not used to round); with fp8 storage the spikes and gradients are bf16; ``h_seq`` is never materialised, so the
+``*_mp`` functions return ``None`` in its place."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from ... import surrogate as _surrogate
+from ..triton_utils import (is_fp8_dtype, normalize_cuda_device, normalize_triton_compute_dtype_name, normalize_triton_storage_dtype,
+                            torch_dtype_to_triton_neuron_dtype_id, triton_compute_dtype_name_to_neuron_dtype_id)
+
+__all__ = ["multistep_if", "multistep_lif", "multistep_plif", "multistep_if_mp", "multistep_lif_mp", "TritonNeuronExecutionPlan",
+           "prepare_triton_neuron_execution_plan"]
+
+
+def _spec(kind: str, tau: float, v_threshold: float, v_reset: Optional[float], detach_reset: bool, surrogate_function):
+    from ....ops.neuron_scan import KIND, NeuronSpec
+    sg = _surrogate.surrogate_spec(surrogate_function)
+    if sg is None:
+        raise ValueError(f"{type(surrogate_function).__name__} has no kernel descriptor; use one of the table-driven surrogates")
+    return NeuronSpec(kind=KIND[kind], v_threshold=float(v_threshold), v_reset=None if v_reset is None else float(v_reset), tau=float(tau), sg=sg,
+                      detach_reset=bool(detach_reset))
+
+
+def _run(x_seq, v_init, spec, r=None, store_v_seq=True):
+    from ....ops.neuron_scan import multistep_neuron
+    s, v_last, v_seq, _ = multistep_neuron(x_seq, v_init, spec, r=r, store_v_seq=store_v_seq)
+    return s, (v_seq if store_v_seq else v_last.unsqueeze(0))
+
+
+def multistep_if(x_seq, v_init, v_threshold: float, v_reset: Optional[float], detach_reset: bool, surrogate_function, store_v_seq: bool = True):
+    return _run(x_seq, v_init, _spec("if", 2.0, v_threshold, v_reset, detach_reset, surrogate_function), store_v_seq=store_v_seq)
+
+
+def multistep_lif(x_seq, v_init, decay_input: bool, tau: float, v_threshold: float, v_reset: Optional[float], detach_reset: bool,
+                  surrogate_function, store_v_seq: bool = True):
+    return _run(x_seq, v_init, _spec("lif_di" if decay_input else "lif_ndi", tau, v_threshold, v_reset, detach_reset, surrogate_function),
+                store_v_seq=store_v_seq)
+
+
+def multistep_plif(x_seq, v_init, r_tau: torch.Tensor, decay_input: bool, v_threshold: float, v_reset: Optional[float], detach_reset: bool,
+                   surrogate_function):
+    """``r_tau``: the reciprocal time constant ``1 / tau = sigmoid(w)`` as a one-element tensor (learnable)."""
+    return _run(x_seq, v_init, _spec("plif_di" if decay_input else "plif_ndi", 2.0, v_threshold, v_reset, detach_reset, surrogate_function), r=r_tau)
+
+
+@dataclass(frozen=True)
+class TritonNeuronExecutionPlan:
+    """What a mixed-precision call was asked to do; ``matches`` tells whether a cached plan fits another request."""
+    neuron_type: str
+    device: torch.device
+    storage_dtype: torch.dtype
+    forward_compute_dtype_name: str
+    backward_compute_dtype_name: str
+    spike_dtype: torch.dtype
+    storage_dtype_id: int
+    forward_compute_dtype_id: int
+    backward_compute_dtype_id: int
+    spike_dtype_id: int
+    save_intermediates: bool
+
+    def matches(self, *, neuron_type, device, storage_dtype, forward_compute_dtype, backward_compute_dtype="fp32", spike_dtype,
+                save_intermediates) -> bool:
+        try:
+            other = prepare_triton_neuron_execution_plan(neuron_type=neuron_type, device=device, storage_dtype=storage_dtype,
+                                                         forward_compute_dtype=forward_compute_dtype, backward_compute_dtype=backward_compute_dtype,
+                                                         spike_dtype=spike_dtype, save_intermediates=save_intermediates)
+        except (ValueError, RuntimeError, TypeError):
+            return False
+        return other == self
+
+
+def prepare_triton_neuron_execution_plan(*, neuron_type: str, device, storage_dtype, forward_compute_dtype="fp32", backward_compute_dtype="fp32",
+                                         spike_dtype: torch.dtype = torch.float32, save_intermediates: bool = True) -> TritonNeuronExecutionPlan:
+    if neuron_type not in ("if", "lif", "plif"):
+        raise ValueError(f"neuron_type must be one of 'if', 'lif', or 'plif', but got {neuron_type!r}.")
+    storage = normalize_triton_storage_dtype(storage_dtype)
+    fwd, bwd = normalize_triton_compute_dtype_name(forward_compute_dtype), normalize_triton_compute_dtype_name(backward_compute_dtype)
+    for label, name in (("compute_dtype", fwd), ("backward_compute_dtype", bwd)):
+        if name == "fp8" and not is_fp8_dtype(storage):
+            raise ValueError(f"{label}='fp8' requires an fp8 storage dtype.")
+    if spike_dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError(f"Unsupported spike dtype {spike_dtype}.")
+    return TritonNeuronExecutionPlan(neuron_type, normalize_cuda_device(device), storage, fwd, bwd, spike_dtype,
+                                     torch_dtype_to_triton_neuron_dtype_id(storage), triton_compute_dtype_name_to_neuron_dtype_id(fwd, storage),
+                                     triton_compute_dtype_name_to_neuron_dtype_id(bwd, storage), torch_dtype_to_triton_neuron_dtype_id(spike_dtype),
+                                     bool(save_intermediates))
+
+
+def _mp(kind: str, x_seq, v_init, tau, v_threshold, v_reset, storage_dtype, compute_dtype, backward_compute_dtype, spike_dtype, save_intermediates,
+        detach_reset, surrogate_function):
+    plan = prepare_triton_neuron_execution_plan(neuron_type="if" if kind == "if" else "lif", device=x_seq.device, storage_dtype=storage_dtype,
+                                                forward_compute_dtype=compute_dtype, backward_compute_dtype=backward_compute_dtype,
+                                                spike_dtype=spike_dtype, save_intermediates=save_intermediates)
+    sg = surrogate_function if surrogate_function is not None else _surrogate.Sigmoid()
+    spec = _spec(kind, tau, v_threshold, v_reset, detach_reset, sg)
+    x = _ToStorage.apply(x_seq, plan.storage_dtype)
+    state = torch.bfloat16 if is_fp8_dtype(plan.storage_dtype) else plan.storage_dtype
+    v0 = v_init.to(state) if torch.is_tensor(v_init) else v_init
+    s, v_seq = _run(x, v0, spec)
+    return s.to(spike_dtype), v_seq, None
+
+
+class _ToStorage(torch.autograd.Function):
+    """Cast to the storage dtype; the gradient comes back in the caller's dtype (fp8 tensors carry no gradient themselves)."""
+
+    @staticmethod
+    def forward(ctx, x, dtype):
+        ctx.dtype = x.dtype
+        return x.to(dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g.to(ctx.dtype), None
+
+
+def multistep_if_mp(x_seq, v_init, *, v_threshold: float, v_reset: Optional[float], storage_dtype, compute_dtype="fp32",
+                    backward_compute_dtype="fp32", spike_dtype: torch.dtype = torch.float32, save_intermediates: bool = True,
+                    detach_reset: bool = False, surrogate_function=None) -> Tuple[torch.Tensor, torch.Tensor, None]:
+    return _mp("if", x_seq, v_init, 2.0, v_threshold, v_reset, storage_dtype, compute_dtype, backward_compute_dtype, spike_dtype,
+               save_intermediates, detach_reset, surrogate_function)
+
+
+def multistep_lif_mp(x_seq, v_init, *, decay_input: bool, tau: float, v_threshold: float, v_reset: Optional[float], storage_dtype,
+                     compute_dtype="fp32", backward_compute_dtype="fp32", spike_dtype: torch.dtype = torch.float32,
+                     save_intermediates: bool = True, detach_reset: bool = False, surrogate_function=None):
+    return _mp("lif_di" if decay_input else "lif_ndi", x_seq, v_init, tau, v_threshold, v_reset, storage_dtype, compute_dtype,
+               backward_compute_dtype, spike_dtype, save_intermediates, detach_reset, surrogate_function)

@@ -1,0 +1,3 @@
+"""Import path of the reference's ``triton_kernel/neuron_kernel/lif.py``; the functions live in the package's ``__init__``."""
+from . import *  # noqa: F401,F403
+from . import __all__  # noqa: F401

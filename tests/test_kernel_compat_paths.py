@@ -99,3 +99,65 @@ def test_cfunction_expression_builders():
         surrogate.ATan(alpha=2.0)(xt).backward()
         assert evaluate(cf.atan_backward("g", "x", 2.0, "float"), v) == pytest.approx(float(xt.grad), rel=1e-6)
     assert "__floats2half2_rn(g_lo, g_hi)" in cf.sigmoid_backward("g", "x", 4.0, "half2")
+
+
+def test_triton_utils_names_and_execution_plan():
+    import torch
+    from spikingjelly_b200.activation_based.triton_kernel import triton_utils as U
+    from spikingjelly_b200.activation_based.triton_kernel.neuron_kernel import utils as plan_mod
+    assert U.normalize_triton_compute_dtype_name("torch.float16") == "fp16" and U.normalize_triton_compute_dtype_name(torch.bfloat16) == "bf16"
+    assert U.normalize_triton_storage_dtype("e5m2") is torch.float8_e5m2 and U.normalize_triton_storage_dtype(torch.float16) is torch.float16
+    assert U.is_fp8_dtype(torch.float8_e4m3fn) and not U.is_fp8_dtype(torch.float16)
+    assert U.triton_neuron_dtype_id_to_torch_dtype(U.torch_dtype_to_triton_neuron_dtype_id(torch.bfloat16)) is torch.bfloat16
+    assert U.triton_compute_dtype_name_to_neuron_dtype_id("fp8", torch.float8_e4m3fn) == U.TRITON_NEURON_DTYPE_FP8_E4M3FN
+    assert U.torch_dtype_for_triton_compute_dtype("fp8", torch.float8_e5m2) is torch.float8_e5m2
+    assert U.use_static_range_for_triton_neuron_kernel(4) and not U.use_static_range_for_triton_neuron_kernel(16)
+    import pytest
+    for bad in (lambda: U.normalize_triton_compute_dtype_name("int8"), lambda: U.normalize_triton_storage_dtype("int8"),
+                lambda: U.triton_compute_dtype_name_to_neuron_dtype_id("fp8", torch.float16), lambda: U.normalize_cuda_device("cpu")):
+        with pytest.raises(ValueError):
+            bad()
+    plan = plan_mod.prepare_triton_neuron_execution_plan(neuron_type="lif", device="cuda:0", storage_dtype="fp8_e4m3fn", spike_dtype=torch.bfloat16)
+    assert plan.storage_dtype is torch.float8_e4m3fn and plan.forward_compute_dtype_name == "fp32" and plan.spike_dtype_id == 2
+    assert plan.matches(neuron_type="lif", device=0, storage_dtype=torch.float8_e4m3fn, forward_compute_dtype="float32", spike_dtype=torch.bfloat16,
+                        save_intermediates=True)
+    assert not plan.matches(neuron_type="if", device=0, storage_dtype=torch.float8_e4m3fn, forward_compute_dtype="fp32", spike_dtype=torch.bfloat16,
+                            save_intermediates=True)
+    with pytest.raises(ValueError):
+        plan_mod.prepare_triton_neuron_execution_plan(neuron_type="qif", device=0, storage_dtype="fp32")
+    with pytest.raises(ValueError):
+        plan_mod.prepare_triton_neuron_execution_plan(neuron_type="lif", device=0, storage_dtype="fp16", forward_compute_dtype="fp8")
+
+    @U.contiguous_and_device_guard
+    def probe(a, b=None):
+        return a.is_contiguous() and (b is None or b.is_contiguous())
+    assert probe(torch.arange(6).view(2, 3).t(), b=torch.arange(6).view(2, 3).t())
+
+
+@pytest.mark.gpu
+def test_functional_neuron_kernels_match_the_modules():
+    import torch
+    from spikingjelly_b200.activation_based import neuron, surrogate
+    from spikingjelly_b200.activation_based.triton_kernel.neuron_kernel import lif as K
+    torch.manual_seed(0)
+    sg = surrogate.ATan()
+    x = torch.randn(6, 4, 64, device="cuda", requires_grad=True)
+    s, v_seq = K.multistep_lif(x, torch.zeros(4, 64, device="cuda"), True, 2.0, 1.0, 0.0, False, sg)
+    node = neuron.LIFNode(tau=2.0, surrogate_function=sg, step_mode="m", backend="cuda", store_v_seq=True).cuda()
+    x2 = x.detach().clone().requires_grad_(True)
+    s2 = node(x2)
+    assert torch.equal(s, s2) and torch.equal(v_seq, node.v_seq)
+    g = torch.randn_like(s)
+    s.backward(g)
+    s2.backward(g)
+    assert torch.equal(x.grad, x2.grad)
+    xb = torch.randn(6, 4, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    s8, v8, h8 = K.multistep_lif_mp(xb, torch.zeros(4, 64, device="cuda"), decay_input=True, tau=2.0, v_threshold=1.0, v_reset=0.0,
+                                    storage_dtype="fp8_e4m3fn", spike_dtype=torch.bfloat16, surrogate_function=sg)
+    assert s8.dtype == torch.bfloat16 and h8 is None and v8.shape == xb.shape
+    s8.float().sum().backward()
+    assert xb.grad is not None and xb.grad.dtype == torch.bfloat16
+    # same spikes as the bf16 kernel fed with the e4m3-rounded input
+    ref, _ = K.multistep_lif(xb.detach().to(torch.float8_e4m3fn).to(torch.bfloat16), torch.zeros(4, 64, device="cuda", dtype=torch.bfloat16), True, 2.0, 1.0,
+                             0.0, False, sg)
+    assert torch.equal(s8, ref)
