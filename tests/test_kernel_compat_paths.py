@@ -161,3 +161,29 @@ def test_functional_neuron_kernels_match_the_modules():
     ref, _ = K.multistep_lif(xb.detach().to(torch.float8_e4m3fn).to(torch.bfloat16), torch.zeros(4, 64, device="cuda", dtype=torch.bfloat16), True, 2.0, 1.0,
                              0.0, False, sg)
     assert torch.equal(s8, ref)
+
+
+def test_object_handles_switch_and_raw_arguments(monkeypatch):
+    import ctypes
+    import gc
+    import numpy as np
+    import torch
+    from spikingjelly_b200.activation_based.cuda_kernel import cuda_utils as U
+
+    class Thing:
+        pass
+    a, b = Thing(), Thing()
+    ha, hb = U.register_python_object(a), U.register_python_object(b)
+    assert ha != hb and U.register_python_object(a) == ha and U.resolve_python_object(hb) is b
+    del a
+    gc.collect()
+    with pytest.raises(RuntimeError, match="Unknown python object"):
+        U.resolve_python_object(ha)
+    monkeypatch.setenv("SJ_USE_CUPY_OP", "off")
+    assert U.use_cupy_custom_op() is False
+    with pytest.raises(TypeError):
+        U.wrap_args_to_raw_kernel(0, "text")
+    out = U.wrap_args_to_raw_kernel(-1, 3, 2.5, np.float32(1.0), True)
+    assert [type(v) for v in out] == [ctypes.c_int, ctypes.c_float, ctypes.c_float, ctypes.c_bool] and out[1].value == 2.5
+    with pytest.raises(ValueError):
+        U.wrap_args_to_raw_kernel(0, torch.zeros(2))              # a CPU tensor is on device -1
