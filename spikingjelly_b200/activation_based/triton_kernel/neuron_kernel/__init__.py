@@ -30,9 +30,9 @@ def _spec(kind: str, tau: float, v_threshold: float, v_reset: Optional[float], d
                       detach_reset=bool(detach_reset))
 
 
-def _run(x_seq, v_init, spec, r=None, store_v_seq=True):
+def _run(x_seq, v_init, spec, r=None, store_v_seq=True, storage_dtype=None):
     from ....ops.neuron_scan import multistep_neuron
-    s, v_last, v_seq, _ = multistep_neuron(x_seq, v_init, spec, r=r, store_v_seq=store_v_seq)
+    s, v_last, v_seq, _ = multistep_neuron(x_seq, v_init, spec, r=r, store_v_seq=store_v_seq, storage_dtype=storage_dtype)
     return s, (v_seq if store_v_seq else v_last.unsqueeze(0))
 
 
@@ -102,24 +102,13 @@ def _mp(kind: str, x_seq, v_init, tau, v_threshold, v_reset, storage_dtype, comp
                                                 spike_dtype=spike_dtype, save_intermediates=save_intermediates)
     sg = surrogate_function if surrogate_function is not None else _surrogate.Sigmoid()
     spec = _spec(kind, tau, v_threshold, v_reset, detach_reset, sg)
-    x = _ToStorage.apply(x_seq, plan.storage_dtype)
     state = torch.bfloat16 if is_fp8_dtype(plan.storage_dtype) else plan.storage_dtype
     v0 = v_init.to(state) if torch.is_tensor(v_init) else v_init
-    s, v_seq = _run(x, v0, spec)
+    if is_fp8_dtype(plan.storage_dtype):
+        s, v_seq = _run(x_seq, v0, spec, storage_dtype=plan.storage_dtype)        # the cast happens inside the autograd function
+    else:
+        s, v_seq = _run(x_seq.to(plan.storage_dtype), v0, spec)
     return s.to(spike_dtype), v_seq, None
-
-
-class _ToStorage(torch.autograd.Function):
-    """Cast to the storage dtype; the gradient comes back in the caller's dtype (fp8 tensors carry no gradient themselves)."""
-
-    @staticmethod
-    def forward(ctx, x, dtype):
-        ctx.dtype = x.dtype
-        return x.to(dtype)
-
-    @staticmethod
-    def backward(ctx, g):
-        return g.to(ctx.dtype), None
 
 
 def multistep_if_mp(x_seq, v_init, *, v_threshold: float, v_reset: Optional[float], storage_dtype, compute_dtype="fp32",

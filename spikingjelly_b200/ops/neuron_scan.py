@@ -38,8 +38,13 @@ class NeuronSpec:
 class _Scan(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_seq, v_init, r, spec: NeuronSpec, v_init_scalar: float, store_v_seq: bool, pack_bits: bool,
-                need_grad: bool):
+                need_grad: bool, storage_dtype=None):
         vr = 0.0 if spec.soft else float(spec.v_reset)
+        ctx.in_dtype = x_seq.dtype
+        if storage_dtype is not None and storage_dtype != x_seq.dtype:
+            # narrower storage of the input (fp8): cast here, inside the function, so that autograd never sees an fp8
+            # tensor (it would round the returned gradient to the input's fp8 dtype)
+            x_seq = x_seq.to(storage_dtype)
         counters.bump("scan_forward")
         spike, v_last, v_seq, packed, ckpt = torch.ops.sjb200.scan_forward(
             x_seq, v_init, v_init_scalar, r, spec.kind, spec.tau, spec.q[0], spec.q[1], spec.q[2],
@@ -70,16 +75,20 @@ class _Scan(torch.autograd.Function):
             ckpt if ckpt.numel() > 0 else None, spec.kind, spec.tau, spec.q[0], spec.q[1], spec.q[2],
             spec.v_threshold, vr, spec.soft, spec.sg[0], spec.sg[1], spec.sg[2], spec.detach_reset, need_gvi)
         g_r = gr.reshape(r.shape).to(r.dtype) if (ctx.has_r and ctx.needs_input_grad[2]) else None
-        return gx, (gvi if need_gvi else None), g_r, None, None, None, None, None
+        if gx.dtype != ctx.in_dtype and ctx.in_dtype.is_floating_point and ctx.in_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2):
+            gx = gx.to(ctx.in_dtype)
+        return gx, (gvi if need_gvi else None), g_r, None, None, None, None, None, None
 
 
 def multistep_neuron(x_seq: torch.Tensor, v_init, spec: NeuronSpec, r: Optional[torch.Tensor] = None,
-                     store_v_seq: bool = False, pack_bits: bool = False):
+                     store_v_seq: bool = False, pack_bits: bool = False, storage_dtype: Optional[torch.dtype] = None):
     """Run ``T = x_seq.shape[0]`` steps.  ``v_init`` is a tensor shaped like
     ``x_seq[0]`` or a Python float (uniform initial potential, no memory read).
 
     Returns ``(spike_seq, v_last, v_seq | None, packed | None)`` where ``packed`` is an
-    int32 tensor ``[T, ceil(N/32)]``: bit ``i`` of word ``j`` is neuron ``32 j + i``.
+    int32 tensor ``[T, ceil(N/32)]``: bit ``i`` of word ``j`` is neuron ``32 j + i``.  ``storage_dtype`` (fp8 e4m3 / e5m2):
+    the input is rounded to that type and kept for backward in it (1 byte per element); spikes and gradients are then bf16
+    and the gradient comes back in ``x_seq``'s own dtype.
     """
     require()
     if isinstance(v_init, torch.Tensor):
@@ -89,5 +98,5 @@ def multistep_neuron(x_seq: torch.Tensor, v_init, spec: NeuronSpec, r: Optional[
     # grad mode is off inside Function.forward, so decide here whether backward can happen
     need_grad = torch.is_grad_enabled() and (
         x_seq.requires_grad or (v_t is not None and v_t.requires_grad) or (r is not None and r.requires_grad))
-    spike, v_last, v_seq, packed = _Scan.apply(x_seq, v_t, r, spec, v_s, store_v_seq, pack_bits, need_grad)
+    spike, v_last, v_seq, packed = _Scan.apply(x_seq, v_t, r, spec, v_s, store_v_seq, pack_bits, need_grad, storage_dtype)
     return spike, v_last, (v_seq if store_v_seq else None), (packed if pack_bits else None)

@@ -155,12 +155,15 @@ def test_functional_neuron_kernels_match_the_modules():
     s8, v8, h8 = K.multistep_lif_mp(xb, torch.zeros(4, 64, device="cuda"), decay_input=True, tau=2.0, v_threshold=1.0, v_reset=0.0,
                                     storage_dtype="fp8_e4m3fn", spike_dtype=torch.bfloat16, surrogate_function=sg)
     assert s8.dtype == torch.bfloat16 and h8 is None and v8.shape == xb.shape
-    s8.float().sum().backward()
+    g8 = torch.randn_like(s8)
+    s8.backward(g8)
     assert xb.grad is not None and xb.grad.dtype == torch.bfloat16
-    # same spikes as the bf16 kernel fed with the e4m3-rounded input
-    ref, _ = K.multistep_lif(xb.detach().to(torch.float8_e4m3fn).to(torch.bfloat16), torch.zeros(4, 64, device="cuda", dtype=torch.bfloat16), True, 2.0, 1.0,
-                             0.0, False, sg)
-    assert torch.equal(s8, ref)
+    # same spikes AND the same gradient as the bf16 kernel fed with the e4m3-rounded input: the cast to the storage type
+    # happens inside the autograd function, so the gradient is not rounded to fp8 on its way back
+    xw = xb.detach().to(torch.float8_e4m3fn).to(torch.bfloat16).requires_grad_(True)
+    ref, _ = K.multistep_lif(xw, torch.zeros(4, 64, device="cuda", dtype=torch.bfloat16), True, 2.0, 1.0, 0.0, False, sg)
+    ref.backward(g8)
+    assert torch.equal(s8, ref) and torch.equal(xb.grad, xw.grad)
 
 
 def test_object_handles_switch_and_raw_arguments(monkeypatch):
