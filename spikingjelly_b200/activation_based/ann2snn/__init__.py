@@ -7,10 +7,10 @@ from .factories import NeuronFactory
 from .modules import ChannelVoltageScaler, VoltageHook, VoltageScaler
 from .qcfs import SignedQCFSSequenceEncoder
 from .recipes import (Qwen2SNNCalibration, Qwen2SNNConfig, Qwen2SNNModel, Qwen2SNNRecipe, calibrate_qwen2_snn, ConversionRecipe, FXConversionRecipe, LocalThresholdBalancingRecipe, ModuleConversionRecipe, RateCodingRecipe,
-                      STATransformerRecipe, TransformerTDEquivalentRecipe)
+                      STATransformerRecipe, SpikeZIPTFQANNRecipe, TransformerTDEquivalentRecipe)
 from .utils import download_url
 
 __all__ = ["Converter", "FXConverter", "ModuleConverter", "ConversionRecipe", "FXConversionRecipe", "ModuleConversionRecipe",
-           "RateCodingRecipe", "LocalThresholdBalancingRecipe", "TransformerTDEquivalentRecipe", "STATransformerRecipe", "ChannelVoltageScaler", "VoltageHook",
+           "RateCodingRecipe", "LocalThresholdBalancingRecipe", "TransformerTDEquivalentRecipe", "STATransformerRecipe", "SpikeZIPTFQANNRecipe", "ChannelVoltageScaler", "VoltageHook",
            "VoltageScaler", "download_url", "NeuronFactory", "operators", "SignedQCFSSequenceEncoder", "estimate_delay_start", "Qwen2SNNCalibration",
            "Qwen2SNNConfig", "Qwen2SNNModel", "Qwen2SNNRecipe", "calibrate_qwen2_snn"]

@@ -22,6 +22,7 @@ the reference are replaced by one attribute-driven attention wrapper).
 from __future__ import annotations
 
 import copy
+import types
 from typing import Optional
 
 import torch
@@ -54,8 +55,20 @@ def _matmul_delta(a, b, a_sum, b_sum, transpose_b: bool = False):
     return a_sum @ b + a @ b_sum - a @ b
 
 
+def _matmul_delta_sequence(a_seq, b_seq, a_prev, b_prev, transpose_b: bool = False):
+    """``_matmul_delta`` for every step of ``[T, ...]`` sequences in three batched products; ``a_prev`` / ``b_prev`` are
+    the sums before the first step (``None`` = zero).  Returns ``(increments, a_sum_last, b_sum_last)``."""
+    a_sum, b_sum = a_seq.cumsum(0), b_seq.cumsum(0)
+    if a_prev is not None:
+        a_sum, b_sum = a_sum + a_prev, b_sum + b_prev
+    last = (a_sum[-1], b_sum[-1])
+    if transpose_b:
+        b_seq, b_sum = b_seq.transpose(-1, -2), b_sum.transpose(-1, -2)
+    return a_sum @ b_seq + a_seq @ (b_sum - b_seq), *last
+
+
 class _StepwiseModule(base.MemoryModule):
-    """Single-step logic in ``step``; multi-step mode loops over the leading axis."""
+    """Single-step logic in ``step``; multi-step mode calls ``sequence`` (default: a loop over the leading axis)."""
 
     def __init__(self, step_mode: str = "s"):
         super().__init__()
@@ -64,10 +77,13 @@ class _StepwiseModule(base.MemoryModule):
     def step(self, *xs):
         raise NotImplementedError
 
+    def sequence(self, *xs):
+        return torch.stack([self.step(*(x[t] for x in xs)) for t in range(xs[0].shape[0])])
+
     def forward(self, *xs):
         if self.step_mode == "s":
             return self.step(*xs)
-        return torch.stack([self.step(*(x[t] for x in xs)) for t in range(xs[0].shape[0])])
+        return self.sequence(*xs)
 
 
 class _BiasInParts(_StepwiseModule):
@@ -94,6 +110,20 @@ class _BiasInParts(_StepwiseModule):
         self.realize_time = self.realize_time - 1
         return self.spikezip_bias / self.bias_steps
 
+    def _bias_parts(self, x_seq: torch.Tensor) -> Optional[torch.Tensor]:
+        """Per-step multiplier ``[T]`` (1 where a bias part is released) for a whole sequence, computed on the device
+        without a host read; the two memories become 0-d tensors, which the single-step path accepts as well."""
+        T = x_seq.shape[0]
+        nz = (x_seq != 0).flatten(1).any(1)
+        started = nz.int().cummax(0).values.bool() | torch.as_tensor(self.is_work, device=x_seq.device)
+        self.is_work = started[-1]
+        if self.spikezip_bias is None:
+            return None
+        left = torch.as_tensor(self.realize_time, device=x_seq.device)
+        release = started & (started.int().cumsum(0) <= left)
+        self.realize_time = left - release.sum()
+        return release.to(x_seq.dtype).view(T, *([1] * (x_seq.dim() - 1)))
+
 
 class SpikeZIPLinear(_BiasInParts):
     def __init__(self, linear: nn.Linear, level: int, bias_steps: Optional[int] = None, step_mode: str = "s"):
@@ -104,6 +134,11 @@ class SpikeZIPLinear(_BiasInParts):
     def step(self, x):
         b = self._bias_part(x)
         return F.linear(x, self.weight, b)
+
+    def sequence(self, x_seq):
+        m = self._bias_parts(x_seq)
+        y = F.linear(x_seq, self.weight)
+        return y if m is None else y + m.view(m.shape[0], *([1] * (y.dim() - 1))) * (self.spikezip_bias / self.bias_steps)
 
 
 class SpikeZIPConv2d(_BiasInParts):
@@ -116,6 +151,13 @@ class SpikeZIPConv2d(_BiasInParts):
         b = self._bias_part(x)
         y = self.conv(x)
         return y if b is None else y + b.view(1, -1, 1, 1)
+
+    def sequence(self, x_seq):
+        m = self._bias_parts(x_seq)
+        T = x_seq.shape[0]
+        y = self.conv(x_seq.flatten(0, 1))
+        y = y.view(T, -1, *y.shape[1:])
+        return y if m is None else y + m.view(T, 1, 1, 1, 1) * (self.spikezip_bias / self.bias_steps).view(1, 1, -1, 1, 1)
 
 
 class SpikeZIPEmbedding(_StepwiseModule):
@@ -131,6 +173,13 @@ class SpikeZIPEmbedding(_StepwiseModule):
         if self.emitted:
             return torch.zeros_like(y)
         self.emitted = True
+        return y
+
+    def sequence(self, ids_seq):
+        y = torch.zeros((*ids_seq.shape, self.embedding.embedding_dim), device=ids_seq.device, dtype=self.embedding.weight.dtype)
+        if not self.emitted:
+            y[0] = self.embedding(ids_seq[0])
+            self.emitted = True
         return y
 
 
@@ -177,6 +226,7 @@ class SpikeZIPSelfAttention(_StepwiseModule):
         self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
         self.query_if, self.key_if, self.value_if = _neuron(pick("query_quan", "quan_q")), _neuron(pick("key_quan", "quan_k")), _neuron(pick("value_quan", "quan_v"))
         self.softmax = SpikeZIPSoftmax(-1)
+        self.is_softmax = bool(getattr(source, "is_softmax", True))      # False: quantised scores divided by the length
         self.attn_if = _neuron(pick("attn_quan"))
         self.after_attn_if = _neuron(pick("after_attn_quan"))
         proj = pick("proj")
@@ -185,9 +235,13 @@ class SpikeZIPSelfAttention(_StepwiseModule):
         for name in ("q_sum", "k_sum", "v_sum", "p_sum"):
             self.register_memory(name, None)
 
-    def _heads(self, x):                                  # [B, L, C] -> [B, H, L, D]
-        b, l, _ = x.shape
-        return x.view(b, l, self.num_heads, self.head_dim).transpose(1, 2)
+    def _heads(self, x):                                  # [..., L, C] -> [..., H, L, D]
+        return x.view(*x.shape[:-1], self.num_heads, self.head_dim).transpose(-3, -2)
+
+    def _probabilities(self, scores):
+        if self.is_softmax:
+            return self.attn_if(self.softmax(scores))
+        return self.attn_if(scores) / scores.shape[-1]
 
     @staticmethod
     def _acc(total, x):
@@ -201,14 +255,45 @@ class SpikeZIPSelfAttention(_StepwiseModule):
         q, k, v = self._heads(self.query_if(q)), self._heads(self.key_if(k)), self._heads(self.value_if(v))
         self.q_sum, self.k_sum, self.v_sum = self._acc(self.q_sum, q), self._acc(self.k_sum, k), self._acc(self.v_sum, v)
         scores = _matmul_delta(q, k, self.q_sum, self.k_sum, transpose_b=True) * self.scale
-        p = self.attn_if(self.softmax(scores))
+        p = self._probabilities(scores)
         self.p_sum = self._acc(self.p_sum, p)
         ctx = self.after_attn_if(_matmul_delta(p, v, self.p_sum, self.v_sum))
-        b, _, l, _ = ctx.shape
-        out = ctx.transpose(1, 2).reshape(b, l, self.num_heads * self.head_dim)
+        out = ctx.transpose(-3, -2).flatten(-2)
         if self.proj is not None:
             out = self.proj_if(self.proj(out))
         return out
+
+    def _children_in(self, mode: str):
+        previous = {m: m.step_mode for m in self.modules() if m is not self and hasattr(m, "step_mode")}
+        for m in previous:
+            m.step_mode = mode
+        return previous
+
+    def sequence(self, x_seq):
+        """The whole sequence at once: projections with time folded into the batch, the neurons on their sequence
+        kernels, and both products as batched increments of the running sums."""
+        previous = self._children_in("m")
+        try:
+            if self.packed:
+                q, k, v = self.qkv(x_seq).chunk(3, dim=-1)
+            else:
+                q, k, v = self.query(x_seq), self.key(x_seq), self.value(x_seq)
+            q, k, v = self._heads(self.query_if(q)), self._heads(self.key_if(k)), self._heads(self.value_if(v))
+            fresh = not (torch.is_tensor(self.q_sum) and self.q_sum.shape == q.shape[1:])
+            scores, self.q_sum, self.k_sum = _matmul_delta_sequence(q, k, None if fresh else self.q_sum, None if fresh else self.k_sum, True)
+            p = self._probabilities(scores * self.scale)
+            fresh_p = fresh or not (torch.is_tensor(self.p_sum) and self.p_sum.shape == p.shape[1:])
+            if fresh_p:
+                ctx, self.p_sum, self.v_sum = _matmul_delta_sequence(p, v, None, None)
+            else:
+                ctx, self.p_sum, self.v_sum = _matmul_delta_sequence(p, v, self.p_sum, self.v_sum)
+            out = self.after_attn_if(ctx).transpose(-3, -2).flatten(-2)
+            if self.proj is not None:
+                out = self.proj_if(self.proj(out))
+            return out
+        finally:
+            for m, mode in previous.items():
+                m.step_mode = mode
 
 
 def _is_qattention(module: nn.Module) -> bool:
@@ -216,6 +301,68 @@ def _is_qattention(module: nn.Module) -> bool:
     has_quan = any(getattr(module, n, None) is not None for n in ("query_quan", "quan_q"))
     has_heads = any(hasattr(module, n) for n in ("num_attention_heads", "num_heads"))
     return has_proj and has_quan and has_heads
+
+
+class _StepClock(base.MemoryModule):
+    """Counts the single steps since the last reset."""
+
+    def __init__(self):
+        super().__init__()
+        self.register_memory("t", 0)
+
+
+def _is_vit(model: nn.Module) -> bool:
+    return all(hasattr(model, n) for n in ("patch_embed", "cls_token", "pos_embed", "head"))
+
+
+def _vit_tokens(model: nn.Module, x: torch.Tensor) -> torch.Tensor:
+    """Patch tokens ``[..., L, C]`` of images ``[B, C, H, W]`` or ``[T, B, C, H, W]``."""
+    embed = model.patch_embed
+    proj = getattr(embed, "proj", None)
+    y = (proj if proj is not None else embed)(x)
+    if y.dim() == x.dim():                                   # still a feature map: [..., C, H', W'] -> [..., L, C]
+        y = y.flatten(-2).transpose(-1, -2)
+        if proj is not None and hasattr(embed, "norm"):
+            y = embed.norm(y)
+    return y
+
+
+def _vit_forward_features(self: nn.Module, x: torch.Tensor) -> torch.Tensor:
+    """Class token and position embedding are constants of the ANN: like a bias they enter once, at the first step,
+    and later steps carry only what the patch tokens release."""
+    if x.dim() not in (4, 5):
+        raise ValueError("SpikeZIP ViT forward expects [B, C, H, W] or [T, B, C, H, W].")
+    tokens = F.pad(_vit_tokens(self, x), (0, 0, 1, 0))       # a zero token in the class position
+    const = self.pos_embed + F.pad(self.cls_token, (0, 0, 0, self.pos_embed.shape[1] - self.cls_token.shape[1]))
+    if x.dim() == 5:
+        hidden = torch.cat((tokens[:1] + const, tokens[1:]))
+    else:
+        hidden = tokens + const if self._spikezip_clock.t == 0 else tokens
+        self._spikezip_clock.t += 1
+    drop = getattr(self, "pos_drop", None)
+    if drop is not None:
+        hidden = drop(hidden)
+    if hasattr(self, "blocks"):
+        hidden = self.norm(self.blocks(hidden))
+    else:
+        hidden = self.norm(hidden + self.attn(self.attn_norm(hidden)))
+    return hidden.select(-2, 0)
+
+
+def _vit_forward(self: nn.Module, x: torch.Tensor) -> torch.Tensor:
+    return self.head(self.forward_features(x))
+
+
+def _install_vit_forward(model: nn.Module) -> None:
+    if not hasattr(model, "norm"):
+        raise ValueError("SpikeZIP ViT model expects a top-level norm module.")
+    if not (hasattr(model, "blocks") or hasattr(model, "attn")):
+        raise ValueError("SpikeZIP ViT model expects top-level blocks or attn.")
+    if not hasattr(model, "blocks"):
+        model.attn_norm = copy.deepcopy(model.norm)          # the single-attention form normalises twice with equal weights
+    model._spikezip_clock = _StepClock()
+    model.forward_features = types.MethodType(_vit_forward_features, model)
+    model.forward = types.MethodType(_vit_forward, model)
 
 
 class SpikeZIPTFQANNRecipe(ModuleConversionRecipe):
@@ -277,6 +424,8 @@ class SpikeZIPTFQANNRecipe(ModuleConversionRecipe):
     def convert_module(self, converter, ann: nn.Module) -> nn.Module:
         model = copy.deepcopy(ann).eval()
         self._replace(model, self._level_from_model(model))
+        if _is_vit(model):
+            _install_vit_forward(model)
         model.ann2snn_recipe = "spikezip_tf_qann"
         model.time_steps = self.time_steps
         model.model_family = self.model_family

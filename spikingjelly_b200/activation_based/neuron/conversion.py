@@ -291,7 +291,9 @@ class STBIFNeuron(base.MemoryModule):
             res = self._compiled_run(x_seq, q, acc_q, cur)
             if res is not None:
                 out_seq, (q, acc_q, cur), _ = res
-                return (out_seq,), (q, acc_q, cur, bool((x_seq != 0).any() | (out_seq != 0).any()))
+                # the activity flag stays on the device (a 0-d bool tensor): reading it here would stall the stream once
+                # per neuron and call
+                return (out_seq,), (q, acc_q, cur, (x_seq != 0).any() | (out_seq != 0).any())
         outs = []
         for t in range(x_seq.shape[0]):
             o, q, acc_q, cur = functional.stbif_step(x_seq[t], q, acc_q, self.q_threshold, self.pos_max, self.neg_min)

@@ -6,6 +6,7 @@ Role of ``triton_kernel/flexsn/wrapper.py:26-…`` and ``flexsn/custom_ops.py:89
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import threading
 import weakref
@@ -24,6 +25,23 @@ _DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 def _struct(name: str, fields: Sequence[Tuple[str, int]]):
     spec = [(f, ctypes.c_void_p * n) for f, n in fields] + [("n", ctypes.c_longlong), ("T", ctypes.c_int)]
     return type(name, (ctypes.Structure,), {"_fields_": spec})
+
+
+def _on_device(device: torch.device):
+    """A device guard that costs nothing when ``device`` is already current (the usual case: one process per GPU)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return contextlib.nullcontext()
+    return torch.cuda.device(device)
+
+
+def _forward_flat(handle: int, flat_args: Sequence[torch.Tensor], store_state_seqs: bool) -> List[torch.Tensor]:
+    """Eager calls go straight to the kernel; the registered operator (Python dispatch, ~100 us per call) is only
+    needed when a tracer has to see one opaque node."""
+    if torch.compiler.is_compiling():
+        return torch.ops.sjb200_flexsn.forward(handle, list(flat_args), store_state_seqs)
+    k = lookup_kernel_handle(handle)
+    outs, seqs, last = k.forward(flat_args[:k.NI], flat_args[k.NI:], store_state_seqs)
+    return [*outs, *(seqs or []), *last]
 
 
 class FlexSNKernel:
@@ -63,8 +81,8 @@ class FlexSNKernel:
 
     @staticmethod
     def _vec(tensors: Sequence[Optional[torch.Tensor]], n: int, itemsize: int) -> int:
-        v = 16 // itemsize
-        if n % v:
+        """1 when the launch may use four-element accesses (16 bytes in fp32, 8 in 16-bit types), else 0."""
+        if n % 4:
             return 0
         return int(all(t is None or t.data_ptr() % 16 == 0 for t in tensors))
 
@@ -96,7 +114,7 @@ class FlexSNKernel:
         self._fill(a.s_last, last)
         a.n, a.T = n, T
         vec = self._vec([*inputs, *states, *outs, *(seqs or []), *last], n, x0.element_size())
-        with torch.cuda.device(x0.device):
+        with _on_device(x0.device):
             stream = torch.cuda.current_stream(x0.device).cuda_stream
             rc = self.lib.flexsn_forward(ctypes.byref(a), code, vec, ctypes.c_void_p(stream))
         if rc != 0:
@@ -129,7 +147,7 @@ class FlexSNKernel:
         self._fill(a.g_s0, g_s0)
         a.n, a.T = n, T
         vec = self._vec([*inputs, *states, *seqs, *g_outs, *g_seqs, *g_last, *g_in, *g_s0], n, x0.element_size())
-        with torch.cuda.device(x0.device):
+        with _on_device(x0.device):
             stream = torch.cuda.current_stream(x0.device).cuda_stream
             rc = self.lib.flexsn_backward(ctypes.byref(a), code, vec, ctypes.c_void_p(stream))
         if rc != 0:
@@ -221,7 +239,7 @@ def _(handle, args, seqs, grads, needs):
 def flexsn_forward(handle: int, flat_args: Sequence[torch.Tensor], store_state_seqs: bool):
     """No-grad path: ``(outputs, state sequences | None, final states)``."""
     k = lookup_kernel_handle(handle)
-    res = torch.ops.sjb200_flexsn.forward(handle, list(flat_args), store_state_seqs)
+    res = _forward_flat(handle, list(flat_args), store_state_seqs)
     outs = res[:k.NO]
     seqs = res[k.NO:k.NO + k.NS] if store_state_seqs else None
     return outs, seqs, res[len(res) - k.NS:]
@@ -231,8 +249,7 @@ class _Training(torch.autograd.Function):
     @staticmethod
     def forward(ctx, handle, *flat_args):
         k = lookup_kernel_handle(handle)
-        with torch.no_grad():
-            res = torch.ops.sjb200_flexsn.forward(handle, list(flat_args), True)
+        res = _forward_flat(handle, list(flat_args), True)
         seqs = res[k.NO:k.NO + k.NS]
         ctx.kernel = k          # a strong reference: backward works after the module released its handle
         ctx.needs = [bool(n and ctx.needs_input_grad[i + 1]) for i, n in enumerate(k.graphs.needs_grad)]

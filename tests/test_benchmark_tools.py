@@ -43,3 +43,25 @@ def test_snn_llm_smoke_is_reproducible(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     rec = json.loads((tmp_path / "snn_llm_smoke.json").read_text())
     assert rec["reproducible"] and rec["result"]["loss_decreased"] and len(rec["result"]["parameter_sha256"]) == 64
+
+
+def _json_line(args):
+    r = subprocess.run([sys.executable, *args], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    return json.loads(r.stdout.strip().splitlines()[-1])
+
+
+def test_ann2snn_benchmarks_run_on_cpu():
+    small = ["--device", "cpu", "--time-steps", "4", "--batch-size", "2", "--batches-per-epoch", "1", "--epochs", "1", "--warmup-epochs", "0",
+             "--num-classes", "10"]
+    d = _json_line([str(ROOT / "benchmark" / "benchmark_ann2snn_step_mode.py"), "--recipe", "rate", "--channels", "8", "--conv-depth", "2", "--hidden-dim", "16",
+                    "--image-size", "16", *small])
+    assert d["parity_max_abs_diff"] <= 1e-5 and d["multi_step_speedup"] > 0
+    d = _json_line([str(ROOT / "benchmark" / "benchmark_ann2snn_step_mode.py"), "--recipe", "sta", "--embed-dim", "16", "--mlp-dim", "32", "--depth", "1",
+                    "--num-heads", "2", "--seq-len", "4", "--input-dim", "8", *small])
+    assert d["parity_max_abs_diff"] <= 1e-4
+    d = _json_line([str(ROOT / "benchmark" / "benchmark_ann2snn_spikezip_stbif.py"), "--device", "cpu", "--numel", "512", "--repeat", "1", "--sym"])
+    assert d["torch_max_abs_diff"] == 0 and d["torch_state_max_abs_diff"] == 0 and d["sum_equals_quantiser"]
+    d = _json_line([str(ROOT / "benchmark" / "benchmark_ann2snn_spikezip_vit_qann.py"), "--device", "cpu", "--dim", "16", "--depth", "1", "--heads", "2",
+                    "--image-size", "32", "--time-steps", "48", "--batches", "1"])
+    assert d["top1_agreement"] >= 0.5 and d["logit_max_abs_diff"] < 1.0

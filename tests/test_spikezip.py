@@ -113,3 +113,95 @@ def test_embedding_and_validation():
         ModuleConverter(SpikeZIPTFQANNRecipe(time_steps=0)).convert(nn.Linear(2, 2))
     with pytest.raises(ValueError):
         ModuleConverter(SpikeZIPTFQANNRecipe(model_family="bert")).convert(nn.Linear(2, 2))
+
+
+def _sequence_run(snn, x, T):
+    functional.reset_net(snn)
+    functional.set_step_mode(snn, "m")
+    seq = torch.zeros(T, *x.shape)
+    seq[0] = x
+    with torch.no_grad():
+        out = snn(seq)
+    functional.set_step_mode(snn, "s")
+    return out
+
+
+def test_multi_step_mode_equals_the_single_step_loop():
+    torch.manual_seed(2)
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.inq = Quan(0.125, 32, True)
+            self.norm = nn.LayerNorm(16)
+            self.nq = Quan(0.125, 32, True)
+            self.attn = QAttention(16, 2, 32)
+            self.fc, self.fq = nn.Linear(16, 8), Quan(0.1, 32, True)
+
+        def forward(self, x):
+            return self.fq(self.fc(self.attn(self.nq(self.norm(self.inq(x))))))
+
+    snn = ModuleConverter(SpikeZIPTFQANNRecipe(time_steps=48, model_family="vit")).convert(Block().eval())
+    x = torch.randn(2, 6, 16)
+    functional.reset_net(snn)
+    with torch.no_grad():
+        loop = torch.stack([snn(x if t == 0 else torch.zeros_like(x)) for t in range(48)])
+    seq = _sequence_run(snn, x, 48)
+    torch.testing.assert_close(seq, loop, rtol=0, atol=1e-5)
+    # a sequence split into two calls continues from the stored sums
+    functional.reset_net(snn)
+    functional.set_step_mode(snn, "m")
+    full = torch.zeros(48, *x.shape)
+    full[0] = x
+    with torch.no_grad():
+        halves = torch.cat([snn(full[:20]), snn(full[20:])])
+    torch.testing.assert_close(halves, loop, rtol=0, atol=1e-5)
+
+
+class _PatchEmbed(nn.Module):
+    def __init__(self, dim, level):
+        super().__init__()
+        self.proj = nn.Sequential(nn.Conv2d(3, dim, 4, stride=4), Quan(0.125, level, True))
+
+    def forward(self, x):
+        return self.proj(x)
+
+
+class _QBlock(nn.Module):
+    def __init__(self, dim, level):
+        super().__init__()
+        self.norm1 = nn.Sequential(nn.LayerNorm(dim), Quan(0.125, level, True))
+        self.attn = QAttention(dim, 2, level)
+
+    def forward(self, x):
+        return x + self.attn(self.norm1(x))
+
+
+class TinyQViT(nn.Module):
+    def __init__(self, dim=16, level=32):
+        super().__init__()
+        self.patch_embed = _PatchEmbed(dim, level)
+        self.cls_token = nn.Parameter(torch.randn(1, 1, dim) * 0.1)
+        self.pos_embed = nn.Parameter(torch.randn(1, 5, dim) * 0.1)
+        self.blocks = nn.Sequential(_QBlock(dim, level))
+        self.norm = nn.Sequential(nn.LayerNorm(dim), Quan(0.125, level, True))
+        self.head = nn.Linear(dim, 7)
+
+    def forward(self, x):
+        x = self.patch_embed(x).flatten(2).transpose(1, 2)
+        x = torch.cat((self.cls_token.expand(x.shape[0], -1, -1), x), dim=1) + self.pos_embed
+        return self.head(self.norm(self.blocks(x))[:, 0])
+
+
+def test_vit_class_token_and_position_embedding_enter_once():
+    torch.manual_seed(3)
+    qann = TinyQViT().eval()
+    snn = ModuleConverter(SpikeZIPTFQANNRecipe(time_steps=64, model_family="vit")).convert(qann)
+    x = torch.randn(2, 3, 8, 8)
+    with torch.no_grad():
+        want = qann(x)
+    got = _run(snn, x, 64)
+    assert ((got - want).abs() > 1e-4).float().mean().item() <= 0.05 and (got - want).abs().max().item() <= 0.2
+    assert (_run(snn, x, 64) - got).abs().max().item() == 0          # reset_net restarts the step clock
+    seq = _sequence_run(snn, x, 64).sum(0)
+    torch.testing.assert_close(seq, got, rtol=0, atol=1e-5)
