@@ -17,8 +17,9 @@ from ... import surrogate as _surrogate
 from ..triton_utils import (is_fp8_dtype, normalize_cuda_device, normalize_triton_compute_dtype_name, normalize_triton_storage_dtype,
                             torch_dtype_to_triton_neuron_dtype_id, triton_compute_dtype_name_to_neuron_dtype_id)
 
-__all__ = ["multistep_if", "multistep_lif", "multistep_plif", "multistep_if_mp", "multistep_lif_mp", "TritonNeuronExecutionPlan",
-           "prepare_triton_neuron_execution_plan"]
+__all__ = ["multistep_if", "multistep_lif", "multistep_plif", "multistep_if_mp", "multistep_lif_mp", "multistep_plif_mp",
+           "multistep_if_mp_with_plan", "multistep_lif_mp_with_plan", "multistep_plif_mp_with_plan", "multistep_if_inference",
+           "multistep_lif_inference", "multistep_plif_inference", "TritonNeuronExecutionPlan", "prepare_triton_neuron_execution_plan"]
 
 
 def _spec(kind: str, tau: float, v_threshold: float, v_reset: Optional[float], detach_reset: bool, surrogate_function):
@@ -95,31 +96,93 @@ def prepare_triton_neuron_execution_plan(*, neuron_type: str, device, storage_dt
                                      bool(save_intermediates))
 
 
-def _mp(kind: str, x_seq, v_init, tau, v_threshold, v_reset, storage_dtype, compute_dtype, backward_compute_dtype, spike_dtype, save_intermediates,
-        detach_reset, surrogate_function):
-    plan = prepare_triton_neuron_execution_plan(neuron_type="if" if kind == "if" else "lif", device=x_seq.device, storage_dtype=storage_dtype,
-                                                forward_compute_dtype=compute_dtype, backward_compute_dtype=backward_compute_dtype,
-                                                spike_dtype=spike_dtype, save_intermediates=save_intermediates)
+def _check_plan(x_seq, v_init, plan: "TritonNeuronExecutionPlan", neuron_type: str) -> None:
+    if plan.neuron_type != neuron_type:
+        raise ValueError(f"{neuron_type.upper()} forward requires a {neuron_type.upper()} plan, got {plan.neuron_type!r}.")
+    if not x_seq.is_cuda or x_seq.device != plan.device:
+        raise ValueError(f"the plan was prepared for {plan.device}, the input is on {x_seq.device}.")
+    if torch.is_tensor(v_init) and v_init.device != x_seq.device:
+        raise ValueError("x_seq and v_init must be on the same device.")
+
+
+def _run_plan(kind: str, x_seq, v_init, plan, tau, v_threshold, v_reset, detach_reset, surrogate_function, r=None):
     sg = surrogate_function if surrogate_function is not None else _surrogate.Sigmoid()
     spec = _spec(kind, tau, v_threshold, v_reset, detach_reset, sg)
     state = torch.bfloat16 if is_fp8_dtype(plan.storage_dtype) else plan.storage_dtype
     v0 = v_init.to(state) if torch.is_tensor(v_init) else v_init
     if is_fp8_dtype(plan.storage_dtype):
-        s, v_seq = _run(x_seq, v0, spec, storage_dtype=plan.storage_dtype)        # the cast happens inside the autograd function
+        s, v_seq = _run(x_seq, v0, spec, r=r, storage_dtype=plan.storage_dtype)   # the cast happens inside the autograd function
     else:
-        s, v_seq = _run(x_seq.to(plan.storage_dtype), v0, spec)
-    return s.to(spike_dtype), v_seq, None
+        s, v_seq = _run(x_seq.to(plan.storage_dtype), v0, spec, r=r)
+    return s.to(plan.spike_dtype), v_seq, None
+
+
+def multistep_if_mp_with_plan(x_seq, v_init, plan: TritonNeuronExecutionPlan, *, v_threshold: float, v_reset: Optional[float],
+                              detach_reset: bool = False, surrogate_function=None):
+    """The ``*_with_plan`` forms skip the validation and dtype look-ups of ``prepare_triton_neuron_execution_plan``: a module
+    prepares the plan once and passes it with every call."""
+    _check_plan(x_seq, v_init, plan, "if")
+    return _run_plan("if", x_seq, v_init, plan, 2.0, v_threshold, v_reset, detach_reset, surrogate_function)
+
+
+def multistep_lif_mp_with_plan(x_seq, v_init, plan: TritonNeuronExecutionPlan, *, decay_input: bool, tau: float, v_threshold: float,
+                               v_reset: Optional[float], detach_reset: bool = False, surrogate_function=None):
+    _check_plan(x_seq, v_init, plan, "lif")
+    return _run_plan("lif_di" if decay_input else "lif_ndi", x_seq, v_init, plan, tau, v_threshold, v_reset, detach_reset, surrogate_function)
+
+
+def multistep_plif_mp_with_plan(x_seq, v_init, r_tau: torch.Tensor, plan: TritonNeuronExecutionPlan, *, decay_input: bool, v_threshold: float,
+                                v_reset: Optional[float], detach_reset: bool = False, surrogate_function=None):
+    _check_plan(x_seq, v_init, plan, "plif")
+    return _run_plan("plif_di" if decay_input else "plif_ndi", x_seq, v_init, plan, 2.0, v_threshold, v_reset, detach_reset, surrogate_function,
+                     r=r_tau)
+
+
+def _plan_for(neuron_type, x_seq, storage_dtype, compute_dtype, backward_compute_dtype, spike_dtype, save_intermediates):
+    return prepare_triton_neuron_execution_plan(neuron_type=neuron_type, device=x_seq.device, storage_dtype=storage_dtype,
+                                                forward_compute_dtype=compute_dtype, backward_compute_dtype=backward_compute_dtype,
+                                                spike_dtype=spike_dtype, save_intermediates=save_intermediates)
 
 
 def multistep_if_mp(x_seq, v_init, *, v_threshold: float, v_reset: Optional[float], storage_dtype, compute_dtype="fp32",
                     backward_compute_dtype="fp32", spike_dtype: torch.dtype = torch.float32, save_intermediates: bool = True,
                     detach_reset: bool = False, surrogate_function=None) -> Tuple[torch.Tensor, torch.Tensor, None]:
-    return _mp("if", x_seq, v_init, 2.0, v_threshold, v_reset, storage_dtype, compute_dtype, backward_compute_dtype, spike_dtype,
-               save_intermediates, detach_reset, surrogate_function)
+    plan = _plan_for("if", x_seq, storage_dtype, compute_dtype, backward_compute_dtype, spike_dtype, save_intermediates)
+    return multistep_if_mp_with_plan(x_seq, v_init, plan, v_threshold=v_threshold, v_reset=v_reset, detach_reset=detach_reset,
+                                     surrogate_function=surrogate_function)
 
 
 def multistep_lif_mp(x_seq, v_init, *, decay_input: bool, tau: float, v_threshold: float, v_reset: Optional[float], storage_dtype,
                      compute_dtype="fp32", backward_compute_dtype="fp32", spike_dtype: torch.dtype = torch.float32,
                      save_intermediates: bool = True, detach_reset: bool = False, surrogate_function=None):
-    return _mp("lif_di" if decay_input else "lif_ndi", x_seq, v_init, tau, v_threshold, v_reset, storage_dtype, compute_dtype,
-               backward_compute_dtype, spike_dtype, save_intermediates, detach_reset, surrogate_function)
+    plan = _plan_for("lif", x_seq, storage_dtype, compute_dtype, backward_compute_dtype, spike_dtype, save_intermediates)
+    return multistep_lif_mp_with_plan(x_seq, v_init, plan, decay_input=decay_input, tau=tau, v_threshold=v_threshold, v_reset=v_reset,
+                                      detach_reset=detach_reset, surrogate_function=surrogate_function)
+
+
+def multistep_plif_mp(x_seq, v_init, r_tau: torch.Tensor, *, decay_input: bool, v_threshold: float, v_reset: Optional[float], storage_dtype,
+                      compute_dtype="fp32", backward_compute_dtype="fp32", spike_dtype: torch.dtype = torch.float32,
+                      save_intermediates: bool = True, detach_reset: bool = False, surrogate_function=None):
+    plan = _plan_for("plif", x_seq, storage_dtype, compute_dtype, backward_compute_dtype, spike_dtype, save_intermediates)
+    return multistep_plif_mp_with_plan(x_seq, v_init, r_tau, plan, decay_input=decay_input, v_threshold=v_threshold, v_reset=v_reset,
+                                       detach_reset=detach_reset, surrogate_function=surrogate_function)
+
+
+# ------------------------------------------------------------------ gradient-free entry points (positional, as the reference's)
+def _inference(kind, x_seq, v_init, tau, v_threshold, v_reset, soft_reset, store_v_seq=True, r=None):
+    with torch.no_grad():
+        return _run(x_seq, v_init, _spec(kind, tau, v_threshold, None if soft_reset else v_reset, False, _surrogate.Sigmoid()), r=r,
+                    store_v_seq=store_v_seq)
+
+
+def multistep_if_inference(x_seq, v_init, v_threshold: float, v_reset: float, soft_reset: bool, store_v_seq: bool = True):
+    return _inference("if", x_seq, v_init, 2.0, v_threshold, v_reset, soft_reset, store_v_seq)
+
+
+def multistep_lif_inference(x_seq, v_init, decay_input: bool, tau: float, v_threshold: float, v_reset: float, soft_reset: bool,
+                            store_v_seq: bool = True):
+    return _inference("lif_di" if decay_input else "lif_ndi", x_seq, v_init, tau, v_threshold, v_reset, soft_reset, store_v_seq)
+
+
+def multistep_plif_inference(x_seq, v_init, r_tau: torch.Tensor, decay_input: bool, v_threshold: float, v_reset: float, soft_reset: bool):
+    return _inference("plif_di" if decay_input else "plif_ndi", x_seq, v_init, 2.0, v_threshold, v_reset, soft_reset, True, r=r_tau)

@@ -65,3 +65,45 @@ def test_ann2snn_benchmarks_run_on_cpu():
     d = _json_line([str(ROOT / "benchmark" / "benchmark_ann2snn_spikezip_vit_qann.py"), "--device", "cpu", "--dim", "16", "--depth", "1", "--heads", "2",
                     "--image-size", "32", "--time-steps", "48", "--batches", "1"])
     assert d["top1_agreement"] >= 0.5 and d["logit_max_abs_diff"] < 1.0
+
+
+def test_fp8_efficiency_gates():
+    import pytest
+    import fp8_efficiency as E
+    base = {"precision": "bf16", "training_samples_per_sec": 100.0, "inference_samples_per_sec": 200.0, "training_peak_allocated_mb": 10.0,
+            "inference_peak_allocated_mb": 4.0}
+    fast = {**base, "precision": "fp8", "training_samples_per_sec": 120.0, "inference_samples_per_sec": 260.0, "training_peak_allocated_mb": 9.0}
+    slow = {**base, "precision": "fp8-b", "training_samples_per_sec": 101.0}
+    rep = E.assess_model_efficiency([base, fast, slow], baseline_precision="bf16", min_training_speedup=1.05, min_inference_speedup=1.05)
+    assert not rep["passed"] and rep["comparisons"][0]["passed"] and rep["comparisons"][0]["training_memory_ratio"] == 0.9
+    assert len(rep["failures"]) == 2 and "fp8-b training speedup 1.0100x" in rep["failures"][0]
+    with pytest.raises(RuntimeError, match="fp8-b"):
+        E.require_efficiency(rep)
+    E.require_efficiency(E.assess_model_efficiency([base, fast], baseline_precision="bf16", min_training_speedup=1.05, min_inference_speedup=1.05))
+    for bad in ([fast], [base], [base, base, fast], [base, {**fast, "training_samples_per_sec": float("nan")}]):
+        with pytest.raises(ValueError):
+            E.assess_model_efficiency(bad, baseline_precision="bf16", min_training_speedup=1.05, min_inference_speedup=1.05)
+    with pytest.raises(ValueError):
+        E.assess_model_efficiency([base, fast], baseline_precision="fp8", min_training_speedup=1.0, min_inference_speedup=1.0)
+    g = {"T": 4, "N": 1024, "neuron_type": "lif", "process": "training"}
+    rows = [{**g, "variant": "stable_fp32", "success": True, "median_ms": 2.0, "peak_allocated_mb": 8.0},
+            {**g, "variant": "mp_plan_float8_e4m3fn", "success": True, "median_ms": 1.0, "peak_allocated_mb": 2.0, "compute_dtype": "fp32"},
+            {**g, "variant": "mp_plan_float8_e5m2", "success": True, "median_ms": 1.6, "peak_allocated_mb": 2.0},
+            {**g, "T": 8, "variant": "mp_plan_float8_e5m2", "success": True, "median_ms": 1.6, "peak_allocated_mb": 2.0},
+            {**g, "N": 64, "variant": "stable_fp32", "success": False, "failure_reason": "boom"}]
+    rep = E.assess_triton_efficiency(rows, min_speedup=1.05)
+    assert rep["comparisons"] == [{**g, "baseline_variant": "stable_fp32", "best_fp8_variant": "mp_plan_float8_e4m3fn", "best_compute_dtype": "fp32",
+                                   "speedup": 2.0, "memory_ratio": 0.25, "passed": True}]
+    assert len(rep["failures"]) == 2 and "boom" in rep["failures"][0] and "T=8" in rep["failures"][1]
+    assert E.percentile([1.0, 3.0], 0.5) == 2.0
+
+
+def test_precision_sweep_collects_rows_and_ratios():
+    import benchmark_train_precision_snn_fc_sweep as S
+    rows = S.collect(["noise", json.dumps({"precision": "fp32", "train_ms": 4.0}), json.dumps({"precision": "bf16", "train_ms": 2.0}),
+                      json.dumps({"precision": "fp8", "train_ms": 1.6}), "{broken", json.dumps({"other": 1})])
+    assert set(rows) == {"fp32", "bf16", "fp8"}
+    assert S.ratios(rows) == {"bf16_over_fp32_speedup": 2.0, "fp8_over_bf16_speedup": 1.25}
+    import pytest
+    with pytest.raises(ValueError):
+        S.main(["--hidden-dims", "100"])

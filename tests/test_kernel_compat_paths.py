@@ -164,6 +164,23 @@ def test_functional_neuron_kernels_match_the_modules():
     ref, _ = K.multistep_lif(xw, torch.zeros(4, 64, device="cuda", dtype=torch.bfloat16), True, 2.0, 1.0, 0.0, False, sg)
     ref.backward(g8)
     assert torch.equal(s8, ref) and torch.equal(xb.grad, xw.grad)
+    # a prepared plan gives the same result as the keyword form; PLIF takes the reciprocal time constant as a tensor
+    from spikingjelly_b200.activation_based.triton_kernel.neuron_kernel import integrate_and_fire as KI, plif as KP, utils as KU
+    plan = KU.prepare_triton_neuron_execution_plan(neuron_type="lif", device=xb.device, storage_dtype="fp8_e4m3fn", spike_dtype=torch.bfloat16)
+    s9, _, _ = K.multistep_lif_mp_with_plan(xb.detach(), torch.zeros(4, 64, device="cuda"), plan, decay_input=True, tau=2.0, v_threshold=1.0,
+                                            v_reset=0.0, surrogate_function=sg)
+    assert torch.equal(s9, s8)
+    with pytest.raises(ValueError):
+        KI.multistep_if_mp_with_plan(xb.detach(), torch.zeros(4, 64, device="cuda"), plan, v_threshold=1.0, v_reset=0.0)
+    r_tau = torch.tensor(0.5, device="cuda", requires_grad=True)
+    xp = x.detach().clone().requires_grad_(True)
+    sp, vp, _ = KP.multistep_plif_mp(xp, torch.zeros(4, 64, device="cuda"), r_tau, decay_input=True, v_threshold=1.0, v_reset=0.0,
+                                     storage_dtype="fp32", surrogate_function=sg)
+    assert torch.equal(sp, s2.detach())                       # 1 / tau = 0.5 is the LIF above
+    sp.backward(g)
+    assert r_tau.grad is not None and torch.allclose(xp.grad, x2.grad)
+    si, vi = K.multistep_lif_inference(x.detach(), torch.zeros(4, 64, device="cuda"), True, 2.0, 1.0, 0.0, False, True)
+    assert torch.equal(si, s2.detach()) and torch.equal(vi, node.v_seq) and not si.requires_grad
 
 
 def test_object_handles_switch_and_raw_arguments(monkeypatch):
