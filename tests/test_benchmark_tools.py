@@ -107,3 +107,24 @@ def test_precision_sweep_collects_rows_and_ratios():
     import pytest
     with pytest.raises(ValueError):
         S.main(["--hidden-dims", "100"])
+
+
+def test_snn_llm_conversion_runners_on_cpu():
+    import pytest
+    pytest.importorskip("transformers")
+    d = _json_line([str(ROOT / "benchmark" / "snn_llm_qwen_conversion.py"), "--device", "cpu", "--time-steps", "8", "--calibration-levels", "8", "--seq-len", "16", "--repeats", "1"])
+    assert d["acceptance"]["passed"] and d["metrics"]["exact_logits_relative_l2"] < 1e-4 and d["structure"]["decoder_layers"] == 2
+    d = _json_line([str(ROOT / "benchmark" / "snn_llm_gpt2_conversion.py"), "--device", "cpu", "--hidden", "32", "--heads", "2", "--vocab", "200",
+                    "--max-length", "24", "--prefill-length", "8", "--max-samples", "2"])
+    assert d["acceptance"]["passed"] and d["cache"]["equivalent"] and d["mlp"]["if_vs_qcfs_max_abs_error"] <= 1e-5
+
+
+def test_distributed_precision_smoke_two_gloo_ranks():
+    import os
+    env = {**os.environ, "OMP_NUM_THREADS": "2"}
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", "29573",
+                        str(ROOT / "benchmark" / "snn_llm_distributed_precision_smoke.py"), "--device", "cpu", "--precisions", "fp32", "bf16",
+                        "--steps", "12", "--dim", "32", "--seq-len", "16"], capture_output=True, text=True, timeout=900, env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    rows = [json.loads(line) for line in r.stdout.splitlines() if line.startswith("{")]
+    assert [x["precision"] for x in rows] == ["fp32", "bf16"] and all(x["passed"] and x["ranks_identical"] for x in rows)
