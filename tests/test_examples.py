@@ -125,3 +125,59 @@ def test_vector_environments():
             obs, rew, done, info = envs.step([1, 0, 1])
         assert obs.shape == (3, 4) and rew.shape == (3,) and done.dtype == bool and len(info) == 3
         envs.close()
+
+
+def test_memopt_example_loss_augmentation_and_callbacks():
+    import numpy as np
+    import torch.nn as nn
+    from spikingjelly_b200.activation_based.examples.memopt import callbacks as C
+    from spikingjelly_b200.activation_based.examples.memopt.data_module import CIFAR10DVSDataModule, CIFAR10DVSNDA, Cutout
+    from spikingjelly_b200.activation_based.examples.memopt.loss import TETLoss, TMeanCrossEntropyLoss
+    torch.manual_seed(0)
+    y, label = torch.randn(5, 6, 10), torch.randint(0, 10, (6,))
+    ce = nn.CrossEntropyLoss()
+    want = 0.9 * sum(ce(y[t], label) for t in range(5)) / 5 + 0.1 * ((y - 1.5) ** 2).mean()
+    assert torch.allclose(TETLoss(ce, mean=1.5, tet_lambda=0.1)(y, label), want, atol=1e-6)
+    per_sample = TETLoss(nn.CrossEntropyLoss(reduction="sum"), tet_lambda=0.0)(y, label)        # non-mean criteria take the loop
+    assert torch.allclose(per_sample, sum(nn.functional.cross_entropy(y[t], label, reduction="sum") for t in range(5)) / 5)
+    assert torch.allclose(TMeanCrossEntropyLoss()(y, label), ce(y.mean(0), label))
+    np.random.seed(0)
+    img = torch.ones(3, 2, 16, 16)
+    cut = Cutout(1, length=8)(img)
+    assert 0 < (cut == 0).sum() <= 3 * 2 * 64 and cut.shape == img.shape
+    assert CIFAR10DVSNDA(M=2, N=2)(torch.rand(4, 2, 32, 32)).shape == (4, 2, 32, 32)
+    dm = CIFAR10DVSDataModule(None, T=3, batch_size=4, synthetic_samples=10, resolution=16)
+    dm.prepare_data(), dm.setup()
+    xb, yb = next(iter(dm.train_dataloader()))
+    assert xb.shape == (4, 3, 2, 16, 16) and yb.shape == (4,) and len(dm.val_dataloader().dataset) == 2
+
+    class T:
+        is_global_zero, max_epochs, current_epoch, device = False, 1, 0, torch.device("cpu")
+    t = C.GlobalMeanBatchTimeCallback(reset_per_epoch=False)
+    for _ in range(3):
+        t.on_train_batch_start(T, None, None, 0)
+        t.on_train_batch_end(T, None, None, None, 0)
+    t.on_train_epoch_end(T, None)
+    assert t.totals["train"][1] == 3 and t.last["train"] >= 0
+    t2 = C.GlobalMeanBatchTimeCallback()
+    t2.load_state_dict(t.state_dict())
+    assert t2.totals == t.totals
+    s = C.SamplePerSecondCallback()
+    s.on_train_epoch_start(T, None)
+    s.on_train_batch_end(T, None, None, (torch.zeros(7, 2), torch.zeros(7)), 0)
+    s.on_train_epoch_end(T, None)
+    assert s.last["train"] > 0 and s.totals["train"] == [0.0, 0.0]
+
+
+def test_memopt_example_trainer_runs_from_the_config(tmp_path):
+    from spikingjelly_b200.activation_based.examples.memopt import train as M
+    cfg = M.override({"a": {"b": 1}}, ["a.b=2.5", "a.c.d=true", "e=null"])
+    assert cfg == {"a": {"b": 2.5, "c": {"d": True}}, "e": None}
+    obj = M.instantiate({"class_path": "torch.nn.Linear", "init_args": {"in_features": 3, "out_features": 2}})
+    assert isinstance(obj, torch.nn.Linear) and M.instantiate(5) == 5
+    hist = M.main(["--device", "cpu", "--max-steps", "1", "--set", "data.synthetic=true", "data.T=2", "model.T=2", "data.batch_size=2",
+                   "data.synthetic_samples=8", "trainer.max_epochs=1", "model.level=0", f"trainer.default_root_dir={tmp_path}"])
+    assert len(hist) == 1 and (tmp_path / "metrics.csv").exists() and (tmp_path / "best.pt").exists()
+    import pytest
+    with pytest.raises(ValueError, match="differ"):
+        M.main(["--device", "cpu", "--set", "data.T=3"])
