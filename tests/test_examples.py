@@ -181,3 +181,20 @@ def test_memopt_example_trainer_runs_from_the_config(tmp_path):
     import pytest
     with pytest.raises(ValueError, match="differ"):
         M.main(["--device", "cpu", "--set", "data.T=3"])
+
+
+def test_lava_and_lynxi_examples_run_up_to_the_vendor_step(tmp_path):
+    from spikingjelly_b200.activation_based.examples import lava_mnist, lynxi_fmnist_inference
+    stats = lava_mnist.main(["--synthetic", "--max-steps", "2", "-T", "4", "--channels", "4", "--device", "cpu", "--out-dir", str(tmp_path)])
+    assert "train_loss" in stats and (tmp_path / "net.pt").exists()
+    try:
+        import lava.lib.dl.slayer  # noqa: F401
+    except ImportError:
+        assert stats["exported"] is False
+    torch.manual_seed(0)
+    res = lynxi_fmnist_inference.main(["--synthetic", "--channels", "8", "-T", "3", "-b", "4"])
+    assert res["host_max_abs_diff"] < 1e-5
+    try:
+        import lynpy  # noqa: F401
+    except ImportError:
+        assert res["device"] is None
