@@ -77,6 +77,7 @@ def main():
     ap.add_argument("--warmup-epochs", type=int, default=1)
     ap.add_argument("--calibration-batches", type=int, default=4)
     ap.add_argument("--seed", type=int, default=20260703)
+    ap.add_argument("--neuron-backend", default=None, help="set_backend(model, ...) on the converted network; 'fast' = this arm's kernel backend")
     ap.add_argument("--atol", type=float, default=None)
     ap.add_argument("--rtol", type=float, default=None)
     # rate-coding model
@@ -117,6 +118,8 @@ def main():
         recipe = ann2snn.STATransformerRecipe(dataloader=calib if a.sta_mode == "spiking_encoder" else None,
                                               time_steps=a.time_steps, mode=a.sta_mode)
     base = ann2snn.Converter(recipe=recipe, device=dev).convert(ann)
+    if a.neuron_backend:
+        functional.set_backend(base, arm.fast_backend if a.neuron_backend == "fast" else a.neuron_backend)
     T = a.time_steps
 
     def sequence(x):                 # rate coding repeats the frame; STA feeds it once and zeros afterwards
@@ -167,7 +170,7 @@ def main():
             dt = time.perf_counter() - t0
             rows[name] = {"seconds_per_epoch": round(dt / a.epochs, 5), "samples_per_second": round(a.epochs * nb * bs / dt, 1)}
     print(json.dumps({"impl": a.impl, "recipe": a.recipe, "device": str(dev), "time_steps": T, "batch_size": bs,
-                      "batches_per_epoch": nb, "parity_max_abs_diff": worst, "results": rows,
+                      "batches_per_epoch": nb, "neuron_backend": a.neuron_backend or "as converted", "parity_max_abs_diff": worst, "results": rows,
                       "multi_step_speedup": round(rows["single_step_loop"]["seconds_per_epoch"] / rows["multi_step"]["seconds_per_epoch"], 3)}))
 
 

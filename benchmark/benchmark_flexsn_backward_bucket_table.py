@@ -51,6 +51,7 @@ def main():
     for name in a.workloads:
         build, classes, shape = table[name]
         net = build(spiking_neuron=flexsn, num_classes=classes, step_mode="m").cuda().eval()
+        functional.set_step_mode(net, "m")
         seen = []
         hooks = [m.register_forward_pre_hook(lambda mod, inp, seen=seen: seen.append((inp[0].shape[0], inp[0][0].numel())))
                  for m in net.modules() if isinstance(m, neuron.FlexSN)]

@@ -267,6 +267,9 @@ class STBIFNeuron(base.MemoryModule):
 
     def _scalars(self):
         """Python copies of the three scalar buffers, refreshed when a buffer is written (no sync per call)."""
+        buffers = (self.q_threshold, self.pos_max, self.neg_min)
+        if any(b.is_inference() for b in buffers):          # no version counter to watch: read the values every time
+            return tuple(float(b) for b in buffers)
         stamp = (self.q_threshold._version, self.pos_max._version, self.neg_min._version, self.q_threshold.data_ptr())
         if getattr(self, "_scalar_stamp", None) != stamp:
             self._scalar_values = (float(self.q_threshold), float(self.pos_max), float(self.neg_min))
@@ -274,15 +277,23 @@ class STBIFNeuron(base.MemoryModule):
         return self._scalar_values
 
     def _compiled_run(self, x_seq, q, acc_q, cur):
+        """The kernel carries a fourth state in registers: 1 once this element has seen a non-zero input or emitted a
+        spike.  The activity flag of the call is then a reduction over one step's worth of values instead of two passes
+        over the input and output sequences."""
         from ._compiled import CompiledSequence, compiled_for
         ref = weakref.ref(self)
 
-        def step(x, q, acc, c):
-            return functional.stbif_step(x, q, acc, *ref()._scalars())
+        def step(x, q, acc, c, seen):
+            out, q, acc, c = functional.stbif_step(x, q, acc, *ref()._scalars())
+            return out, q, acc, c, torch.where((x != 0) | (out != 0), torch.ones_like(seen), seen)
 
-        seq = compiled_for(self, lambda: CompiledSequence(step, 3, lambda: ("stbif", *ref()._scalars()), "stbif"))
+        seq = compiled_for(self, lambda: CompiledSequence(step, 4, lambda: ("stbif", *ref()._scalars()), "stbif"))
         with torch.no_grad():
-            return seq.run(x_seq, (q, acc_q, cur))
+            res = seq.run(x_seq, (q, acc_q, cur, torch.zeros_like(q)))
+        if res is None:
+            return None
+        out_seq, (q, acc_q, cur, seen), _ = res
+        return out_seq, (q, acc_q, cur), seen.any()
 
     def multi_step_functional_forward(self, inputs, states, **kwargs):
         x_seq = inputs[0]
@@ -290,10 +301,10 @@ class STBIFNeuron(base.MemoryModule):
         if x_seq.is_cuda and not (torch.is_grad_enabled() and x_seq.requires_grad):
             res = self._compiled_run(x_seq, q, acc_q, cur)
             if res is not None:
-                out_seq, (q, acc_q, cur), _ = res
+                out_seq, (q, acc_q, cur), active = res
                 # the activity flag stays on the device (a 0-d bool tensor): reading it here would stall the stream once
                 # per neuron and call
-                return (out_seq,), (q, acc_q, cur, (x_seq != 0).any() | (out_seq != 0).any())
+                return (out_seq,), (q, acc_q, cur, active)
         outs = []
         for t in range(x_seq.shape[0]):
             o, q, acc_q, cur = functional.stbif_step(x_seq[t], q, acc_q, self.q_threshold, self.pos_max, self.neg_min)

@@ -33,6 +33,8 @@ def _spec(kind: str, tau: float, v_threshold: float, v_reset: Optional[float], d
 
 def _run(x_seq, v_init, spec, r=None, store_v_seq=True, storage_dtype=None):
     from ....ops.neuron_scan import multistep_neuron
+    if r is not None and r.dtype != torch.float32:
+        r = r.float()                                    # the kernels read the reciprocal time constant as one fp32 value
     s, v_last, v_seq, _ = multistep_neuron(x_seq, v_init, spec, r=r, store_v_seq=store_v_seq, storage_dtype=storage_dtype)
     return s, (v_seq if store_v_seq else v_last.unsqueeze(0))
 

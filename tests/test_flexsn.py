@@ -211,3 +211,6 @@ def test_library_neurons_without_handwritten_kernels_run_compiled():
         want = ref(xs.cpu())
     assert torch.allclose(out.cpu(), want) and torch.allclose(st.acc_q.cpu(), ref.acc_q)
     assert counters.by_name().get("flexsn_forward", 0) >= before + 3
+    with torch.inference_mode():                     # buffers created here have no version counter
+        st2 = neuron.STBIFNeuron(0.25, level=8, step_mode="m").cuda()
+        assert torch.allclose(st2(xs).cpu(), want)
