@@ -133,10 +133,16 @@ class _Prefetcher:
 class _Deferred:
     """Non-blocking read-back of a device scalar; ``get()`` waits for the copy."""
 
+    _ring, _next = [], 0          # four pinned scalars, reused in turn: at most two reads are in flight at a time
+
     def __init__(self, torch, value):
         v = value.detach().reshape(1)
-        self.host = torch.empty(1, dtype=v.dtype, pin_memory=True)
-        self.host.copy_(v, non_blocking=True)
+        cls = type(self)
+        if len(cls._ring) < 4:
+            cls._ring.append(torch.empty(1, dtype=torch.float32, pin_memory=True))
+        self.host = cls._ring[cls._next % len(cls._ring)]
+        cls._next += 1
+        self.host.copy_(v.float(), non_blocking=True)
         self.event = torch.cuda.Event()
         self.event.record(torch.cuda.current_stream(v.device))
 
@@ -378,23 +384,27 @@ def main():
         # queued right behind step i).  Every step still pays one H2D copy of its inputs and one D2H read of its loss
         # inside the timed region; both arms run the same loop.
         pf = _Prefetcher(torch, device)
-        for i in range(2):
-            train_step(host_x[i % 2].to(device, non_blocking=True), host_y[i % 2].to(device, non_blocking=True)).item()
+
+        def pipelined(n):
+            staged = pf.stage(host_x[0], host_y[0])
+            pending = value = None
+            for i in range(n):
+                x, y = pf.take(staged)
+                if i + 1 < n:
+                    staged = pf.stage(host_x[(i + 1) % 2], host_y[(i + 1) % 2])
+                reader = _Deferred(torch, train_step(x, y))
+                if pending is not None:
+                    value = pending.get()
+                pending = reader
+                flush.zero_()
+            return pending.get() if pending is not None else value
+        # warm-up through the same loop: the side stream's memory pool and the pinned read-back buffers are allocated here,
+        # not inside the timed region (a first pinned allocation costs milliseconds)
+        pipelined(max(3, min(args.warmup, 5)))
         barrier()
         t0 = time.perf_counter()
         ev0.record()
-        staged = pf.stage(host_x[0], host_y[0])
-        pending = None
-        for i in range(args.steps):
-            x, y = pf.take(staged)
-            if i + 1 < args.steps:
-                staged = pf.stage(host_x[(i + 1) % 2], host_y[(i + 1) % 2])
-            reader = _Deferred(torch, train_step(x, y))
-            if pending is not None:
-                loss_val = pending.get()
-            pending = reader
-            flush.zero_()
-        loss_val = pending.get()
+        loss_val = pipelined(args.steps)
         ev1.record()
         barrier()
         check_comm()

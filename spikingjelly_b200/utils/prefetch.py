@@ -54,10 +54,21 @@ class DevicePrefetcher:
 class DeferredScalar:
     """``DeferredScalar(t)`` queues a device-to-host copy of the one-element tensor ``t``; ``get()`` waits for it."""
 
+    # Pinned landing buffers are reused in turn (a first pinned allocation costs milliseconds and may synchronise the
+    # device); eight cover every loop that reads a value at most seven steps late.
+    _ring: dict = {}
+    _cursor = 0
+    _RING = 8
+
     def __init__(self, value: torch.Tensor):
         v = value.detach().reshape(1)
         if v.is_cuda:
-            self._host = torch.empty(1, dtype=v.dtype, pin_memory=True)
+            cls = DeferredScalar
+            ring = cls._ring.setdefault(v.dtype, [])
+            if len(ring) < cls._RING:
+                ring.append(torch.empty(1, dtype=v.dtype, pin_memory=True))
+            self._host = ring[cls._cursor % len(ring)]
+            cls._cursor += 1
             self._host.copy_(v, non_blocking=True)
             self._event = torch.cuda.Event()
             self._event.record(torch.cuda.current_stream(v.device))
