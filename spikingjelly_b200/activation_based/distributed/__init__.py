@@ -12,3 +12,13 @@ for _name in ("api", "analysis", "config", "data_parallel", "execution", "fsdp",
     _mod = importlib.import_module(f"spikingjelly_b200.parallel.{_name}")
     sys.modules[f"{__name__}.{_name}"] = _mod
     globals()[_name] = _mod
+
+# The reference splits three of these into packages (``distributed/pipeline/partition.py`` ...); here each is one module,
+# so the sub-module paths resolve to that module.
+for _pkg, _subs in (("pipeline", ("cifar10dvs_vgg", "memopt", "partition", "runtime", "spikformer")),
+                    ("tensor_parallel", ("channel", "cifar10dvs_vgg", "debug", "linear", "spikformer", "state")),
+                    ("adapters", ("base", "cifar10dvs_vgg", "spikformer"))):
+    for _sub in _subs:
+        sys.modules[f"{__name__}.{_pkg}.{_sub}"] = globals()[_pkg]
+        if not hasattr(globals()[_pkg], _sub):          # ``import a.b.c as m`` reads the attribute c of a.b
+            setattr(globals()[_pkg], _sub, globals()[_pkg])

@@ -1,0 +1,4 @@
+"""Import path of the reference's ``spikingjelly/activation_based/neuron/few_spike.py``: the names below live in the ``neuron`` package here."""
+from . import FewSpikeTable, FewSpikeNode, OutlierAwareThresholdNode, HGNode  # noqa: F401
+
+__all__ = ['FewSpikeTable', 'FewSpikeNode', 'OutlierAwareThresholdNode', 'HGNode']

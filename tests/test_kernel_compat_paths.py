@@ -207,3 +207,23 @@ def test_object_handles_switch_and_raw_arguments(monkeypatch):
     assert [type(v) for v in out] == [ctypes.c_int, ctypes.c_float, ctypes.c_float, ctypes.c_bool] and out[1].value == 2.5
     with pytest.raises(ValueError):
         U.wrap_args_to_raw_kernel(0, torch.zeros(2))              # a CPU tensor is on device -1
+
+
+def test_reference_submodule_import_paths():
+    """Modules the reference splits into several files resolve here too (same names, one implementation)."""
+    import importlib
+    for path, names in (("activation_based.neuron.noisy", ["NoisyCUBALIFNode", "powerlaw_psd_gaussian"]),
+                        ("activation_based.neuron.plif", ["ParametricLIFNode"]),
+                        ("activation_based.neuron.spikezip", ["STBIFNeuron"]),
+                        ("activation_based.layer.stateless_wrapper", ["Conv2d", "WSLinear"]),
+                        ("activation_based.op_counter.synop", ["SynOpCounter"]),
+                        ("activation_based.op_counter.neuromc.mux_counter", ["NeuroMCMuxCounter"]),
+                        ("activation_based.precision.float8_te", []),
+                        ("activation_based.distributed.pipeline.partition", []),
+                        ("activation_based.distributed.tensor_parallel.linear", []),
+                        ("activation_based.distributed.adapters.base", [])):
+        m = importlib.import_module("spikingjelly_b200." + path)
+        for n in names:
+            assert hasattr(m, n), (path, n)
+    import spikingjelly_b200.activation_based.distributed.pipeline.runtime as r
+    assert r.__name__ == "spikingjelly_b200.parallel.pipeline"
