@@ -35,7 +35,7 @@ from ..operators import TDGELU, TDLayerNorm, TDSoftmax
 from .base import ModuleConversionRecipe
 
 __all__ = ["SpikeZIPTFQANNRecipe", "SpikeZIPLinear", "SpikeZIPConv2d", "SpikeZIPEmbedding", "SpikeZIPLayerNorm",
-           "SpikeZIPSoftmax", "SpikeZIPSelfAttention", "is_quantizer"]
+           "SpikeZIPSoftmax", "SpikeZIPSelfAttention", "SpikeZIPRobertaSelfAttention", "SpikeZIPViTSelfAttention", "is_quantizer"]
 
 
 def is_quantizer(module: nn.Module) -> bool:
@@ -296,6 +296,15 @@ class SpikeZIPSelfAttention(_StepwiseModule):
                 m.step_mode = mode
 
 
+class SpikeZIPRobertaSelfAttention(SpikeZIPSelfAttention):
+    """The attribute-driven wrapper under the reference's name for the RoBERTa layout (``query`` / ``key`` / ``value`` linears,
+    ``query_quan`` ... quantisers, ``num_attention_heads``)."""
+
+
+class SpikeZIPViTSelfAttention(SpikeZIPSelfAttention):
+    """The same wrapper under the reference's name for the ViT layout (packed ``qkv``, ``quan_q`` ..., ``num_heads``, ``proj``)."""
+
+
 def _is_qattention(module: nn.Module) -> bool:
     has_proj = getattr(module, "qkv", None) is not None or all(getattr(module, n, None) is not None for n in ("query", "key", "value"))
     has_quan = any(getattr(module, n, None) is not None for n in ("query_quan", "quan_q"))
@@ -397,7 +406,8 @@ class SpikeZIPTFQANNRecipe(ModuleConversionRecipe):
         for name, child in list(model.named_children()):
             new = None
             if _is_qattention(child):
-                new = SpikeZIPSelfAttention(child, self._attention_level(child))
+                cls = SpikeZIPViTSelfAttention if getattr(child, "qkv", None) is not None else SpikeZIPRobertaSelfAttention
+                new = cls(child, self._attention_level(child))
             elif isinstance(child, nn.Embedding):
                 new = SpikeZIPEmbedding(child)
             elif isinstance(child, nn.Conv2d):

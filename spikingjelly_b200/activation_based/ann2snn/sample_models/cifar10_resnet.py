@@ -89,3 +89,10 @@ def ResNet101(**kw):
 
 def ResNet152(**kw):
     return ResNet(Bottleneck, [3, 8, 36, 3], **kw)
+
+
+def test():
+    """Shape check of ``ResNet18`` on one CIFAR-sized image; returns the output shape."""
+    shape = tuple(ResNet18()(torch.randn(1, 3, 32, 32)).shape)
+    assert shape == (1, 10), shape
+    return shape

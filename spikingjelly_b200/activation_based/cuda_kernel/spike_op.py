@@ -21,7 +21,8 @@ from torch.nn.modules.utils import _pair, _single, _triple
 
 from . import tensor_cache
 
-__all__ = ["spike_linear", "spike_conv1d", "spike_conv2d", "spike_conv3d", "SpikeLinear", "SpikeConv1d", "SpikeConv2d", "SpikeConv3d"]
+__all__ = ["spike_linear", "spike_conv1d", "spike_conv2d", "spike_conv3d", "SpikeLinear", "SpikeConv1d", "SpikeConv2d", "SpikeConv3d",
+           "cupy_spike_linear_forward", "cupy_spike_convolution_forward"]
 
 _OPS = {0: F.linear, 1: F.conv1d, 2: F.conv2d, 3: F.conv3d}
 
@@ -197,3 +198,18 @@ SpikeConv2d = _conv_module(nn.Conv2d, spike_conv2d, _pair)
 SpikeConv2d.__name__ = SpikeConv2d.__qualname__ = "SpikeConv2d"
 SpikeConv3d = _conv_module(nn.Conv3d, spike_conv3d, _triple)
 SpikeConv3d.__name__ = SpikeConv3d.__qualname__ = "SpikeConv3d"
+
+
+def cupy_spike_linear_forward(spike: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """The reference's operator name for :func:`spike_linear` (the input is kept for backward as bits)."""
+    return spike_linear(spike, weight, bias)
+
+
+def cupy_spike_convolution_forward(spike: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], stride, padding, dilation,
+                                   groups: int) -> torch.Tensor:
+    """The reference's operator name for ``spike_conv1d / 2d / 3d``, chosen by the rank of ``spike``."""
+    fn = {3: spike_conv1d, 4: spike_conv2d, 5: spike_conv3d}.get(spike.dim())
+    if fn is None:
+        raise ValueError(f"expected a 3-, 4- or 5-dimensional spike tensor, got {spike.dim()} dimensions")
+    as_arg = lambda v: v if isinstance(v, (int, str)) else tuple(v)          # noqa: E731
+    return fn(spike, weight, bias, as_arg(stride), as_arg(padding), as_arg(dilation), groups)

@@ -13,7 +13,7 @@ import torch
 from ... import configure
 from ...ops import bitpack
 
-__all__ = ["float_spike_to_bool", "bool_spike_to_float", "tensor_key", "BoolTensorCache", "BOOL_TENSOR_CACHE"]
+__all__ = ["float_spike_to_bool", "bool_spike_to_float", "tensor_key", "BoolTensorCache", "BOOL_TENSOR_CACHE", "DataTypeConvertCUDACode"]
 
 
 def float_spike_to_bool(spike: torch.Tensor) -> Tuple[torch.Tensor, torch.dtype, torch.Size, int]:
@@ -70,3 +70,12 @@ class BoolTensorCache:
 
 
 BOOL_TENSOR_CACHE = BoolTensorCache()
+
+
+class DataTypeConvertCUDACode:
+    """Where the conversion kernels live.  The reference keeps four CuPy source strings under these attribute names
+    (``float2bool``, ``half2bool``, ``bool2float``, ``bool2half``: 8 spikes <-> 1 byte); here the conversions are compiled
+    kernels of the native library (32 spikes <-> one 32-bit word, any floating dtype), and each attribute names its entry point."""
+    source_file = "spikingjelly_b200/ops/csrc/bitpack.cu"
+    float2bool = half2bool = "torch.ops.sjb200.bit_pack"
+    bool2float = bool2half = "torch.ops.sjb200.bit_unpack"

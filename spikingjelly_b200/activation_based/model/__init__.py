@@ -8,7 +8,8 @@ import sys
 from ...models.spikformer import *  # noqa: F401,F403
 
 _SUBMODULES = ("spikformer", "sew_resnet", "spiking_resnet", "spiking_vgg", "parametric_lif_net", "train_classify",
-               "tv_ref_classify", "spiking_vggws_ottt", "snas_net", "spike_dhs")
+               "tv_ref_classify", "spiking_vggws_ottt", "snas_net", "spike_dhs", "train_imagenet_example",
+               "train_flexsn_inductor_example")
 
 for _name in _SUBMODULES:
     try:
@@ -19,5 +20,11 @@ for _name in _SUBMODULES:
         continue
     sys.modules[f"{__name__}.{_name}"] = _mod
     globals()[_name] = _mod
+
+# sub-modules of the torchvision-reference helpers, registered under this path as well: found through the package's
+# ``__path__`` alone they would be loaded a second time under the alias name
+for _name in ("presets", "sampler", "transforms", "utils"):
+    _mod = importlib.import_module(f"spikingjelly_b200.models.tv_ref_classify.{_name}")
+    sys.modules[f"{__name__}.tv_ref_classify.{_name}"] = _mod
 
 from ...models.train_classify import Trainer  # noqa: E402,F401

@@ -19,7 +19,9 @@ from ..triton_utils import (is_fp8_dtype, normalize_cuda_device, normalize_trito
 
 __all__ = ["multistep_if", "multistep_lif", "multistep_plif", "multistep_if_mp", "multistep_lif_mp", "multistep_plif_mp",
            "multistep_if_mp_with_plan", "multistep_lif_mp_with_plan", "multistep_plif_mp_with_plan", "multistep_if_inference",
-           "multistep_lif_inference", "multistep_plif_inference", "TritonNeuronExecutionPlan", "prepare_triton_neuron_execution_plan"]
+           "multistep_lif_inference", "multistep_plif_inference", "multistep_if_forward", "multistep_lif_forward", "multistep_plif_forward",
+           "multistep_if_mp_inference", "multistep_lif_mp_inference", "multistep_plif_mp_inference", "multistep_if_mp_forward",
+           "multistep_lif_mp_forward", "multistep_plif_mp_forward", "TritonNeuronExecutionPlan", "prepare_triton_neuron_execution_plan"]
 
 
 def _spec(kind: str, tau: float, v_threshold: float, v_reset: Optional[float], detach_reset: bool, surrogate_function):
@@ -188,3 +190,93 @@ def multistep_lif_inference(x_seq, v_init, decay_input: bool, tau: float, v_thre
 
 def multistep_plif_inference(x_seq, v_init, r_tau: torch.Tensor, decay_input: bool, v_threshold: float, v_reset: float, soft_reset: bool):
     return _inference("plif_di" if decay_input else "plif_ndi", x_seq, v_init, 2.0, v_threshold, v_reset, soft_reset, True, r=r_tau)
+
+
+# ------------------------------------------------------------------ positional forms (the reference's custom-op signatures)
+# A surrogate is given as (sg_triton_id, sg_alpha) in the reference's numbering (triton_kernel/surrogate_kernel.py); dtypes as the
+# integer ids of triton_utils.  Every form returns (spike_seq, v_seq, h_seq) with h_seq = None: it is never materialised here.
+def _sg_from_id(sg_triton_id: int, sg_alpha: float):
+    from ..surrogate_kernel import _BY_ID
+    if sg_triton_id not in _BY_ID:
+        raise ValueError(f"unknown surrogate id {sg_triton_id}")
+    return _BY_ID[sg_triton_id](alpha=float(sg_alpha))
+
+
+def _reset(v_reset, soft_reset):
+    return None if soft_reset else v_reset
+
+
+def multistep_if_forward(x_seq, v_init, v_threshold: float, v_reset: float, soft_reset: bool, detach_reset: bool, sg_triton_id: int,
+                         sg_alpha: float, store_v_seq: bool = True):
+    return (*multistep_if(x_seq, v_init, v_threshold, _reset(v_reset, soft_reset), detach_reset, _sg_from_id(sg_triton_id, sg_alpha), store_v_seq), None)
+
+
+def multistep_lif_forward(x_seq, v_init, decay_input: bool, tau: float, v_threshold: float, v_reset: float, soft_reset: bool,
+                          detach_reset: bool, sg_triton_id: int, sg_alpha: float, store_v_seq: bool = True):
+    return (*multistep_lif(x_seq, v_init, decay_input, tau, v_threshold, _reset(v_reset, soft_reset), detach_reset,
+                           _sg_from_id(sg_triton_id, sg_alpha), store_v_seq), None)
+
+
+def multistep_plif_forward(x_seq, v_init, r_tau: torch.Tensor, decay_input: bool, v_threshold: float, v_reset: float, soft_reset: bool,
+                           detach_reset: bool, sg_triton_id: int, sg_alpha: float):
+    return (*multistep_plif(x_seq, v_init, r_tau, decay_input, v_threshold, _reset(v_reset, soft_reset), detach_reset,
+                            _sg_from_id(sg_triton_id, sg_alpha)), None)
+
+
+def _plan_from_ids(neuron_type, x_seq, storage_dtype_id, forward_compute_dtype_id, backward_compute_dtype_id, spike_dtype_id, save_intermediates):
+    from ..triton_utils import triton_neuron_dtype_id_to_torch_dtype as to_dtype
+    names = {torch.float32: "fp32", torch.float16: "fp16", torch.bfloat16: "bf16"}
+    comp = lambda i: names.get(to_dtype(i), "fp8")          # noqa: E731
+    return prepare_triton_neuron_execution_plan(neuron_type=neuron_type, device=x_seq.device, storage_dtype=to_dtype(storage_dtype_id),
+                                                forward_compute_dtype=comp(forward_compute_dtype_id),
+                                                backward_compute_dtype=comp(backward_compute_dtype_id), spike_dtype=to_dtype(spike_dtype_id),
+                                                save_intermediates=save_intermediates)
+
+
+def multistep_if_mp_inference(x_seq, v_init, v_threshold: float, v_reset: float, soft_reset: bool, storage_dtype_id: int,
+                              forward_compute_dtype_id: int, spike_dtype_id: int, save_intermediates: bool = False):
+    plan = _plan_from_ids("if", x_seq, storage_dtype_id, forward_compute_dtype_id, 0, spike_dtype_id, save_intermediates)
+    with torch.no_grad():
+        return multistep_if_mp_with_plan(x_seq, v_init, plan, v_threshold=v_threshold, v_reset=_reset(v_reset, soft_reset))
+
+
+def multistep_lif_mp_inference(x_seq, v_init, decay_input: bool, tau: float, v_threshold: float, v_reset: float, soft_reset: bool,
+                               storage_dtype_id: int, forward_compute_dtype_id: int, spike_dtype_id: int, save_intermediates: bool = False):
+    plan = _plan_from_ids("lif", x_seq, storage_dtype_id, forward_compute_dtype_id, 0, spike_dtype_id, save_intermediates)
+    with torch.no_grad():
+        return multistep_lif_mp_with_plan(x_seq, v_init, plan, decay_input=decay_input, tau=tau, v_threshold=v_threshold,
+                                          v_reset=_reset(v_reset, soft_reset))
+
+
+def multistep_plif_mp_inference(x_seq, v_init, r_tau: torch.Tensor, decay_input: bool, v_threshold: float, v_reset: float, soft_reset: bool,
+                                storage_dtype_id: int, forward_compute_dtype_id: int, spike_dtype_id: int, save_intermediates: bool = False):
+    plan = _plan_from_ids("plif", x_seq, storage_dtype_id, forward_compute_dtype_id, 0, spike_dtype_id, save_intermediates)
+    with torch.no_grad():
+        return multistep_plif_mp_with_plan(x_seq, v_init, r_tau, plan, decay_input=decay_input, v_threshold=v_threshold,
+                                           v_reset=_reset(v_reset, soft_reset))
+
+
+def multistep_if_mp_forward(x_seq, v_init, v_threshold: float, v_reset: float, soft_reset: bool, detach_reset: bool, sg_triton_id: int,
+                            sg_alpha: float, storage_dtype_id: int, forward_compute_dtype_id: int, backward_compute_dtype_id: int,
+                            spike_dtype_id: int):
+    plan = _plan_from_ids("if", x_seq, storage_dtype_id, forward_compute_dtype_id, backward_compute_dtype_id, spike_dtype_id, True)
+    return multistep_if_mp_with_plan(x_seq, v_init, plan, v_threshold=v_threshold, v_reset=_reset(v_reset, soft_reset), detach_reset=detach_reset,
+                                     surrogate_function=_sg_from_id(sg_triton_id, sg_alpha))
+
+
+def multistep_lif_mp_forward(x_seq, v_init, decay_input: bool, tau: float, v_threshold: float, v_reset: float, soft_reset: bool,
+                             detach_reset: bool, sg_triton_id: int, sg_alpha: float, storage_dtype_id: int, forward_compute_dtype_id: int,
+                             backward_compute_dtype_id: int, spike_dtype_id: int):
+    plan = _plan_from_ids("lif", x_seq, storage_dtype_id, forward_compute_dtype_id, backward_compute_dtype_id, spike_dtype_id, True)
+    return multistep_lif_mp_with_plan(x_seq, v_init, plan, decay_input=decay_input, tau=tau, v_threshold=v_threshold,
+                                      v_reset=_reset(v_reset, soft_reset), detach_reset=detach_reset,
+                                      surrogate_function=_sg_from_id(sg_triton_id, sg_alpha))
+
+
+def multistep_plif_mp_forward(x_seq, v_init, r_tau: torch.Tensor, decay_input: bool, v_threshold: float, v_reset: float, soft_reset: bool,
+                              detach_reset: bool, sg_triton_id: int, sg_alpha: float, storage_dtype_id: int, forward_compute_dtype_id: int,
+                              backward_compute_dtype_id: int, spike_dtype_id: int):
+    plan = _plan_from_ids("plif", x_seq, storage_dtype_id, forward_compute_dtype_id, backward_compute_dtype_id, spike_dtype_id, True)
+    return multistep_plif_mp_with_plan(x_seq, v_init, r_tau, plan, decay_input=decay_input, v_threshold=v_threshold,
+                                       v_reset=_reset(v_reset, soft_reset), detach_reset=detach_reset,
+                                       surrogate_function=_sg_from_id(sg_triton_id, sg_alpha))

@@ -11,7 +11,8 @@ from typing import Callable, Union
 
 import torch
 
-__all__ = ["TRITON_NEURON_DTYPE_FP32", "TRITON_NEURON_DTYPE_FP16", "TRITON_NEURON_DTYPE_BF16", "TRITON_NEURON_DTYPE_FP8_E4M3FN",
+__all__ = ["triton_neuron_compute_dtype_id_to_tl_dtype", "torch_dtype_for_triton_neuron_compute_dtype_id", "convert_and_store",
+           "register_op", "wrap_triton", "TRITON_NEURON_DTYPE_FP32", "TRITON_NEURON_DTYPE_FP16", "TRITON_NEURON_DTYPE_BF16", "TRITON_NEURON_DTYPE_FP8_E4M3FN",
            "TRITON_NEURON_DTYPE_FP8_E5M2", "normalize_triton_compute_dtype_name", "normalize_triton_storage_dtype", "is_fp8_dtype",
            "torch_dtype_to_triton_neuron_dtype_id", "triton_neuron_dtype_id_to_torch_dtype", "triton_compute_dtype_name_to_neuron_dtype_id",
            "resolve_triton_compute_dtype", "torch_dtype_for_triton_compute_dtype", "normalize_cuda_device", "contiguous_and_device_guard",
@@ -124,3 +125,35 @@ def contiguous_and_device_guard(f: Callable) -> Callable:
 def use_static_range_for_triton_neuron_kernel(T: int) -> bool:
     """Whether the reference would unroll the time loop at compile time; here: whether T fits one register chunk."""
     return T <= 8
+
+
+def triton_neuron_compute_dtype_id_to_tl_dtype(dtype_id: int, storage_dtype_id: int):
+    """The reference maps a compute dtype id to a Triton language dtype; the CUDA kernels compute in fp32 registers whatever is
+    asked, so the answer here is the torch dtype the id names (after the same validity checks: fp8 compute needs the matching
+    fp8 storage)."""
+    dt = triton_neuron_dtype_id_to_torch_dtype(dtype_id)
+    if is_fp8_dtype(dt) and dtype_id != storage_dtype_id:
+        raise ValueError("FP8 compute requires the matching FP8 storage dtype.")
+    return dt
+
+
+def torch_dtype_for_triton_neuron_compute_dtype_id(dtype_id: int) -> torch.dtype:
+    """Dtype of reduction buffers for a compute dtype id: fp32 for the fp8 ids (no useful reductions exist on fp8 tensors)."""
+    dt = triton_neuron_dtype_id_to_torch_dtype(dtype_id)
+    return torch.float32 if is_fp8_dtype(dt) else dt
+
+
+def convert_and_store(pointer: torch.Tensor, value: torch.Tensor, boundary_check=None) -> None:
+    """``pointer[...] = value`` with an explicit cast to the destination dtype (in a Triton kernel the reference needs this for
+    block pointers; on tensors it is a converting copy)."""
+    pointer.copy_(value.to(pointer.dtype))
+
+
+def register_op(opname: str, mutates_args=()):
+    """Decorator registering a custom operator (``torch.library.custom_op``; there is no Triton-op variant to choose)."""
+    return torch.library.custom_op(opname, mutates_args=mutates_args)
+
+
+def wrap_triton(kernel):
+    """Identity: kernels here are CUDA launchers, which need no wrapping to be traced as opaque calls."""
+    return kernel

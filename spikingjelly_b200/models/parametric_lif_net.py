@@ -86,3 +86,23 @@ class DVSGestureNet(_PLIFNet):
         super().__init__()
         sn = lambda: spiking_neuron(**deepcopy(kwargs))
         self.conv_fc = nn.Sequential(*_conv_stack(2, channels, 5, 1, sn), *_head(channels * 4 * 4, 512, 110, layer.VotingLayer(10), sn))
+
+
+def test_models():
+    """Builds every network of this file with IF neurons and runs one batch in both step modes; returns
+    ``{name: (single-step output shape, multi-step output shape)}``."""
+    import torch
+
+    from ..activation_based import functional, neuron, surrogate
+    shapes = {"MNISTNet": (1, 28, 28), "FashionMNISTNet": (1, 28, 28), "NMNISTNet": (2, 32, 32), "CIFAR10Net": (3, 32, 32),
+              "CIFAR10DVSNet": (2, 128, 128), "DVSGestureNet": (2, 128, 128)}
+    out = {}
+    for name, chw in shapes.items():
+        net = globals()[name](16, neuron.IFNode, surrogate_function=surrogate.ATan())
+        with torch.no_grad():
+            single = tuple(net(torch.rand(2, *chw)).shape)
+            functional.reset_net(net)
+            functional.set_step_mode(net, "m")
+            multi = tuple(net(torch.rand(3, 2, *chw)).shape)
+        out[name] = (single, multi)
+    return out

@@ -74,6 +74,26 @@ class _DSpikeFn(torch.autograd.Function):
         return g.masked_fill(x.abs() > 0.5, 0), None
 
 
+def dSpike_backward(grad_output: torch.Tensor, x: torch.Tensor, alpha: float):
+    """``(grad_x, None)``: the gradient :class:`DSpike` applies, as a function of the saved input."""
+    const = alpha / (2.0 * tanh(alpha / 2.0))
+    return (grad_output * const / torch.cosh(alpha * x).square()).masked_fill(x.abs() > 0.5, 0), None
+
+
+dSpike = _DSpikeFn          # the autograd function under the reference's name: ``dSpike.apply(x, alpha)``
+
+
+class Nearest(nn.Module):
+    """Nearest-neighbour resize to a fixed spatial ``shape``."""
+
+    def __init__(self, shape) -> None:
+        super().__init__()
+        self._shape = shape
+
+    def forward(self, x):
+        return F.interpolate(x, self._shape, mode="nearest")
+
+
 class DSpike(SurrogateFunctionBase):
     """Heaviside forward; backward ``alpha / (2 tanh(alpha / 2)) / cosh^2(alpha x)`` inside ``|x| <= 1/2`` and zero
     outside: the derivative of a tanh ramp whose temperature ``alpha`` moves it between a box and a delta."""

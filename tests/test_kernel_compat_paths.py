@@ -181,6 +181,27 @@ def test_functional_neuron_kernels_match_the_modules():
     assert r_tau.grad is not None and torch.allclose(xp.grad, x2.grad)
     si, vi = K.multistep_lif_inference(x.detach(), torch.zeros(4, 64, device="cuda"), True, 2.0, 1.0, 0.0, False, True)
     assert torch.equal(si, s2.detach()) and torch.equal(vi, node.v_seq) and not si.requires_grad
+    # positional forms: surrogate as (id, alpha) in the reference's numbering (1 = ATan), dtypes as ids
+    sf, vf, hf = K.multistep_lif_forward(x.detach(), torch.zeros(4, 64, device="cuda"), True, 2.0, 1.0, 0.0, False, False, 1, sg.alpha, True)
+    assert torch.equal(sf, s2.detach()) and hf is None
+    from spikingjelly_b200.activation_based.triton_kernel import triton_utils as TU
+    e4, b16 = TU.torch_dtype_to_triton_neuron_dtype_id(torch.float8_e4m3fn), TU.torch_dtype_to_triton_neuron_dtype_id(torch.bfloat16)
+    sm, _, _ = K.multistep_lif_mp_inference(xb.detach(), torch.zeros(4, 64, device="cuda"), True, 2.0, 1.0, 0.0, False, e4, 0, b16, False)
+    assert torch.equal(sm, s8.detach())
+    from spikingjelly_b200.activation_based.triton_kernel.neuron_kernel import stbif as KS
+    xs = torch.randn(6, 512, device="cuda") * 0.5
+    args = (torch.full((512,), 0.5, device="cuda"), torch.zeros(512, device="cuda"), torch.tensor(0.25), torch.tensor(7.0), torch.tensor(-8.0))
+    og, qg, ag, cg, fg = KS.multi_step_stbif(xs, *args)
+    oc, qc, ac, cc, fc = KS.multi_step_stbif(xs.cpu(), *(a.cpu() for a in args))
+    assert torch.equal(og.cpu(), oc) and torch.equal(ag.cpu(), ac) and torch.equal(qg.cpu(), qc) and bool(fg) == bool(fc)
+    from spikingjelly_b200.activation_based.cuda_kernel.neuron_kernel.multi_step import izhikevich as KZ, lif as KL
+    sl, vl = KL.lif_multi_step(x.detach(), torch.zeros(4, 64, device="cuda"), True, 2.0, 1.0, 0.0, False, sg)
+    assert torch.equal(sl, s2.detach()) and torch.equal(vl, node.v_seq)
+    xz = torch.rand(5, 300, device="cuda") * 3
+    z = torch.zeros(300, device="cuda")
+    zg = KZ.izhikevich_multi_step(xz, z, z.clone(), 2.0, 1.0, 0.0, -0.1, 0.02, 0.2, 200.0, 0.5, 1.0, False, sg)
+    zc = KZ.izhikevich_multi_step(xz.cpu(), z.cpu(), z.cpu(), 2.0, 1.0, 0.0, -0.1, 0.02, 0.2, 200.0, 0.5, 1.0, False, sg)
+    assert torch.equal(zg[0].cpu(), zc[0]) and torch.allclose(zg[1].cpu(), zc[1], atol=1e-5) and torch.allclose(zg[2].cpu(), zc[2], atol=1e-5)
 
 
 def test_object_handles_switch_and_raw_arguments(monkeypatch):
@@ -227,3 +248,133 @@ def test_reference_submodule_import_paths():
             assert hasattr(m, n), (path, n)
     import spikingjelly_b200.activation_based.distributed.pipeline.runtime as r
     assert r.__name__ == "spikingjelly_b200.parallel.pipeline"
+
+
+def test_compat_packages_on_cpu():
+    """torch2triton, triton_kernel.flexsn, surrogate_kernel, ilif / stbif functional forms, inductor_cache: CPU behaviour."""
+    import torch
+    from spikingjelly_b200.activation_based import neuron, surrogate
+    from spikingjelly_b200.activation_based.neuron import inductor_cache as IC
+    from spikingjelly_b200.activation_based.triton_kernel import dummy, flexsn as TF, surrogate_kernel as SK, torch2triton as T2
+    from spikingjelly_b200.activation_based.triton_kernel.flexsn import custom_ops as C, hop, template, wrapper
+    from spikingjelly_b200.activation_based.triton_kernel.neuron_kernel import ilif, stbif
+    sg = surrogate.Sigmoid(alpha=4.0)
+
+    def core(x, v):
+        h = v + (x - v) * 0.5
+        s = sg(h - 1.0)
+        return s, h * (1.0 - s)
+    fwd, bwd = T2.generate_forward_and_backward_graph(core, (torch.rand(8), torch.rand(8)), (True, False))
+    assert len([n for n in fwd.nodes if n.op == "placeholder"]) == 2 and len([n for n in bwd.nodes if n.op == "placeholder"]) == 4
+    src, name = T2.generate_triton_code_str(fwd, "lif core")
+    assert name.startswith("lif_core_") and f"void {name}(" in src
+    fk, bk, info = TF.build_training_kernels(core, 1, 1, 1)
+    assert fk is bk and info.fwd_kernel_returns == ["s0", "v0"] and info.num_fwd_kernel_returns == 2
+    before = C.flexsn_kernel_registry_info()["entries"]
+    h = C.register_flexsn_kernel_handle(forward_kernel=fk, backward_kernel=bk, training_info=info)
+    assert C.flexsn_kernel_registry_info()["entries"] == before + 1
+    C.release_flexsn_kernel_handle(h)
+    assert C.flexsn_kernel_registry_info()["entries"] == before
+    with pytest.raises(TypeError):
+        C.register_flexsn_kernel_handle(forward_kernel=object())
+    assert template.get_flexsn_backward_kernel(fk.graphs)[1] == "flexsn_backward"
+    x, v0 = torch.rand(5, 8), torch.zeros(8)
+    full, last = hop.eager_scan(core, 1, 1, 1, x, v0), hop.eager_scan_final_state(core, 1, 1, 1, x, v0)
+    assert torch.equal(full[1][-1], last[1]) and not hop.lowerable_scan_available()
+    assert [wrapper.flexsn_backward_ncl_bucket(n) for n in (1, 4097, 131073, 1048577, 8388609)] == [0, 1, 2, 3, 4]
+    assert SK.resolve_sg_triton_id_and_alpha(surrogate.ATan(alpha=3.0)) == (1, 3.0)
+    with pytest.raises(NotImplementedError):
+        SK.resolve_sg_triton_id_and_alpha(surrogate.PiecewiseLeakyReLU())
+    hh = torch.linspace(-1, 1, 7)
+    assert torch.allclose(SK.sg_triton(hh, 4.0, 0), 4.0 * torch.sigmoid(4 * hh) * (1 - torch.sigmoid(4 * hh)))
+    assert not dummy.DummyImport().a.b(1)[2]
+    xs = torch.randn(6, 8) * 0.5
+    out, q, acc, cur, flag = stbif.multi_step_stbif(xs, torch.full((8,), 0.5), torch.zeros(8), torch.tensor(0.25), torch.tensor(7.0), torch.tensor(-8.0))
+    node = neuron.STBIFNeuron(0.25, level=16, sym=True, step_mode="m")
+    assert torch.equal(out, node(xs)) and torch.equal(acc, node.acc_q) and bool(flag)
+    xi = torch.rand(5, 4) * 3
+    s, v = ilif.multistep_ilif_forward_no_grad(xi, torch.zeros(4), 0.25, 1.0, 4, True)
+    ref = neuron.ILIFNode(tau=4 / 3, step_mode="m", store_v_seq=True)
+    assert torch.equal(s, ref(xi)) and torch.equal(v, ref.v_seq)
+    IC.clear()
+    key = ("lif", IC.surrogate_key(sg), IC.runtime_key(x))
+    f1 = IC.compile_graph(key, lambda: 1)
+    assert IC.compile_graph(key, lambda: 2) is f1 and IC.info()["hits"] == 1 and IC.compile_graph(None, core) is core
+    assert torch.equal(IC.surrogate_callable(sg)(hh), sg(hh))
+
+
+@pytest.mark.gpu
+def test_fragment_assembled_neuron_kernels_match_autograd():
+    """IF / LIF / PLIF kernels built from code fragments (the custom-neuron extension classes) against an eager loop."""
+    import torch
+    from spikingjelly_b200.activation_based import functional, surrogate
+    from spikingjelly_b200.activation_based.cuda_kernel.neuron_kernel.multi_step import integrate_and_fire as MI, lif as ML, plif as MP
+    from spikingjelly_b200.activation_based.cuda_kernel.neuron_kernel.multi_step.base import NeuronBPTTKernel, NeuronFPTTKernel
+    from spikingjelly_b200.activation_based.cuda_kernel.neuron_kernel.multi_step import _atgf
+    from spikingjelly_b200.activation_based.cuda_kernel.neuron_kernel.single_step import lif as SL
+    torch.manual_seed(0)
+    sg = surrogate.ATan()
+    T, N = 6, 257
+    x0 = (torch.rand(T, N, device="cuda") * 2.5)
+    gs, gv = torch.randn(T, N, device="cuda"), torch.randn(T, N, device="cuda") * 0.1
+
+    def eager(step, extra=()):
+        x = x0.clone().requires_grad_(True)
+        v = torch.zeros(N, device="cuda", requires_grad=True)
+        vv, ss, vs = v, [], []
+        for t in range(T):
+            s, vv = step(x[t], vv)
+            ss.append(s)
+            vs.append(vv)
+        s_seq, v_seq = torch.stack(ss), torch.stack(vs)
+        grads = torch.autograd.grad((s_seq * gs).sum() + (v_seq * gv).sum(), [x, v, *extra], allow_unused=True)
+        return s_seq, v_seq, grads
+
+    def check(run, step, extra=()):
+        x = x0.clone().requires_grad_(True)
+        v = torch.zeros(N, device="cuda", requires_grad=True)
+        s, vs, _ = run(x, v)
+        want_s, want_v, want_g = eager(step, extra)
+        assert torch.equal(s, want_s) and torch.allclose(vs, want_v, atol=1e-6)
+        got = torch.autograd.grad((s * gs).sum() + (vs * gv).sum(), [x, v, *extra], allow_unused=True)
+        for a, b in zip(got, want_g):
+            assert torch.allclose(a, b, atol=2e-4, rtol=1e-4), (a - b).abs().max()
+    for soft, detach in ((False, False), (True, True)):
+        vr = None if soft else 0.0
+        check(lambda x, v: MI.cupy_multistep_if_forward(x, v, 1.0, 0.0, soft, detach, sg),
+              lambda x, v: functional.neuron.if_step(x, v, 1.0, vr, sg, detach))
+        for di in (True, False):
+            check(lambda x, v: ML.cupy_multistep_lif_forward(x, v, 1.0, 0.0, soft, detach, 0.5, di, sg),
+                  lambda x, v: functional.neuron.lif_step(x, v, 2.0, di, 1.0, vr, sg, detach))
+    w = torch.tensor(0.3, device="cuda", requires_grad=True)
+    for di in (True, False):
+        check(lambda x, v: MP.cupy_multistep_plif_forward(x, v, 1.0, 0.0, False, False, w.sigmoid(), di, sg),
+              lambda x, v: functional.neuron.plif_step(x, v, w, di, 1.0, 0.0, sg, False), extra=(w,))
+
+    # a custom neuron through the extension classes: h = 0.9 v + 0.5 x
+    class FP(NeuronFPTTKernel):
+        def neuronal_charge(self):
+            return "h_seq[t] = 0.9f * v_v_seq[t] + 0.5f * x_seq[t];"
+
+    class BP(NeuronBPTTKernel):
+        def grad_h_next_to_v(self):
+            return "const float grad_h_next_to_v = 0.9f;"
+
+        def grad_h_to_x(self):
+            return "const float grad_h_to_x = 0.5f;"
+
+    def custom(xt, vv):
+        h = 0.9 * vv + 0.5 * xt
+        sp = sg(h - 1.0)
+        return sp, h * (1 - sp)
+    check(lambda x, v: (*_atgf.run(x, v, 1.0, 0.0, FP(True, "float"), BP(sg, True, False, "float")), None), custom)
+    # single step
+    x1 = x0[0].clone().requires_grad_(True)
+    v1 = (torch.rand(N, device="cuda") * 0.5).requires_grad_(True)
+    s1, vn, _ = SL.cupy_single_step_lif_forward(x1, v1, 1.0, 0.0, False, 0.5, True, sg)
+    x2, v2 = x1.detach().clone().requires_grad_(True), v1.detach().clone().requires_grad_(True)
+    s2, vn2 = functional.neuron.lif_step(x2, v2, 2.0, True, 1.0, 0.0, sg, False)
+    assert torch.equal(s1, s2) and torch.allclose(vn, vn2, atol=1e-6)
+    g1 = torch.autograd.grad((s1 * gs[0]).sum() + (vn * gv[0]).sum(), [x1, v1])
+    g2 = torch.autograd.grad((s2 * gs[0]).sum() + (vn2 * gv[0]).sum(), [x2, v2])
+    assert all(torch.allclose(a, b, atol=2e-4, rtol=1e-4) for a, b in zip(g1, g2))

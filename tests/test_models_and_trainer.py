@@ -253,3 +253,31 @@ def test_spiking_vgg_fused_triples_under_autocast():
     assert counters.by_name().get("bn_lif_forward", 0) == 8          # the eight convolution stages of VGG-11 ran fused
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in net.features.parameters())
     functional.reset_net(net)
+
+
+def test_example_trainers_build_their_models_and_shapes():
+    """``SResNetTrainer`` / ``FlexSNTrainer``: argument parsing, model construction, sample repetition and rate read-out."""
+    from spikingjelly_b200.activation_based.model import train_flexsn_inductor_example as F, train_imagenet_example as R
+    from spikingjelly_b200.models.train_imagenet_example import SResNetTrainer
+    assert R.SResNetTrainer is SResNetTrainer
+    t = R.SResNetTrainer()
+    args = t.get_args_parser().parse_args(["--T", "3", "--model", "spiking_resnet18", "--cupy"])
+    assert t.get_tb_logdir_name(args).endswith("_T3")
+    net = t.load_model(args, 7)
+    x = t.preprocess_train_sample(args, torch.rand(2, 3, 32, 32))
+    assert x.shape == (3, 2, 3, 32, 32)
+    with torch.no_grad():
+        y = t.process_model_output(args, net(x))
+    assert y.shape == (2, 7)
+    args.model = "resnet18"
+    with pytest.raises(ValueError, match="args.model should be one of"):
+        t.load_model(args, 7)
+    f = F.FlexSNTrainer()
+    fargs = f.get_args_parser().parse_args(["--T", "2", "--model", "spiking_vgg11_bn", "--surrogate-alpha", "2.0"])
+    assert "flexsn_cuda_sa2.0" in f.get_tb_logdir_name(fargs)
+    vgg = f.load_model(fargs, 5)
+    flex = [m for m in vgg.modules() if isinstance(m, neuron.FlexSN)]
+    assert len(flex) == 10 and flex[0].step_mode == "m"
+    with torch.no_grad():
+        out = f.process_model_output(fargs, vgg(f.preprocess_test_sample(fargs, torch.rand(1, 3, 32, 32))))
+    assert out.shape == (1, 5)
