@@ -305,10 +305,11 @@ class CKernel2D(CKernel):
         return "\n        }\n" + wrap_with_comment(self.post_core, "post_core") + "    }\n}\n"
 
     def check_shape(self, py_dict: dict) -> None:
-        """Every 2-D tensor is ``[T, N]`` with the same ``N``; every 1-D tensor has ``N`` elements."""
+        """Every 2-D tensor is ``[T, N]`` with the same ``N``; every 1-D tensor has ``N`` elements.  One-element tensors are
+        parameters (a learnable scalar and its gradient accumulator) and are not checked."""
         n = None
         for key, v in py_dict.items():
-            if isinstance(v, torch.Tensor) and v.dim() >= 1:
+            if isinstance(v, torch.Tensor) and v.dim() >= 1 and v.numel() != 1:
                 cols = v.shape[1] if v.dim() == 2 else (v.shape[0] if v.dim() == 1 else None)
                 if cols is None:
                     raise ValueError(f"{key}: CKernel2D takes [T, N] and [N] tensors, got shape {tuple(v.shape)}")
