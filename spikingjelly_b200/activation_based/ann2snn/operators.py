@@ -101,6 +101,12 @@ class TDModule(base.MemoryModule):
             return self.multi_step_forward(*inputs, **kwargs)
         raise ValueError(self.step_mode)
 
+    def reset_parameters(self) -> None:
+        """Re-initialises the wrapped ANN operator(s) the way their own ``reset_parameters`` does."""
+        for m in self.children():
+            if hasattr(m, "reset_parameters"):
+                m.reset_parameters()
+
 
 class TDSoftmax(TDModule):
     def __init__(self, dim: int = -1, step_mode: str = "m") -> None:
@@ -158,6 +164,10 @@ class TDRMSNorm(TDModule):
     def ann_forward(self, x):
         return F.rms_norm(x, self.normalized_shape, self.weight, self.eps)
 
+    def reset_parameters(self) -> None:
+        if self.weight is not None:
+            nn.init.ones_(self.weight)
+
 
 class TDGELU(TDModule):
     def __init__(self, approximate: str = "none", step_mode: str = "m") -> None:
@@ -181,9 +191,12 @@ class TDLinear(TDModule):
         self.in_features, self.out_features = in_features, out_features
         self.weight = nn.Parameter(torch.empty(out_features, in_features, device=device, dtype=dtype))
         self.bias = nn.Parameter(torch.empty(out_features, device=device, dtype=dtype)) if bias else None
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
         nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
-        if bias:
-            bound = 1 / math.sqrt(in_features)
+        if self.bias is not None:
+            bound = 1 / math.sqrt(self.in_features)
             nn.init.uniform_(self.bias, -bound, bound)
 
     @classmethod

@@ -300,6 +300,10 @@ class SpikeZIPRobertaSelfAttention(SpikeZIPSelfAttention):
     """The attribute-driven wrapper under the reference's name for the RoBERTa layout (``query`` / ``key`` / ``value`` linears,
     ``query_quan`` ... quantisers, ``num_attention_heads``)."""
 
+    def transpose_for_scores(self, x):
+        """``[..., L, C] -> [..., H, L, D]`` (the name the RoBERTa attention uses for the head split)."""
+        return self._heads(x)
+
 
 class SpikeZIPViTSelfAttention(SpikeZIPSelfAttention):
     """The same wrapper under the reference's name for the ViT layout (packed ``qkv``, ``quan_q`` ..., ``num_heads``, ``proj``)."""

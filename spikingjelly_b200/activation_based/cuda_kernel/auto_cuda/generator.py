@@ -55,6 +55,17 @@ class VarNode:
     def cu_grad(self) -> str:
         return f"g_{self.name}"
 
+    @property
+    def name_bp(self) -> str:
+        """Name of the gradient tensor that goes with this variable in a backward kernel's argument list."""
+        return "grad_" + self.name
+
+    @property
+    def cu_var_bp(self) -> str:
+        """The register holding this variable's gradient inside the generated backward code (the reference's name for
+        :attr:`cu_grad`)."""
+        return self.cu_grad
+
     def __repr__(self) -> str:
         return f"VarNode({self.name}, {self.kind}, requires_grad={self.requires_grad})"
 

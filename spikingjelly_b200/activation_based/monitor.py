@@ -64,11 +64,16 @@ class BaseMonitor:
     def _attach(self, net, instance, register: str, pick: Callable, fn: Callable):
         """``register``: name of the nn.Module registration method; ``pick(module, *hook_args)``
         extracts the raw value; ``fn`` post-processes it."""
+        self._pick, self._post = pick, fn
         for name, module in self._monitor_modules(net, instance):
-            def hook(m, *args, _name=name):
-                if self._enable:
-                    self._record(_name, fn(pick(m, *args)))
-            self.hooks.append(getattr(module, register)(hook))
+            self.hooks.append(getattr(module, register)(self.create_hook(name)))
+
+    def create_hook(self, name):
+        """The hook registered on the module called ``name``; a subclass may override it to record something else."""
+        def hook(m, *args):
+            if self._enable:
+                self._record(name, self._post(self._pick(m, *args)))
+        return hook
 
     def clear_recorded_data(self):
         self.records.clear()

@@ -88,6 +88,16 @@ class ComputeEnergyProfiler:
         logger.info("compute_energy_summary total_pj=%.3f mac=%s ac=%s synop=%s flop=%s", rep.energy_total_pj, mac, ac, synop, flop)
         return rep
 
+    # the reference's accessor names
+    def get_report(self) -> ComputeEnergyReport:
+        return self.report()
+
+    def get_total(self) -> float:
+        return self.report().energy_total_pj
+
+    def get_counts(self) -> dict:
+        return self.report().counts
+
 
 def estimate_compute_energy(model: nn.Module, inputs, *, config: Optional[ComputeEnergyConfig] = None, reset: bool = True) -> ComputeEnergyReport:
     """One inference pass of ``model`` on ``inputs`` under the profiler (neuron state reset afterwards)."""

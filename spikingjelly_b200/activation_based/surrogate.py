@@ -404,12 +404,23 @@ class MultiLevelSpikeCount(SurrogateFunctionBase):
 
 # ---- function-style aliases (``surrogate.atan.apply(x, alpha)`` etc.) ---------
 def _fn_alias(row: str):
-    class _Alias:
-        @staticmethod
-        def apply(x, *params):
-            return _spike(row, x, *params)
-    _Alias.__name__ = row
-    return _Alias
+    """An autograd function per table row: ``forward(x, *params)`` is the Heaviside step, ``backward`` multiplies by the
+    row's derivative; one ``None`` comes back for every parameter."""
+    spec = SURROGATES[row]
+
+    def forward(x, *params):
+        return heaviside(x)
+
+    def setup_context(ctx, inputs, output):
+        ctx.save_for_backward(inputs[0])
+        ctx.params = tuple(inputs[1:])
+
+    def backward(ctx, grad_output):
+        (x,) = ctx.saved_tensors
+        return (grad_output * spec.grad(x, *ctx.params[: len(spec.params)]),) + (None,) * len(ctx.params)
+
+    return type(row, (torch.autograd.Function,), {"forward": staticmethod(forward), "setup_context": staticmethod(setup_context),
+                                                  "backward": staticmethod(backward), "__doc__": _fn_alias.__doc__})
 
 
 for _r in _ROWS:
