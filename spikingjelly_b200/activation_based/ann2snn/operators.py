@@ -123,14 +123,14 @@ class TDSoftmax(TDModule):
 
 
 class TDLayerNorm(TDModule):
-    def __init__(self, normalized_shape, eps: float = 1e-5, elementwise_affine: bool = True, bias: bool = True, step_mode: str = "m",
-                 device=None, dtype=None) -> None:
+    def __init__(self, normalized_shape, eps: float = 1e-5, elementwise_affine: bool = True, bias: bool = True, device=None, dtype=None,
+                 step_mode: str = "m") -> None:
         super().__init__(step_mode)
         self.norm = nn.LayerNorm(normalized_shape, eps=eps, elementwise_affine=elementwise_affine, bias=bias, device=device, dtype=dtype)
 
     @classmethod
     def from_ann(cls, m: nn.LayerNorm, step_mode: str = "m"):
-        new = cls(m.normalized_shape, m.eps, m.elementwise_affine, m.bias is not None, step_mode)
+        new = cls(m.normalized_shape, m.eps, m.elementwise_affine, m.bias is not None, step_mode=step_mode)
         new.norm = m
         return new
 
@@ -147,8 +147,8 @@ class TDLayerNorm(TDModule):
 
 
 class TDRMSNorm(TDModule):
-    def __init__(self, normalized_shape, eps: Optional[float] = None, elementwise_affine: bool = True, step_mode: str = "m",
-                 device=None, dtype=None) -> None:
+    def __init__(self, normalized_shape, eps: Optional[float] = None, elementwise_affine: bool = True, device=None, dtype=None,
+                 step_mode: str = "m") -> None:
         super().__init__(step_mode)
         self.normalized_shape = (normalized_shape,) if isinstance(normalized_shape, int) else tuple(normalized_shape)
         self.eps = eps
@@ -156,7 +156,7 @@ class TDRMSNorm(TDModule):
 
     @classmethod
     def from_ann(cls, m, step_mode: str = "m"):
-        new = cls(m.normalized_shape, getattr(m, "eps", None), getattr(m, "weight", None) is not None, step_mode)
+        new = cls(m.normalized_shape, getattr(m, "eps", None), getattr(m, "weight", None) is not None, step_mode=step_mode)
         if getattr(m, "weight", None) is not None:
             new.weight = m.weight
         return new
@@ -186,7 +186,7 @@ class TDSiLU(TDModule):
 class TDLinear(TDModule):
     """``y_t = W x_t`` (+ ``b`` on the first step only: the bias belongs to the accumulated output once)."""
 
-    def __init__(self, in_features: int, out_features: int, bias: bool = True, step_mode: str = "m", device=None, dtype=None) -> None:
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype=None, step_mode: str = "m") -> None:
         super().__init__(step_mode)
         self.in_features, self.out_features = in_features, out_features
         self.weight = nn.Parameter(torch.empty(out_features, in_features, device=device, dtype=dtype))
@@ -235,7 +235,7 @@ class TDLinear(TDModule):
 
 class TDConv2d(TDModule):
     def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, groups=1, bias=True,
-                 padding_mode="zeros", step_mode: str = "m", device=None, dtype=None) -> None:
+                 padding_mode="zeros", device=None, dtype=None, step_mode: str = "m") -> None:
         super().__init__(step_mode)
         self.conv = nn.Conv2d(in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias, padding_mode,
                               device=device, dtype=dtype)
@@ -263,7 +263,7 @@ class SNNMatrixOperator(TDModule):
     """``A @ B`` of two activation sequences (both accumulate): ``y_t = A_cum B_cum - (previous)``.
     ``transpose_b`` contracts with ``B^T`` (attention scores)."""
 
-    def __init__(self, transpose_b: bool = False, scale: Optional[float] = None, step_mode: str = "m") -> None:
+    def __init__(self, step_mode: str = "m", transpose_b: bool = False, scale: Optional[float] = None) -> None:
         super().__init__(step_mode)
         self.transpose_b, self.scale = transpose_b, scale
 
@@ -280,24 +280,25 @@ class SNNElementWiseProduct(TDModule):
 class TDScaledDotProductAttention(TDModule):
     """``softmax(Q K^T / sqrt(d) + mask) V`` on accumulated Q, K, V (``[..., L, E]``)."""
 
-    def __init__(self, dropout_p: float = 0.0, is_causal: bool = False, scale: Optional[float] = None, step_mode: str = "m") -> None:
+    def __init__(self, is_causal: bool = False, scale: Optional[float] = None, step_mode: str = "m", dropout_p: float = 0.0) -> None:
         super().__init__(step_mode)
         if dropout_p != 0.0:
             raise ValueError("TDScaledDotProductAttention is deterministic: dropout_p must be 0.")
         self.is_causal, self.scale = is_causal, scale
         self.attn_mask = None
 
-    def ann_forward(self, q, k, v):
-        mask = self.attn_mask
+    def ann_forward(self, query, key, value, attn_mask: Optional[torch.Tensor] = None):
+        q, k, v = query, key, value
+        mask = self.attn_mask if attn_mask is None else attn_mask
         if mask is not None and mask.dim() == q.dim() and mask.shape[0] not in (1, q.shape[0]) and q.shape[0] % mask.shape[0] == 0:
             # a whole sequence is evaluated with time folded into the batch (time-major): the per-sample mask repeats
             mask = mask.repeat(q.shape[0] // mask.shape[0], *([1] * (mask.dim() - 1)))
         return F.scaled_dot_product_attention(q, k, v, attn_mask=mask, is_causal=self.is_causal and mask is None, scale=self.scale)
 
-    def forward(self, q, k, v, attn_mask: Optional[torch.Tensor] = None):
+    def forward(self, query, key, value, attn_mask: Optional[torch.Tensor] = None):
         self.attn_mask = attn_mask
         try:
-            return super().forward(q, k, v)
+            return super().forward(query, key, value)
         finally:
             self.attn_mask = None
 
@@ -309,9 +310,11 @@ class TDMultiheadAttention(TDModule):
     ``need_weights=False``."""
     time_batched = False
 
-    def __init__(self, embed_dim: int, num_heads: int, bias: bool = True, batch_first: bool = False, step_mode: str = "m",
-                 device=None, dtype=None) -> None:
+    def __init__(self, embed_dim: int, num_heads: int, dropout: float = 0.0, bias: bool = True, batch_first: bool = False, device=None,
+                 dtype=None, step_mode: str = "m") -> None:
         super().__init__(step_mode)
+        if dropout != 0.0:
+            raise ValueError("TDMultiheadAttention is deterministic: dropout must be 0.")
         self.mha = nn.MultiheadAttention(embed_dim, num_heads, bias=bias, batch_first=batch_first, device=device, dtype=dtype)
 
     @classmethod
@@ -323,8 +326,11 @@ class TDMultiheadAttention(TDModule):
         new.mha = m
         return new
 
-    def ann_forward(self, q, k, v, **kwargs):
-        return self.mha(q, k, v, need_weights=False, **kwargs)[0]
+    def ann_forward(self, query, key, value, key_padding_mask=None, need_weights: bool = False, attn_mask=None,
+                    average_attn_weights: bool = True, is_causal: bool = False):
+        if need_weights:
+            raise ValueError("TDMultiheadAttention returns no attention weights: need_weights must be False.")
+        return self.mha(query, key, value, key_padding_mask=key_padding_mask, need_weights=False, attn_mask=attn_mask, is_causal=is_causal)[0]
 
     def forward(self, query, key=None, value=None, **kwargs):
         key = query if key is None else key

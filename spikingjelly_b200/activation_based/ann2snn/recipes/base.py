@@ -22,22 +22,34 @@ def replace_submodule(fx_model: fx.GraphModule, target: str, module: nn.Module) 
     setattr(owner, leaf, module)
 
 
-def _pass_through(self, converter, graph_or_module):
-    return graph_or_module
-
-
 class FXConversionRecipe:
-    """Base of the graph recipes.  ``converter`` is the running converter (``converter.device`` is where the result goes)."""
+    """Base of the graph recipes.  ``converter`` is the running converter (``converter.device`` is where the result goes).
+    Every stage returns what it was given unless a recipe overrides it."""
 
     def validate(self, converter) -> None:
         """Check the recipe's own settings; raise on a contradiction."""
 
-    before_trace = _pass_through        # (converter, ann) -> ann            e.g. switch to eval mode
-    after_trace = _pass_through         # (converter, graph) -> graph        e.g. fold batch norms
-    insert_observers = _pass_through    # (converter, graph) -> graph
-    calibrate = _pass_through           # (converter, graph) -> graph        run the calibration data
-    replace = _pass_through             # (converter, graph) -> graph        put the spiking modules in
-    finalize = _pass_through            # (converter, graph) -> nn.Module
+    def before_trace(self, converter, ann: nn.Module) -> nn.Module:
+        """Prepare the ANN for tracing, e.g. switch to eval mode."""
+        return ann
+
+    def after_trace(self, converter, fx_model: fx.GraphModule) -> fx.GraphModule:
+        """Clean the traced graph, e.g. fold batch norms."""
+        return fx_model
+
+    def insert_observers(self, converter, fx_model: fx.GraphModule) -> fx.GraphModule:
+        return fx_model
+
+    def calibrate(self, converter, fx_model: fx.GraphModule) -> fx.GraphModule:
+        """Run the calibration data through the observed graph."""
+        return fx_model
+
+    def replace(self, converter, fx_model: fx.GraphModule) -> fx.GraphModule:
+        """Put the spiking modules in."""
+        return fx_model
+
+    def finalize(self, converter, fx_model: fx.GraphModule) -> nn.Module:
+        return fx_model
 
     def run_graph_stages(self, converter, graph: fx.GraphModule) -> nn.Module:
         """All stages that take the traced graph, in order."""
@@ -56,4 +68,6 @@ class ModuleConversionRecipe:
     def validate(self, converter) -> None:
         """Check the recipe's own settings; raise on a contradiction."""
 
-    convert_module = _pass_through      # (converter, ann) -> converted module
+    def convert_module(self, converter, ann: nn.Module) -> nn.Module:
+        """The converted module; the base class returns ``ann`` unchanged."""
+        return ann

@@ -6,6 +6,8 @@ from __future__ import annotations
 
 import operator
 
+from typing import Optional
+
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
@@ -31,11 +33,17 @@ _FUNCTION_MODULES = {F.gelu: lambda node: TDGELU(node.kwargs.get("approximate", 
 
 
 class TransformerTDEquivalentRecipe(FXConversionRecipe):
-    """``step_mode``: mode given to the created operators.  Unsupported non-linear modules raise
-    (``strict=True``, default) or are left untouched (which breaks exactness)."""
+    """``time_steps``: optional number of steps the converted model is meant to run (recorded on it as ``time_steps``; the
+    operators themselves work for any length).  ``step_mode``: mode given to the created operators.  Unsupported non-linear
+    modules raise (``strict=True``, default) or are left untouched (which breaks exactness)."""
 
-    def __init__(self, step_mode: str = "m", strict: bool = True) -> None:
-        self.step_mode, self.strict = step_mode, strict
+    def __init__(self, time_steps: Optional[int] = None, step_mode: str = "m", strict: bool = True) -> None:
+        self.time_steps, self.step_mode, self.strict = time_steps, step_mode, strict
+
+    def validate(self, converter) -> None:
+        t = self.time_steps
+        if t is not None and (not isinstance(t, int) or isinstance(t, bool) or t <= 0):
+            raise ValueError("time_steps must be a positive integer when set.")
 
     def before_trace(self, converter, ann):
         ann.eval()

@@ -122,11 +122,24 @@ def sigmoid(y: Optional[str], x: str, alpha: float, dtype: str) -> str:
 
 
 def _surrogate_backward(formula):
-    """``formula(v, params...)`` gives the fp32 C expression of g'(v); the builder adapts it to the two dtypes."""
-    def build(y: str, x: str, *params_and_dtype) -> str:
-        *params, dtype = params_and_dtype
+    """``formula(v, params...)`` gives the fp32 C expression of g'(v); the builder adapts it to the two dtypes.  The built
+    function is ``f(y, x, <params...>, dtype)``; parameters and ``dtype`` may also be given by keyword (their names are the
+    formula's argument names)."""
+    import inspect
+    names = list(inspect.signature(formula).parameters)[1:]
+
+    def build(y: str, x: str, *args, **kwargs) -> str:
+        bound = dict(zip(names + ["dtype"], args))
+        for k, v in kwargs.items():
+            if k not in names + ["dtype"] or k in bound:
+                raise TypeError(f"unexpected or repeated argument {k!r}; expected {names + ['dtype']}")
+            bound[k] = v
+        missing = [n for n in names + ["dtype"] if n not in bound]
+        if missing or len(args) > len(names) + 1:
+            raise TypeError(f"expected (y, x, {', '.join(names)}, dtype); missing {missing}")
+        dtype = bound["dtype"]
         _check(dtype)
-        lits = [f"{float(p)!r}f" for p in params]
+        lits = [f"{float(bound[n])!r}f" for n in names]
         if dtype == "float":
             return f"const float {y} = {formula(x, *lits)};"
         lo, hi = f"{y}_lo", f"{y}_hi"
@@ -137,18 +150,18 @@ def _surrogate_backward(formula):
 
 
 sigmoid_backward = _surrogate_backward(
-    lambda v, a: f"(1.0f - 1.0f / (1.0f + expf(-{a} * {v}))) * (1.0f / (1.0f + expf(-{a} * {v}))) * {a}")
+    lambda v, alpha: f"(1.0f - 1.0f / (1.0f + expf(-{alpha} * {v}))) * (1.0f / (1.0f + expf(-{alpha} * {v}))) * {alpha}")
 atan_backward = _surrogate_backward(
-    lambda v, a: f"{a} * 0.5f / (1.0f + (1.5707963267948966f * {a} * {v}) * (1.5707963267948966f * {a} * {v}))")
+    lambda v, alpha: f"{alpha} * 0.5f / (1.0f + (1.5707963267948966f * {alpha} * {v}) * (1.5707963267948966f * {alpha} * {v}))")
 piecewise_leaky_relu_backward = _surrogate_backward(
     lambda v, w, c: f"(fabsf({v}) > {w} ? {c} : 1.0f / {w})")
 s2nn_backward = _surrogate_backward(
-    lambda v, a, b: f"({v} < 0.0f ? {a} * (1.0f / (1.0f + expf(-{a} * {v}))) * (1.0f - 1.0f / (1.0f + expf(-{a} * {v}))) : {b} / ({v} + 1.0f))")
+    lambda v, alpha, beta: f"({v} < 0.0f ? {alpha} * (1.0f / (1.0f + expf(-{alpha} * {v}))) * (1.0f - 1.0f / (1.0f + expf(-{alpha} * {v}))) : {beta} / ({v} + 1.0f))")
 q_pseudo_spike_backward = _surrogate_backward(
-    lambda v, a: f"__powf(1.0f + 2.0f / ({a} - 1.0f) * fabsf({v}), -{a})")
+    lambda v, alpha: f"__powf(1.0f + 2.0f / ({alpha} - 1.0f) * fabsf({v}), -{alpha})")
 leaky_k_relu_backward = _surrogate_backward(
     lambda v, leak, k: f"({v} >= 0.0f ? {k} : {leak})")
 fake_numerical_gradient_backward = _surrogate_backward(
-    lambda v, a: f"fminf(({v} >= 0.0f ? 1.0f : -1.0f) / {v}, {a})")
+    lambda v, alpha: f"fminf(({v} >= 0.0f ? 1.0f : -1.0f) / {v}, {alpha})")
 log_tailed_relu_backward = _surrogate_backward(
-    lambda v, a: f"({v} > 1.0f ? 1.0f / {v} : ({v} > 0.0f ? 1.0f : {a}))")
+    lambda v, alpha: f"({v} > 1.0f ? 1.0f / {v} : ({v} > 0.0f ? 1.0f : {alpha}))")

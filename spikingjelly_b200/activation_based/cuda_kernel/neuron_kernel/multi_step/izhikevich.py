@@ -31,7 +31,7 @@ def izhikevich_multi_step(x_seq: torch.Tensor, v_init: torch.Tensor, w_init: tor
         res = seq.run(x_seq, (v_init, w_init), want_state_seqs=True)
         if res is not None and res[2] is not None:
             return res[0], res[2][0], res[2][1]
-    s, _, _, v_seq, w_seq = functional.neuron.izhikevich_multi_step_cupy(x_seq, v_init, w_init, tau, v_threshold, v_reset, v_rest, v_c, a0, tau_w, a,
+    s, _, _, v_seq, w_seq = functional.neuron.izhikevich_multi_step_eager(x_seq, v_init, w_init, tau, v_threshold, v_reset, v_rest, v_c, a0, tau_w, a,
                                                                          b, surrogate_function, detach_reset, store_v_seq=True)
     return s, v_seq, w_seq
 

@@ -30,7 +30,8 @@ __all__ = [
     "if_multi_step_cupy", "lif_multi_step_cupy", "plif_multi_step_cupy", "qif_multi_step_cupy",
     "eif_multi_step_cupy", "if_multi_step_triton", "lif_multi_step_triton", "plif_multi_step_triton",
     "if_multi_step_inductor", "lif_multi_step_inductor", "plif_multi_step_inductor", "if_step_cupy",
-    "lif_step_cupy", "izhikevich_multi_step_cupy", "activation_aware_if_multi_step_triton",
+    "lif_step_cupy", "izhikevich_multi_step_cupy", "izhikevich_multi_step_eager", "activation_aware_if_multi_step_triton",
+    "activation_aware_if_sequence",
     "stbif_single_step_triton", "stbif_multi_step_triton", "ilif_multi_step_triton",
 ]
 
@@ -283,8 +284,8 @@ def lif_step_cuda(x, v, tau, decay_input, v_threshold, v_reset, surrogate_functi
     return s[0], v_next
 
 
-def izhikevich_multi_step_cupy(x_seq, v, w, tau, v_threshold, v_reset, v_rest, v_c, a0, tau_w, a, b,
-                               surrogate_function, detach_reset=False, store_v_seq=False):
+def izhikevich_multi_step_eager(x_seq, v, w, tau, v_threshold, v_reset, v_rest, v_c, a0, tau_w, a, b,
+                                surrogate_function, detach_reset=False, store_v_seq=False):
     """Two-state neuron: runs the eager rule per step on whatever device holds the data."""
     spikes, vs, ws = [], [], []
     for t in range(x_seq.shape[0]):
@@ -298,8 +299,8 @@ def izhikevich_multi_step_cupy(x_seq, v, w, tau, v_threshold, v_reset, v_rest, v
             torch.stack(ws) if store_v_seq else None)
 
 
-def activation_aware_if_multi_step_triton(x_seq, v, v_threshold, v_offset, v_reset, store_v_seq=False):
-    """Inference-only per-channel-threshold IF over a sequence."""
+def activation_aware_if_sequence(x_seq, v, v_threshold, v_offset, v_reset, store_v_seq=False):
+    """Inference-only per-channel-threshold IF over a sequence; ``v_threshold`` / ``v_offset`` broadcast against one step."""
     with torch.no_grad():
         spikes, vs = [], []
         for t in range(x_seq.shape[0]):
@@ -308,6 +309,18 @@ def activation_aware_if_multi_step_triton(x_seq, v, v_threshold, v_offset, v_res
             if store_v_seq:
                 vs.append(v)
         return torch.stack(spikes), v, (torch.stack(vs) if store_v_seq else None)
+
+
+def activation_aware_if_multi_step_triton(x_seq, v, v_threshold, v_offset, channel_size: int, inner_size: int, v_reset, store_v_seq=False):
+    """The reference's calling convention: one step of ``x_seq`` is laid out as ``[outer, channel_size, inner_size]`` (flattened or
+    not) and ``v_threshold`` / ``v_offset`` hold one value per channel (or one value in all)."""
+    step = x_seq.shape[1:]
+    if channel_size * inner_size == 0 or x_seq[0].numel() % (channel_size * inner_size):
+        raise ValueError(f"a step of {x_seq[0].numel()} elements is not a multiple of channel_size * inner_size = {channel_size * inner_size}")
+    per = lambda t: t if not torch.is_tensor(t) or t.numel() == 1 else t.reshape(1, 1, channel_size, 1)          # noqa: E731
+    xs = x_seq.reshape(x_seq.shape[0], -1, channel_size, inner_size)
+    s, v_last, v_seq = activation_aware_if_sequence(xs, v.reshape(xs.shape[1:]), per(v_threshold), per(v_offset), v_reset, store_v_seq)
+    return s.reshape(x_seq.shape), v_last.reshape(step), (None if v_seq is None else v_seq.reshape(x_seq.shape))
 
 
 def ilif_multi_step_triton(x_seq, v, tau, v_threshold, surrogate_function, detach_reset=False, store_v_seq=False):
@@ -332,8 +345,35 @@ def stbif_multi_step_triton(x_seq, q, acc_q, q_threshold, pos_max, neg_min):
 # Names of the reference's GPU paths: all served by the native kernels.
 if_multi_step_cupy = if_multi_step_triton = if_multi_step_inductor = if_multi_step_cuda
 lif_multi_step_cupy = lif_multi_step_triton = lif_multi_step_inductor = lif_multi_step_cuda
-plif_multi_step_cupy = plif_multi_step_triton = plif_multi_step_inductor = plif_multi_step_cuda
-qif_multi_step_cupy = qif_multi_step_cuda
-eif_multi_step_cupy = eif_multi_step_cuda
+
+
+# The remaining back-end names take their arguments in the reference's order (functional/neuron.py:1300-2800 there).
+def plif_multi_step_cupy(x_seq, v, w, decay_input, v_threshold, v_reset, surrogate_function, detach_reset=False, store_v_seq=False):
+    """``w``: the raw learnable parameter; ``1 / tau = sigmoid(w)`` is taken here."""
+    return plif_multi_step_cuda(x_seq, v, w.sigmoid(), decay_input, v_threshold, v_reset, surrogate_function, detach_reset, store_v_seq)
+
+
+plif_multi_step_triton = plif_multi_step_inductor = plif_multi_step_cupy
+
+
+def qif_multi_step_cupy(x_seq, v, tau, v_threshold, v_reset, v_rest, v_c, a0, detach_reset, surrogate_function, store_v_seq=False):
+    return qif_multi_step_cuda(x_seq, v, tau, v_c, a0, v_threshold, v_rest, v_reset, surrogate_function, detach_reset, store_v_seq)
+
+
+def eif_multi_step_cupy(x_seq, v, tau, v_threshold, v_reset, v_rest, theta_rh, delta_t, detach_reset, surrogate_function, store_v_seq=False):
+    return eif_multi_step_cuda(x_seq, v, tau, v_threshold, v_reset, v_rest, theta_rh, delta_t, surrogate_function, detach_reset, store_v_seq)
+
+
+def izhikevich_multi_step_cupy(x_seq, v, w, tau, v_threshold, v_reset, v_rest, a, b, tau_w, v_c, a0, detach_reset, surrogate_function,
+                               store_state_seq=False):
+    """``(spike_seq, v, w, v_seq | None, w_seq | None)``; on a CUDA tensor the sequence runs as one generated kernel."""
+    from ..cuda_kernel.neuron_kernel.multi_step.izhikevich import izhikevich_multi_step
+    if x_seq.is_cuda:
+        s, v_seq, w_seq = izhikevich_multi_step(x_seq, v, w, tau, v_threshold, v_reset, v_rest, a, b, tau_w, v_c, a0, detach_reset, surrogate_function)
+        return s, v_seq[-1], w_seq[-1], (v_seq if store_state_seq else None), (w_seq if store_state_seq else None)
+    return izhikevich_multi_step_eager(x_seq, v, w, tau, v_threshold, v_reset, v_rest, v_c, a0, tau_w, a, b, surrogate_function, detach_reset,
+                                       store_state_seq)
+
+
 if_step_cupy = if_step_cuda
 lif_step_cupy = lif_step_cuda

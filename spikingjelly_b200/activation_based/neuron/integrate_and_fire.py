@@ -181,7 +181,7 @@ class ActivationAwareIFNode(base.MemoryModule):
             raise RuntimeError("ActivationAwareIFNode native backend does not support autograd.")
         th = self._broadcast_parameter(self.v_threshold, x_seq[0], "v_threshold")
         off = self._broadcast_parameter(self.v_offset, x_seq[0], "v_offset")
-        return functional.activation_aware_if_multi_step_triton(x_seq, v, th, off, self.v_reset, store_v_seq)
+        return functional.activation_aware_if_sequence(x_seq, v, th, off, self.v_reset, store_v_seq)
 
     def multi_step_functional_forward(self, inputs, states, **kwargs):
         if self.native:

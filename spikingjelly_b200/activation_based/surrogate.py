@@ -356,8 +356,8 @@ class _PoissonPassFn(torch.autograd.Function):
         pass
 
     @staticmethod
-    def backward(ctx, g):
-        return g
+    def backward(ctx, grad_output):
+        return grad_output
 
 
 class PoissonPass(SurrogateFunctionBase):
@@ -423,10 +423,24 @@ def _fn_alias(row: str):
                                                   "backward": staticmethod(backward), "__doc__": _fn_alias.__doc__})
 
 
+def _backward_fn(row: _Spec):
+    """``<name>_backward(grad_output, x, <params...>) -> (grad_x, None, ...)``; the parameters may be given by position or by the
+    row's parameter names (``alpha=...``)."""
+    def backward(grad_output, x, *args, **kwargs):
+        unknown = set(kwargs) - set(row.params)
+        if unknown or len(args) + len(kwargs) > len(row.params):
+            raise TypeError(f"{row.name}_backward takes (grad_output, x, {', '.join(row.params)}); got unexpected {sorted(unknown) or 'extra positional arguments'}")
+        values = list(args) + [kwargs[n] for n in row.params[len(args):] if n in kwargs]
+        if len(values) != len(row.params):
+            raise TypeError(f"{row.name}_backward is missing {row.params[len(values):]}")
+        return (grad_output * row.grad(x, *values),) + (None,) * len(values)
+    backward.__name__ = backward.__qualname__ = row.name + "_backward"
+    return backward
+
+
 for _r in _ROWS:
     globals()[_r.name] = _fn_alias(_r.name)
-    globals()[_r.name + "_backward"] = (
-        lambda grad_output, x, *p, _row=_r: (grad_output * _row.grad(x, *p),) + (None,) * len(p))
+    globals()[_r.name + "_backward"] = _backward_fn(_r)
 poisson_pass = _PoissonPassFn
 
 

@@ -127,8 +127,19 @@ def _make_bottleneck(sew: bool):
     return Bottleneck
 
 
+def _without_cnf(block):
+    """The plain spiking ResNet blocks have no connect function, and no ``cnf`` parameter in front of ``spiking_neuron``."""
+    class Block(block):
+        def __init__(self, inplanes, planes, stride=1, downsample=None, groups=1, base_width=64, dilation=1, norm_layer=None,
+                     spiking_neuron: Callable = None, **kwargs):
+            kwargs.pop("cnf", None)
+            super().__init__(inplanes, planes, stride, downsample, groups, base_width, dilation, norm_layer, None, spiking_neuron, **kwargs)
+    Block.__name__, Block.__qualname__, Block.__doc__ = block.__name__, block.__qualname__, block.__doc__
+    return Block
+
+
 SEWBasicBlock, SEWBottleneck = _make_basic(True), _make_bottleneck(True)
-SpikingBasicBlock, SpikingBottleneck = _make_basic(False), _make_bottleneck(False)
+SpikingBasicBlock, SpikingBottleneck = _without_cnf(_make_basic(False)), _without_cnf(_make_bottleneck(False))
 
 
 class ResidualSNN(nn.Module):
@@ -179,7 +190,7 @@ class ResidualSNN(nn.Module):
             downsample = nn.Sequential(conv1x1(self.inplanes, planes * block.expansion, stride),
                                        norm_layer(planes * block.expansion))
         stack = [block(self.inplanes, planes, stride, downsample, self.groups, self.base_width, previous_dilation, norm_layer,
-                       cnf, spiking_neuron, **kwargs)]
+                       cnf=cnf, spiking_neuron=spiking_neuron, **kwargs)]
         self.inplanes = planes * block.expansion
         for _ in range(1, blocks):
             stack.append(block(self.inplanes, planes, groups=self.groups, base_width=self.base_width, dilation=self.dilation,

@@ -51,11 +51,11 @@ def _reduce_device() -> torch.device:
     return torch.device("cpu")
 
 
-def reduce_across_processes(val, op=None):
-    """Sum (default) of a scalar / tensor over all ranks; a plain tensor without a process group."""
+def reduce_across_processes(val, op=None, dtype=None):
+    """Sum (default) of a scalar / tensor over all ranks; a plain tensor without a process group.  ``dtype``: dtype of the result."""
     if not is_dist_avail_and_initialized():
-        return torch.as_tensor(val)
-    t = torch.as_tensor(val, device=_reduce_device())
+        return torch.as_tensor(val, dtype=dtype)
+    t = torch.as_tensor(val, dtype=dtype, device=_reduce_device())
     dist.barrier()
     dist.all_reduce(t, op=op if op is not None else dist.ReduceOp.SUM)
     return t

@@ -399,7 +399,27 @@ def configure_snn_pipeline(units: Sequence[nn.Module], example_input: torch.Tens
                                        virtual_pipeline_size, delayed_wgrad, counts, group, loss_fn)
 
 
-def configure_spikformer_pipeline(module: nn.Module, example_input: torch.Tensor, n_microbatches: int, **kwargs) -> SNNPipelineRuntime:
+def _pipeline_arguments(device, n_microbatches, pp_schedule, pp_virtual_stages, pp_layout, pp_delay_wgrad, stage_index, group, kwargs) -> dict:
+    """The reference's argument names (``device, n_microbatches, pp_schedule, pp_virtual_stages, pp_layout, pp_delay_wgrad``) mapped
+    onto :func:`configure_snn_pipeline`'s.  ``(module, example_input, n_microbatches)``, the older positional form, is still read."""
+    if n_microbatches is None and isinstance(device, int) and not isinstance(device, bool):
+        device, n_microbatches = None, device
+    if n_microbatches is None:
+        raise TypeError("n_microbatches is required")
+    out = dict(kwargs)
+    out.setdefault("device", device)
+    out.setdefault("schedule_kind", pp_schedule)
+    out.setdefault("virtual_pipeline_size", pp_virtual_stages)
+    out.setdefault("layout", pp_layout)
+    out.setdefault("delayed_wgrad", pp_delay_wgrad)
+    out.setdefault("stage_index", stage_index)
+    out.setdefault("group", group)
+    return {"n_microbatches": int(n_microbatches), **out}
+
+
+def configure_spikformer_pipeline(module: nn.Module, example_input: torch.Tensor, device=None, n_microbatches: Optional[int] = None,
+                                  pp_schedule: str = "auto", pp_virtual_stages: int = 1, pp_layout=None, pp_delay_wgrad: bool = False,
+                                  stage_index: Optional[int] = None, group=None, **kwargs) -> SNNPipelineRuntime:
     """Units: patch stem, every block, head (features are averaged over the spatial axes before the
     head).  A 4-D ``[N, C, H, W]`` input is repeated over ``module.T`` time-steps by the first stage.
     Micro-batches are cut along the batch axis, so inputs are ``[N, ...]`` (time is added inside)."""
@@ -431,16 +451,20 @@ def configure_spikformer_pipeline(module: nn.Module, example_input: torch.Tensor
     units[-1] = _ToBatchFirst(units[-1])
     kwargs.setdefault("model_family", "spikformer")
     kwargs.setdefault("loss_fn", lambda out, tgt: snn_sequence_cross_entropy(out.transpose(0, 1), tgt))
-    return configure_snn_pipeline(units, example_input, n_microbatches, pre=add_time, glue={len(units) - 1: pool}, **kwargs)
+    a = _pipeline_arguments(device, n_microbatches, pp_schedule, pp_virtual_stages, pp_layout, pp_delay_wgrad, stage_index, group, kwargs)
+    return configure_snn_pipeline(units, example_input, a.pop("n_microbatches"), pre=add_time, glue={len(units) - 1: pool}, **a)
 
 
-def configure_cifar10dvs_vgg_pipeline(module: nn.Module, example_input: torch.Tensor, n_microbatches: int, **kwargs) -> SNNPipelineRuntime:
+def configure_cifar10dvs_vgg_pipeline(module: nn.Module, example_input: torch.Tensor, device=None, n_microbatches: Optional[int] = None,
+                                      pp_schedule: str = "auto", pp_virtual_stages: int = 1, pp_layout=None, pp_delay_wgrad: bool = False,
+                                      stage_index: Optional[int] = None, group=None, **kwargs) -> SNNPipelineRuntime:
     """Units: the children of ``module.features`` and of ``module.classifier`` (flatten in between)."""
     if not (hasattr(module, "features") and hasattr(module, "classifier")):
         raise TypeError("Expected a VGG-like module with features and classifier.")
     feats, cls = list(module.features.children()), list(module.classifier.children())
     kwargs.setdefault("model_family", "cifar10dvs_vgg")
-    return configure_snn_pipeline(feats + cls, example_input, n_microbatches, glue={len(feats): lambda x: torch.flatten(x, 1)}, **kwargs)
+    a = _pipeline_arguments(device, n_microbatches, pp_schedule, pp_virtual_stages, pp_layout, pp_delay_wgrad, stage_index, group, kwargs)
+    return configure_snn_pipeline(feats + cls, example_input, a.pop("n_microbatches"), glue={len(feats): lambda x: torch.flatten(x, 1)}, **a)
 
 
 # ----------------------------------------------------------------------------- memopt per stage

@@ -367,13 +367,18 @@ class _ChannelShardConv(nn.Module):
     channels, consumes the local slice and all-reduces the partial sums."""
     _nd = 2
 
-    def __init__(self, source, group=None, shard: str = "out", gather_output: bool = False):
+    def __init__(self, source, process_group=None, mode: str = "colwise", gather_output: bool = False, *, group=None, shard: Optional[str] = None):
+        """``mode``: ``"colwise"`` (= ``shard="out"``: a slice of the output channels) or ``"rowwise"`` (= ``shard="in"``: a slice of
+        the input channels, partial sums all-reduced).  ``group`` / ``shard`` are the older keyword names of the first two."""
         super().__init__()
+        group = process_group if group is None else group
+        shard = {"colwise": "out", "rowwise": "in"}.get(mode, mode) if shard is None else shard
         if source.groups != 1:
             raise ValueError("channel sharding supports groups == 1 only")
         if shard not in ("out", "in"):
-            raise ValueError(shard)
+            raise ValueError(f"mode must be 'colwise' or 'rowwise', got {mode!r}")
         self.group, self.shard, self.gather_output = group, shard, gather_output
+        self.mode = "colwise" if shard == "out" else "rowwise"
         self.in_channels, self.out_channels = source.in_channels, source.out_channels
         self.kernel_size, self.stride, self.padding, self.dilation = source.kernel_size, source.stride, source.padding, source.dilation
         self.padding_mode = source.padding_mode
@@ -420,8 +425,9 @@ class _ChannelShardBatchNorm(nn.Module):
     """BatchNorm over the local slice of the channels (statistics are per channel, so no communication)."""
     _cls = nn.BatchNorm2d
 
-    def __init__(self, source, group=None):
+    def __init__(self, source, process_group=None, *, group=None):
         super().__init__()
+        group = process_group if group is None else group
         self.group, self.num_features = group, source.num_features
         ws, r = _ws(group), _rank(group)
         n = _even(source.num_features, ws, "num_features")
