@@ -213,3 +213,7 @@ def cupy_spike_convolution_forward(spike: torch.Tensor, weight: torch.Tensor, bi
         raise ValueError(f"expected a 3-, 4- or 5-dimensional spike tensor, got {spike.dim()} dimensions")
     as_arg = lambda v: v if isinstance(v, (int, str)) else tuple(v)          # noqa: E731
     return fn(spike, weight, bias, as_arg(stride), as_arg(padding), as_arg(dilation), groups)
+
+
+#: the reference records here why its inline C++ wrapper failed to build; this package has no such wrapper
+cpp_wrapper_error = None

@@ -36,6 +36,10 @@ __all__ = [
 ]
 
 
+#: what the functional forms accept as ``surrogate_function``
+SurrogateFunction = Callable[[torch.Tensor], torch.Tensor]
+
+
 def voltage_reset(v, spike, v_threshold: float, v_reset: Optional[float], detach_reset: bool):
     """Soft (``v_reset is None``): ``v - s*v_th``; hard: ``s*v_reset + (1-s)*v``."""
     s = spike.detach() if detach_reset else spike

@@ -4,7 +4,7 @@ the loop itself into a CUDA kernel, so the lowering probes answer ``False`` and 
 which is also what the FlexSN module falls back to on the CPU."""
 from __future__ import annotations
 
-from typing import Callable, Tuple
+from typing import Callable, Tuple, Union
 
 import torch
 
@@ -48,3 +48,9 @@ class FlexSNScan:
 
     def __call__(self, core_fn: Callable, num_inputs: int, num_states: int, num_outputs: int, *flat_args, final_state_only: bool = False):
         return (eager_scan_final_state if final_state_only else eager_scan)(core_fn, num_inputs, num_states, num_outputs, *flat_args)
+
+
+flex_sn_scan = FlexSNScan()
+#: ``(shape, dtype)`` or ``(shape, dtype, device)`` of one output of a step, used to build empty outputs for ``T = 0``
+OutputTemplateSpec = Union[Tuple[Tuple[int, ...], torch.dtype], Tuple[Tuple[int, ...], torch.dtype, torch.device]]
+OutputTemplateSpecs = Tuple[OutputTemplateSpec, ...]

@@ -280,3 +280,11 @@ def multistep_plif_mp_forward(x_seq, v_init, r_tau: torch.Tensor, decay_input: b
     return multistep_plif_mp_with_plan(x_seq, v_init, r_tau, plan, decay_input=decay_input, v_threshold=v_threshold,
                                        v_reset=_reset(v_reset, soft_reset), detach_reset=detach_reset,
                                        surrogate_function=_sg_from_id(sg_triton_id, sg_alpha))
+
+
+# longer names of the mixed-precision forms, and the debugging slots the reference's kernels fill with the loop style they
+# chose ("static" / "dynamic"); the CUDA kernels have one loop style, so the slots stay empty
+multistep_if_mixed_precision_forward, multistep_if_mixed_precision_forward_with_plan = multistep_if_mp, multistep_if_mp_with_plan
+multistep_lif_mixed_precision_forward, multistep_lif_mixed_precision_forward_with_plan = multistep_lif_mp, multistep_lif_mp_with_plan
+multistep_plif_mixed_precision_forward, multistep_plif_mixed_precision_forward_with_plan = multistep_plif_mp, multistep_plif_mp_with_plan
+LAST_FORWARD_LOOP_MODE = LAST_BACKWARD_LOOP_MODE = None

@@ -14,6 +14,14 @@ __all__ = ["CIFAR10DVS_CLASS_NAMES", "CIFAR10DVS", "CIFAR10DVSTEBNSplit"]
 
 CIFAR10DVS_CLASS_NAMES = ("airplane", "automobile", "bird", "cat", "deer", "dog", "frog", "horse", "ship", "truck")
 
+# Event type codes and the address layout of the DAVIS-style 32-bit event word (the defaults of the reference's generic AEDAT
+# reader).  The CIFAR10-DVS files themselves come from a DVS128 and are decoded with the 16-bit layout in ``_load_origin_data``.
+EVT_DVS, EVT_APS = 0, 1
+y_mask, y_shift = 0x7FC00000, 22
+x_mask, x_shift = 0x003FF000, 12
+polarity_mask, polarity_shift = 0x800, 11
+valid_mask, valid_shift = 0x80000000, 31
+
 
 def _load_origin_data(file_name: Union[str, Path]) -> dict:
     """AEDAT 2 of the DVS128: skip ``#`` header lines; address bits 1-7 = x, 8-14 = y, bit 0 = polarity; the image

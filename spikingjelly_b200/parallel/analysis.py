@@ -77,3 +77,11 @@ def analyze_snn_distributed_capability(module: nn.Module, tensor_parallel_roots:
         remarks.append("nothing linear-like under the selected roots: no automatic tensor-parallel plan is possible")
     return SNNDistributedAnalysis(stateful, tuple(found["candidate"]), tuple(found["convolution"]), tuple(remarks),
                                   None if tensor_parallel_roots is None else tuple(tensor_parallel_roots))
+
+
+def __getattr__(name: str):
+    # ``LinearLike``: the tuple of shardable linear types, resolved on first use (the conversion toolbox imports this
+    # package, so the tuple cannot be built while this module is being imported)
+    if name == "LinearLike":
+        return linear_like_types()
+    raise AttributeError(name)

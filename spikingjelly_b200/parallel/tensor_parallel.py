@@ -579,3 +579,11 @@ def parallelize_spikformer_patch_stem(module: nn.Module, device_mesh, roots: Seq
     if hasattr(module, "fused"):
         module.fused = False
     return module
+
+
+def __getattr__(name: str):
+    # type tuples the VGG channel-sharding plan matches against, under the reference's names
+    if name in ("Conv2dLike", "BatchNorm2dLike"):
+        from ..activation_based import layer
+        return (nn.Conv2d, layer.Conv2d) if name == "Conv2dLike" else (nn.BatchNorm2d, layer.BatchNorm2d)
+    raise AttributeError(name)
