@@ -310,7 +310,7 @@ class TDMultiheadAttention(TDModule):
     ``need_weights=False``."""
     time_batched = False
 
-    def __init__(self, embed_dim: int, num_heads: int, dropout: float = 0.0, bias: bool = True, batch_first: bool = False, device=None,
+    def __init__(self, embed_dim: int, num_heads: int, dropout: float = 0.0, bias: bool = True, batch_first: bool = True, device=None,
                  dtype=None, step_mode: str = "m") -> None:
         super().__init__(step_mode)
         if dropout != 0.0:

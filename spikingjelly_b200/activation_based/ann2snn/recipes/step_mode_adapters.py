@@ -58,10 +58,12 @@ def _make_step_module(module: nn.Module) -> nn.Module:
     raise TypeError(type(module).__name__)
 
 
-def adapt_step_mode_graph(fx_model: fx.GraphModule, *, context: str = "step-mode backend", wrap_module_types=_RATE_CODING_STATELESS_MODULE_TYPES,
-                          safe_module_types=_RATE_CODING_SAFE_MODULE_TYPES, safe_call_functions=()) -> fx.GraphModule:
-    """Replace, in place, every ``call_module`` target whose type is in ``wrap_module_types`` by its
-    step-mode twin."""
+def adapt_step_mode_graph(fx_model: fx.GraphModule, context: str = "step-mode backend", wrap_module_types=(), safe_module_types=(),
+                          safe_call_functions=()) -> fx.GraphModule:
+    """Replace, in place, every ``call_module`` target whose type is in ``wrap_module_types`` by its step-mode twin.  With no
+    types given, the stateless layers a rate-coded network is made of are wrapped (``_RATE_CODING_STATELESS_MODULE_TYPES``)."""
+    wrap_module_types = tuple(wrap_module_types) or _RATE_CODING_STATELESS_MODULE_TYPES
+    safe_module_types = tuple(safe_module_types) or _RATE_CODING_SAFE_MODULE_TYPES
     modules = dict(fx_model.named_modules())
     seen = {}
     for node in fx_model.graph.nodes:

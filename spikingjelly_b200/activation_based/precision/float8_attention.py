@@ -37,13 +37,13 @@ class TransformerEngineDotProductAttentionAdapter(nn.Module):
         return {"bhsd": lambda x: x, "bshd": lambda x: x.transpose(1, 2), "sbhd": lambda x: x.permute(2, 0, 1, 3)}[self.qkv_format](t)
 
     def forward(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, attn_mask: Optional[torch.Tensor] = None,
-                dropout_p: Optional[float] = None, is_causal: bool = False, scale: Optional[float] = None, *, attention_mask=None):
+                dropout_p: float = 0.0, is_causal: bool = False, scale: Optional[float] = None, *, attention_mask=None):
         """The arguments of ``F.scaled_dot_product_attention``.  ``attn_mask`` is used when the adapter was built with
         ``attn_mask_type="arbitrary"``; ``is_causal`` or ``attn_mask_type="causal"`` gives the causal mask; ``dropout_p``, when given,
         must agree with the adapter's own (``attention_dropout`` in training, 0 in evaluation)."""
         attn_mask = attention_mask if attn_mask is None else attn_mask
         expected = self.attention_dropout if self.training else 0.0
-        if dropout_p is not None and abs(dropout_p - expected) > 1e-12:
+        if dropout_p != 0.0 and abs(dropout_p - expected) > 1e-12:      # 0.0 (the default) means: the adapter's own setting
             raise ValueError(f"dropout_p={dropout_p} disagrees with the adapter ({expected} in this mode).")
         q, k, v = (self._to_bhsd(t) for t in (query, key, value))
         for name, t in (("query", q), ("key", k), ("value", v)):

@@ -79,7 +79,7 @@ def triton_compute_dtype_name_to_neuron_dtype_id(compute_dtype_name: str, storag
     return {"fp32": 0, "fp16": 1, "bf16": 2}[name]
 
 
-def resolve_triton_compute_dtype(compute_dtype, storage_dtype) -> str:
+def resolve_triton_compute_dtype(compute_dtype, storage_dtype=None) -> str:
     return normalize_triton_compute_dtype_name(compute_dtype)
 
 
