@@ -218,7 +218,8 @@ class NonSpikingBaseNode(nn.Module, base.MultiStepModule):
     def __init__(self, decode: Optional[str] = None):
         super().__init__()
         self.decode = decode
-        self._step_mode = "m"
+        # no ``_step_mode`` is set: like in the reference, ``hasattr(node, "step_mode")`` is False, so ``set_step_mode(net, "s")`` on
+        # a network that ends in a non-spiking read-out leaves this node alone (it always consumes a whole sequence)
 
     @abstractmethod
     def neuronal_charge(self, x: torch.Tensor):

@@ -47,6 +47,8 @@ class _CubaCharge:
         self.v = torch.full_like(data, fill_value=self.v_reset)
 
 
+# The sequence-only nodes of this file set no ``_step_mode``: as in the reference, ``hasattr(node, "step_mode")`` is False and
+# ``functional.set_step_mode`` passes them by.
 class ILCBaseNode(_Dynamics, nn.Module, base.MultiStepModule):
     """Each action owns ``dec_pop_dim`` neurons; the spikes of step ``t`` are mixed within each
     population by a grouped ``Conv1d`` (``conn``) and added to the input of step ``t + 1``."""
@@ -56,7 +58,6 @@ class ILCBaseNode(_Dynamics, nn.Module, base.MultiStepModule):
         assert isinstance(v_reset, float) or v_reset is None
         assert isinstance(v_threshold, float)
         super().__init__()
-        self._step_mode = "m"
         self.act_dim, self.dec_pop_dim, self.out_pop_dim = act_dim, dec_pop_dim, act_dim * dec_pop_dim
         self.conn = nn.Conv1d(act_dim, self.out_pop_dim, dec_pop_dim, groups=act_dim)
         self.v_threshold, self.v_reset, self.surrogate_function = v_threshold, v_reset, surrogate_function
@@ -153,7 +154,6 @@ class NoisyBaseNode(_Dynamics, nn.Module, base.MultiStepModule):
         assert isinstance(v_reset, float) or v_reset is None
         assert isinstance(v_threshold, float)
         super().__init__()
-        self._step_mode = "m"
         self.num_node, self.is_training, self.T, self.beta = num_node, is_training, T, beta
         self.sigma_v = self.sigma_s = sigma_init / math.sqrt(num_node)
         self.cn_v = self.cn_s = None
@@ -239,7 +239,6 @@ class NoisyNonSpikingBaseNode(nn.Module, base.MultiStepModule):
     def __init__(self, num_node, is_training: bool = True, T: int = 5, sigma_init: float = 0.5, beta: float = 0.0,
                  decode: Optional[str] = None):
         super().__init__()
-        self._step_mode = "m"
         self.num_node, self.is_training, self.T, self.beta, self.decode = num_node, is_training, T, beta, decode
         self.sigma = nn.Parameter(torch.full((num_node,), sigma_init / math.sqrt(num_node), dtype=torch.float))
         self.cn = None
