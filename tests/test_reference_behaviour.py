@@ -110,3 +110,88 @@ def test_neuron_equals_the_reference(name):
         for ta, tb in zip(ya, yb):
             assert ta.shape == tb.shape and torch.allclose(ta, tb, atol=1e-5, rtol=1e-5), (name, mode, float((ta - tb).abs().max()))
         assert torch.allclose(ga, gb, atol=1e-5, rtol=1e-4), (name, mode, "grad", float((ga - gb).abs().max()))
+
+
+LAYER_CASES = {
+    "Conv2d": (dict(in_channels=3, out_channels=4, kernel_size=3, padding=1, step_mode="m"), (5, 2, 3, 8, 8)),
+    "Conv1d": (dict(in_channels=3, out_channels=4, kernel_size=3, step_mode="m"), (5, 2, 3, 8)),
+    "Linear": (dict(in_features=6, out_features=4, step_mode="m"), (5, 2, 6)),
+    "BatchNorm2d": (dict(num_features=3, step_mode="m"), (5, 2, 3, 4, 4)),
+    "BatchNorm1d": (dict(num_features=3, step_mode="m"), (5, 2, 3, 4)),
+    "GroupNorm": (dict(num_groups=1, num_channels=4, step_mode="m"), (5, 2, 4, 3, 3)),
+    "MaxPool2d": (dict(kernel_size=2, step_mode="m"), (5, 2, 3, 4, 4)),
+    "AvgPool2d": (dict(kernel_size=2, step_mode="m"), (5, 2, 3, 4, 4)),
+    "AdaptiveAvgPool2d": (dict(output_size=1, step_mode="m"), (5, 2, 3, 4, 4)),
+    "Flatten": (dict(step_mode="m"), (5, 2, 3, 4)),
+    "Dropout": (dict(p=0.5, step_mode="m"), (5, 2, 16)),
+    "Dropout2d": (dict(p=0.5, step_mode="m"), (5, 2, 4, 3, 3)),
+    "SynapseFilter": (dict(tau=3.0, learnable=True, step_mode="m"), (5, 2, 6)),
+    "VotingLayer": (dict(voting_size=2, step_mode="m"), (5, 2, 8)),
+    "ThresholdDependentBatchNorm2d": (dict(alpha=1.0, v_th=1.0, num_features=3), (5, 2, 3, 4, 4)),
+    "BatchNormThroughTime2d": (dict(T=5, num_features=3, step_mode="m"), (5, 2, 3, 4, 4)),
+    "TemporalEffectiveBatchNorm2d": (dict(T=5, num_features=3), (5, 2, 3, 4, 4)),
+    "WSConv2d": (dict(in_channels=3, out_channels=4, kernel_size=3, step_mode="m"), (5, 2, 3, 6, 6)),
+    "TemporalWiseAttention": (dict(T=5, reduction=1), (5, 2, 3, 4, 4)),
+    "MultiDimensionalAttention": (dict(T=5, C=4, reduction_t=1, reduction_c=1), (5, 2, 4, 3, 3)),
+}
+
+
+@pytest.mark.parametrize("name", sorted(LAYER_CASES))
+def test_layer_equals_the_reference(name):
+    """Same parameters, same input and the same random stream: outputs, input gradient and the state dict after one training
+    forward (running statistics, dropout masks drawn from the same seed) agree."""
+    _packages()
+    from spikingjelly.activation_based import layer as rl
+    from spikingjelly_b200.activation_based import layer as ol
+    kw, shape = LAYER_CASES[name]
+    torch.manual_seed(0)
+    a = getattr(ol, name)(**kw)
+    torch.manual_seed(0)
+    b = getattr(rl, name)(**kw)
+    b.load_state_dict(a.state_dict())
+    x0 = torch.rand(shape)
+    got = []
+    for m in (a, b):
+        m.train()
+        torch.manual_seed(7)
+        x = x0.clone().requires_grad_(True)
+        y = m(x)
+        y.sum().backward()
+        got.append((y.detach(), x.grad, {k: v.clone().float() for k, v in m.state_dict().items()}))
+    (ya, ga, sa), (yb, gb, sb) = got
+    assert torch.allclose(ya, yb, atol=1e-5) and torch.allclose(ga, gb, atol=1e-5), name
+    assert sa.keys() == sb.keys() and all(torch.allclose(sa[k], sb[k], atol=1e-5) for k in sa), name
+
+
+def _surrogate_names():
+    _packages()
+    from spikingjelly.activation_based import surrogate as rsg
+    from spikingjelly_b200.activation_based import surrogate as osg
+    return sorted(n for n in dir(rsg) if n[0].isupper() and inspect.isclass(getattr(rsg, n)) and issubclass(getattr(rsg, n), torch.nn.Module)
+                  and hasattr(osg, n) and "Base" not in n)
+
+
+@pytest.mark.parametrize("name", _surrogate_names() if (REF / "spikingjelly").is_dir() else [])
+def test_surrogate_equals_the_reference(name):
+    """Forward values and gradients on ``[-2, 2]`` in the spiking form and (where one exists) in the primitive form."""
+    _packages()
+    from spikingjelly.activation_based import surrogate as rsg
+    from spikingjelly_b200.activation_based import surrogate as osg
+    make = (lambda mod: getattr(mod, name)(4)) if name == "MultiLevelSpikeCount" else (lambda mod: getattr(mod, name)())
+    x0 = torch.linspace(-2, 2, 101) if name != "PoissonPass" else torch.linspace(0, 1, 101)
+    results = []
+    for mod in (osg, rsg):
+        m, out = make(mod), []
+        for spiking in (True, False):
+            m.spiking = spiking
+            x = x0.clone().requires_grad_(True)
+            torch.manual_seed(3)
+            try:
+                y = m(x)
+                y.sum().backward()
+                out += [y.detach(), x.grad]
+            except NotImplementedError:
+                out += ["no primitive", "no primitive"]
+        results.append(out)
+    for p, q in zip(*results):
+        assert (p == q) if isinstance(p, str) or isinstance(q, str) else torch.allclose(p, q, atol=1e-5, equal_nan=True), name
