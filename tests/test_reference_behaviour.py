@@ -195,3 +195,41 @@ def test_surrogate_equals_the_reference(name):
         results.append(out)
     for p, q in zip(*results):
         assert (p == q) if isinstance(p, str) or isinstance(q, str) else torch.allclose(p, q, atol=1e-5, equal_nan=True), name
+
+
+def test_functional_helpers_quantisers_and_stdp_equal_the_reference():
+    _packages()
+    from spikingjelly.activation_based import functional as rf, learning as rlr, quantize as rq
+    from spikingjelly_b200.activation_based import functional as of, learning as olr, quantize as oq
+    torch.manual_seed(0)
+    s = (torch.rand(4, 10, 6) > 0.6).float()
+    labels, similar = torch.randint(0, 10, (4,)), torch.randint(0, 2, (4, 4)).float()
+
+    def same(fa, fb):
+        torch.manual_seed(1)
+        a = fa()
+        torch.manual_seed(1)
+        b = fb()
+        a, b = (a if isinstance(a, (tuple, list)) else (a,)), (b if isinstance(b, (tuple, list)) else (b,))
+        return len(a) == len(b) and all(torch.allclose(torch.as_tensor(p).float(), torch.as_tensor(q).float(), atol=1e-5) for p, q in zip(a, b))
+    assert same(lambda: of.first_spike_index(s), lambda: rf.first_spike_index(s))
+    assert same(lambda: of.redundant_one_hot(labels, 10, 3), lambda: rf.redundant_one_hot(labels, 10, 3))
+    for kernel, args in (("linear", ()), ("sigmoid", (0.5,)), ("gaussian", (1.5,))):
+        assert same(lambda: of.kernel_dot_product(s[0], s[1], kernel, *args), lambda: rf.kernel_dot_product(s[0], s[1], kernel, *args)), kernel
+        for loss in ("mse", "l1", "bce"):
+            assert same(lambda: of.spike_similar_loss(s, similar, kernel, loss, *args), lambda: rf.spike_similar_loss(s, similar, kernel, loss, *args)), (kernel, loss)
+    out = torch.rand(5, 4, 10)                                       # [T, N, C]
+    assert same(lambda: of.temporal_efficient_training_cross_entropy(out, labels), lambda: rf.temporal_efficient_training_cross_entropy(out, labels))
+    x = torch.randn(50)
+    for name, args in (("round", ()), ("ceil", ()), ("floor", ()), ("clamp", (-1.0, 1.0)), ("step_quantize", (0.25,)), ("k_bit_quantize", (3,)),
+                       ("multi_level_spike_count", (4,))):
+        def run(mod):
+            xi = x.clone().requires_grad_(True)
+            y = getattr(mod, name)(xi, *args)
+            y.sum().backward()
+            return y.detach(), xi.grad
+        assert same(lambda: run(oq), lambda: run(rq)), name
+    fo, fr = torch.nn.Linear(5, 3, bias=False), torch.nn.Linear(5, 3, bias=False)
+    fr.load_state_dict(fo.state_dict())
+    pre, post = (torch.rand(2, 5) > 0.5).float(), (torch.rand(2, 3) > 0.5).float()
+    assert same(lambda: olr.stdp_linear_single_step(fo, pre, post, None, None, 2.0, 2.0), lambda: rlr.stdp_linear_single_step(fr, pre, post, None, None, 2.0, 2.0))
