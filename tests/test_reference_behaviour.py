@@ -233,3 +233,139 @@ def test_functional_helpers_quantisers_and_stdp_equal_the_reference():
     fr.load_state_dict(fo.state_dict())
     pre, post = (torch.rand(2, 5) > 0.5).float(), (torch.rand(2, 3) > 0.5).float()
     assert same(lambda: olr.stdp_linear_single_step(fo, pre, post, None, None, 2.0, 2.0), lambda: rlr.stdp_linear_single_step(fr, pre, post, None, None, 2.0, 2.0))
+
+
+MODEL_CASES = {
+    "spiking_resnet18": ("spiking_resnet", {}, (2, 2, 3, 32, 32), True),
+    "spiking_resnext50_32x4d": ("spiking_resnet", {}, (2, 1, 3, 32, 32), True),
+    "sew_resnet18": ("sew_resnet", {"cnf": "ADD"}, (2, 2, 3, 32, 32), True),
+    "sew_resnet50": ("sew_resnet", {"cnf": "IAND"}, (2, 1, 3, 32, 32), True),
+    "spiking_vgg11_bn": ("spiking_vgg", {}, (2, 1, 3, 32, 32), True),
+    "ottt_spiking_vggws": ("spiking_vggws_ottt", None, (2, 3, 32, 32), False),
+}
+
+
+@pytest.mark.parametrize("name", sorted(MODEL_CASES))
+def test_model_zoo_forward_equals_the_reference_with_shared_weights(name):
+    """Both packages build the same architecture (the reference's state dict loads strictly into it) and give the same output."""
+    import importlib
+    (on, of), (rn, rf) = _packages()
+    from spikingjelly.activation_based import surrogate as rsg
+    from spikingjelly_b200.activation_based import surrogate as osg
+    module, extra, shape, multi = MODEL_CASES[name]
+    nets = []
+    for pkg, n_, sg in (("spikingjelly_b200", on, osg), ("spikingjelly", rn, rsg)):
+        kw = {} if extra is None else dict(spiking_neuron=n_.IFNode, surrogate_function=sg.ATan(), detach_reset=True, **extra)
+        torch.manual_seed(0)
+        nets.append(getattr(importlib.import_module(f"{pkg}.activation_based.model.{module}"), name)(**kw).eval())
+    nets[0].load_state_dict(nets[1].state_dict(), strict=True)
+    torch.manual_seed(1)
+    x, outs = torch.rand(shape), []
+    for net, F_ in zip(nets, (of, rf)):
+        if multi:
+            F_.set_step_mode(net, "m")
+        F_.reset_net(net)
+        with torch.no_grad():
+            outs.append(net(x))
+    assert outs[0].shape == outs[1].shape
+    assert torch.allclose(outs[0], outs[1], atol=1e-4), float((outs[0] - outs[1]).abs().max())
+
+
+def _tensors(y):
+    if torch.is_tensor(y):
+        return [y]
+    return [t for v in y for t in _tensors(v)] if isinstance(y, (tuple, list)) else []
+
+
+def _same(a, b, atol=1e-5):
+    a, b = _tensors(a), _tensors(b)
+    return len(a) == len(b) and all(p.shape == q.shape and torch.allclose(p.float(), q.float(), atol=atol) for p, q in zip(a, b))
+
+
+ENCODER_CASES = {
+    "PeriodicEncoder": dict(spike=(torch.arange(96).reshape(3, 4, 8) % 3 == 0).float()),
+    "LatencyEncoder-linear": dict(T=6, enc_function="linear"), "LatencyEncoder-log": dict(T=6, enc_function="log"),
+    "PoissonEncoder": {}, "WeightedPhaseEncoder": dict(K=4),
+    "PopSpikeEncoderDeterministic": dict(obs_dim=8, pop_dim=3, spike_ts=4, mean_range=(-1, 1), std=0.5),
+    "PopSpikeEncoderRandom": dict(obs_dim=8, pop_dim=3, spike_ts=4, mean_range=(-1, 1), std=0.5),
+    "PopEncoder": dict(obs_dim=8, pop_dim=3, spike_ts=4, mean_range=(-1, 1), std=0.5),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ENCODER_CASES))
+def test_encoder_equals_the_reference(name):
+    _packages()
+    from spikingjelly.activation_based import encoding as renc
+    from spikingjelly_b200.activation_based import encoding as oenc
+    kw, cls = ENCODER_CASES[name], name.split("-")[0]
+    x = torch.rand(4, 8, generator=torch.Generator().manual_seed(0)) * 0.9
+    outs = []
+    for mod in (oenc, renc):
+        torch.manual_seed(0)
+        enc = getattr(mod, cls)(**kw)
+        torch.manual_seed(2)
+        if cls in ("PeriodicEncoder", "LatencyEncoder", "WeightedPhaseEncoder"):      # stateful: encode at the first call, then replay
+            first = kw["spike"] if cls == "PeriodicEncoder" else x
+            ys = [enc(first)] + [enc() for _ in range(6)]
+            enc.reset()
+            ys.append(enc(first))
+        else:
+            ys = [enc(x)]
+        outs.append(ys)
+    assert _same(*outs)
+
+
+@pytest.mark.parametrize("learner,synapse", [("STDPLearner", "linear"), ("STDPLearner", "conv"), ("MSTDPLearner", "linear"), ("MSTDPETLearner", "linear")])
+@pytest.mark.parametrize("step_mode", ["s", "m"])
+def test_learning_rule_equals_the_reference(learner, synapse, step_mode):
+    (on, of), (rn, rf) = _packages()
+    from spikingjelly.activation_based import layer as rlay, learning as rlr
+    from spikingjelly_b200.activation_based import layer as olay, learning as olr
+    extra = {"STDPLearner": {}, "MSTDPLearner": dict(batch_size=2), "MSTDPETLearner": dict(tau_trace=3.0)}[learner]
+    reward = {"STDPLearner": None, "MSTDPLearner": torch.tensor([0.5, -0.3]), "MSTDPETLearner": torch.tensor(0.7)}[learner]
+    results = []
+    for lm, nm, lay in ((olr, on, olay), (rlr, rn, rlay)):
+        torch.manual_seed(0)
+        syn = lay.Linear(6, 4, bias=False, step_mode=step_mode) if synapse == "linear" else lay.Conv2d(2, 3, 3, bias=False, step_mode=step_mode)
+        sn = nm.IFNode(step_mode=step_mode)
+        rule = getattr(lm, learner)(step_mode=step_mode, synapse=syn, sn=sn, tau_pre=2.0, tau_post=2.0, **extra)
+        rule.enable()
+        torch.manual_seed(3)
+        deltas = []
+        for _ in range(6):
+            shape = (2, 2, 6, 6) if synapse == "conv" else (6,) if learner == "MSTDPETLearner" else (2, 6)     # the eligibility trace is unbatched
+            x = (torch.rand((4,) + shape if step_mode == "m" else shape) > 0.5).float()
+            sn(syn(x) * 2)
+            try:
+                deltas.append(rule.step(on_grad=False) if reward is None else rule.step(reward, on_grad=False))
+            except Exception as exc:                                  # both arms have to refuse the same configurations
+                deltas.append(type(exc).__name__)
+        results.append(deltas)
+    assert step_mode == "m" or any(torch.is_tensor(d) and float(d.abs().sum()) > 0 for d in results[0]), "the case never produced a weight update"
+    for p, q in zip(*results):
+        assert (p == q) if isinstance(p, str) or isinstance(q, str) else _same(p, q), (learner, synapse, step_mode)
+
+
+RNN_CASES = {
+    "SpikingLSTM": dict(input_size=5, hidden_size=7, num_layers=2), "SpikingGRU": dict(input_size=5, hidden_size=7, num_layers=1, bidirectional=True),
+    "SpikingVanillaRNN": dict(input_size=5, hidden_size=7, num_layers=2, bidirectional=True), "SpikingLSTMCell": dict(input_size=5, hidden_size=7),
+    "SpikingGRUCell": dict(input_size=5, hidden_size=7), "SpikingVanillaRNNCell": dict(input_size=5, hidden_size=7),
+}
+
+
+@pytest.mark.parametrize("name", sorted(RNN_CASES))
+def test_rnn_equals_the_reference(name):
+    _packages()
+    from spikingjelly.activation_based import rnn as rrnn
+    from spikingjelly_b200.activation_based import rnn as ornn
+    torch.manual_seed(0)
+    ours, ref = getattr(ornn, name)(**RNN_CASES[name]), getattr(rrnn, name)(**RNN_CASES[name])
+    ref.load_state_dict(ours.state_dict(), strict=True)
+    x = torch.rand(2, 5) if name.endswith("Cell") else torch.rand(3, 2, 5)
+    grads = []
+    for m in (ours, ref):
+        xi = x.clone().requires_grad_(True)
+        y = m(xi)
+        sum(t.sum() for t in _tensors(y)).backward()
+        grads.append((y, xi.grad, [p.grad for p in m.parameters()]))
+    assert _same(grads[0], grads[1], atol=1e-4)
