@@ -48,9 +48,10 @@ class ComputeEnergyReport:
     energy_total_pj: float
     energy_mac_pj: float
     energy_ac_pj: float
-    breakdown_pj: Dict[str, float]
+    breakdown_pj: Dict[str, float]              # {"mac_pj", "ac_pj"}
     counts: Dict[str, int]
     warnings: List[str]
+    per_module_pj: Dict[str, float] = field(default_factory=dict, compare=False)     # energy by module scope ("Global" = all)
 
 
 class ComputeEnergyProfiler:
@@ -82,9 +83,15 @@ class ComputeEnergyProfiler:
             per_module[scope] = sum(self.mac_counter.records[scope].values()) * cost.e_mac_pj + \
                 sum(self.ac_counter.records[scope].values()) * cost.e_ac_pj
         notes = []
-        if mac == 0 and ac == 0:
-            notes.append("No countable operation was executed inside the profiler context.")
-        rep = ComputeEnergyReport(e_mac + e_ac, e_mac, e_ac, per_module, {"mac": mac, "ac": ac, "synop": synop, "flop": flop}, notes)
+        counters = (self.mac_counter, self.ac_counter, self.synop_counter, self.flop_counter)
+        if not any(c.get_counts().get("Global") for c in counters):
+            message = ("ComputeEnergyProfiler did not match any supported operators. "
+                       "The model may not contain supported operators for this estimator.")
+            if self.config.strict:
+                raise RuntimeError(message)
+            notes.append(message)
+        rep = ComputeEnergyReport(e_mac + e_ac, e_mac, e_ac, {"mac_pj": e_mac, "ac_pj": e_ac},
+                                  {"mac": mac, "ac": ac, "synop": synop, "flop": flop}, notes, per_module)
         logger.info("compute_energy_summary total_pj=%.3f mac=%s ac=%s synop=%s flop=%s", rep.energy_total_pj, mac, ac, synop, flop)
         return rep
 

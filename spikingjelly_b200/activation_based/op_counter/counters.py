@@ -317,17 +317,79 @@ def _io_bytes(args, kwargs, out):
     return sum(_bytes(t) for t in flat_in) + sum(_bytes(t) for t in outs)
 
 
+def _first_and_out(args, kwargs, out):
+    return _bytes(args[0]) + _bytes(out)
+
+
+def _two_and_out(args, kwargs, out):
+    return _bytes(args[0]) + _bytes(args[1] if len(args) > 1 else None) + _bytes(out)
+
+
+def _biased_product_bytes(args, kwargs, out):
+    """``beta * bias + a @ b``: the bias is read only when ``beta`` is not zero."""
+    return sum(_bytes(t) for t in args[1:3]) + _bytes(out) + (_bytes(args[0]) if kwargs.get("beta", 1.0) != 0 else 0)
+
+
+def _convolution_bytes(args, kwargs, out):
+    return sum(_bytes(t) for t in args[:3]) + _bytes(out)
+
+
+def _convolution_backward_bytes(args, kwargs, out):
+    """The gradient of the output is read once; each requested gradient reads its other operand and writes itself."""
+    grad_out, x, w, want = args[0], args[1], args[2], args[10]
+    total = _bytes(grad_out)
+    if want[0]:
+        total += _bytes(w) + _bytes(out[0])
+    if want[1]:
+        total += _bytes(x) + _bytes(out[1])
+    if want[2]:
+        total += _bytes(out[2])
+    return total
+
+
+def _batch_norm_bytes(args, kwargs, out):
+    """Input, affine pair and running pair are read; training writes the output and the two saved statistics, inference the
+    output alone."""
+    return sum(_bytes(t) for t in args[:5]) + (sum(_bytes(t) for t in out[:3]) if args[5] else _bytes(out[0]))
+
+
+def _batch_norm_backward_bytes(args, kwargs, out):
+    """Reads only (the rule set counts no writes for this operator).  Training: the first requested gradient decides what is
+    read (the input gradient needs everything, the scale gradient everything but the scale, the shift gradient the output
+    gradient alone).  Inference: each requested gradient adds the operands the ones before it have not read yet."""
+    grad_out, x, gamma, mean, invstd = args[0], args[1], args[2], args[5], args[6]
+    train, want = args[-3], args[-1]
+    stats = _bytes(x) + _bytes(mean) + _bytes(invstd)
+    if train:
+        if want[0]:
+            return _bytes(grad_out) + stats + _bytes(gamma)
+        return _bytes(grad_out) + stats if want[1] else _bytes(grad_out) if want[2] else 0
+    total = _bytes(grad_out) + _bytes(invstd) + _bytes(gamma) if want[0] else 0
+    if want[1]:
+        total += _bytes(x) + _bytes(mean) + (0 if want[0] else _bytes(invstd) + _bytes(grad_out))
+    if want[2] and not want[0] and not want[1]:
+        total += _bytes(grad_out)
+    return total
+
+
 class MemoryAccessCounter(BaseCounter):
-    """Bytes moved: every tensor argument is read once, every output written once (views and
-    metadata-only operators move nothing)."""
+    """Lower bound of the bytes an operator moves: the operands it has to read plus the results it has to write, per operator
+    (views and metadata-only operators move nothing; ``full_like`` / ``ones_like`` only write; ``stack`` reads every listed
+    tensor).  Same rule set as ``spikingjelly/activation_based/op_counter/memory_access.py:15-411``."""
 
     def default_rules(self):
-        ops = [aten.mm.default, aten.addmm.default, aten.bmm.default, aten.baddbmm.default, aten.convolution.default,
-               aten.convolution_backward.default, aten.native_batch_norm.default, aten.native_batch_norm_backward.default,
-               aten.max_pool2d_with_indices.default, aten.max_pool2d_with_indices_backward.default, aten.avg_pool2d.default,
-               aten.sum.default, aten.sum.dim_IntList, aten.mean.dim, aten.sigmoid_.default, aten.stack.default, aten.clone.default,
-               aten._to_copy.default, aten.full_like.default, aten.ones_like.default, aten.select_backward.default]
-        rules = {op: _io_bytes for op in ops + _ADD_LIKE + _ELEMENTWISE}
+        rules = {op: _two_and_out for op in _ADD_LIKE + _ELEMENTWISE + [aten.mm.default, aten.bmm.default]}
+        rules.update({op: _first_and_out for op in (aten.neg.default, aten.neg_.default, aten.avg_pool2d.default, aten.sum.default,
+                                                    aten.sum.dim_IntList, aten.mean.dim, aten.sigmoid_.default, aten.clone.default,
+                                                    aten._to_copy.default, aten.select_backward.default)})
+        rules.update({
+            aten.addmm.default: _biased_product_bytes, aten.baddbmm.default: _biased_product_bytes,
+            aten.convolution.default: _convolution_bytes, aten.convolution_backward.default: _convolution_backward_bytes,
+            aten.native_batch_norm.default: _batch_norm_bytes, aten.native_batch_norm_backward.default: _batch_norm_backward_bytes,
+            aten.max_pool2d_with_indices.default: lambda a, k, o: _bytes(a[0]) + _bytes(o[0]) + _bytes(o[1]),
+            aten.max_pool2d_with_indices_backward.default: _two_and_out,
+            aten.stack.default: lambda a, k, o: sum(_bytes(t) for t in a[0]) + _bytes(o),
+            aten.full_like.default: lambda a, k, o: _bytes(o), aten.ones_like.default: lambda a, k, o: _bytes(o)})
         rules.update({op: _zero for op in (aten.view.default, aten.empty.memory_format, aten.select.int, aten.detach.default,
                                            aten.t.default, aten.expand.default)})
         for name in ("gemm_16bit", "gemm_fp8", "scan_forward", "scan_backward", "bn_lif_forward", "bn_lif_backward", "ssa_forward",

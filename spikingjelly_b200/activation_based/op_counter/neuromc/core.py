@@ -120,6 +120,7 @@ class _Fragment:
     b_type: int = 0
     t_type: int = 0
     optimizer: Dict[str, bool] = field(default_factory=dict)
+    source: str = "module"                  # "module": seen by a layer hook; "trace": recovered from the operator trace
 
 
 def _layout(x, module) -> Tuple[int, int, int, Tuple[int, ...]]:
@@ -317,10 +318,10 @@ class NeuroMCEnergyProfiler:
             core, name, bits = ("fp_soma" if spikes_in else "ann_fe"), "forward", (1 if spikes_in else 16, 16, 16)
             numel = (a.numel(), module.weight.numel(), b.numel())
         elif role == "grad_input":
-            core, name, bits = ("bp_grad" if spikes_in else "ann_be"), "grad_input", (16, 16, 16)
+            core, name, bits = ("bp_grad" if spikes_in else "ann_be"), "backward.grad_input", (16, 16, 16)
             numel = (a.numel(), module.weight.numel(), b.numel())
         else:
-            core, name, bits = ("wg" if spikes_in else "ann_we"), "grad_weight", (1 if spikes_in else 16, 16, 16)
+            core, name, bits = ("wg" if spikes_in else "ann_we"), "backward.grad_weight", (1 if spikes_in else 16, 16, 16)
             numel = (a.numel() if torch.is_tensor(a) else 0, b.numel(), module.weight.numel())
         kind = "linear" if isinstance(module, nn.Linear) else "conv"
         bt, tt = self._position(stage)
@@ -341,25 +342,39 @@ class NeuroMCEnergyProfiler:
         return _Fragment(stage, phase, f"soma.{phase}", core, "with_sg", dims, (16, 16, out_bits), (a.numel(), 0, b.numel()), 0, b_type=bt, t_type=tt)
 
     def record_optimizer_step(self, stage: str = "optimizer") -> None:
-        """One fragment per parameter tensor of the bound optimizer (SGD, Adam or AdamW)."""
+        """Adam / AdamW: one fragment for the whole update.  SGD: one fragment per (momentum, weight decay, momentum buffer
+        present, vector or matrix) bucket.  ``K`` of the loop dimensions holds the element count of the vector parameters (biases,
+        normalisation scales and shifts), ``FX`` the element count of all others."""
         opt = self._optimizer
         if opt is None:
             return
         kind = type(opt).__name__.lower()
         if kind not in ("sgd", "adam", "adamw"):
             raise ValueError(f"NeuroMC models SGD, Adam and AdamW updates, got {type(opt).__name__}.")
+        buckets: Dict[Tuple[bool, bool, bool, str], int] = defaultdict(int)
         for group in opt.param_groups:
             if kind == "sgd" and (group.get("nesterov") or group.get("dampening", 0) != 0 or group.get("maximize")):
                 raise ValueError("NeuroMC SGD model supports plain / momentum / weight-decay SGD only (no nesterov, dampening or maximize).")
+            momentum, decay = kind == "sgd" and float(group.get("momentum", 0.0)) > 0, kind == "sgd" and float(group.get("weight_decay", 0.0)) > 0
             for p in group["params"]:
                 if p.grad is None:
                     continue
-                shape = tuple(p.shape) + (1,) * (4 - p.dim()) if p.dim() <= 4 else (p.shape[0], prod(p.shape[1:]), 1, 1)
-                dims = _dims(1, 1, shape[1], shape[0], 1, 1, shape[2], shape[3])
-                flags = {"momentum": bool(group.get("momentum", 0)), "weight_decay": bool(group.get("weight_decay", 0)),
-                         "momentum_buffer": "momentum_buffer" in opt.state.get(p, {})}
-                self._fragments.append(_Fragment(stage, "optimizer", kind, "bp_grad_opt", "with_opt", dims, (32, 32, 32),
-                                                 (p.numel(), p.numel(), p.numel()), 0, optimizer=flags))
+                has_buffer = momentum and "momentum_buffer" in opt.state.get(p, {})
+                key = (momentum, decay, has_buffer) if kind == "sgd" else (False, False, False)
+                buckets[key + ("vector" if p.dim() <= 1 else "matrix",)] += int(p.numel())
+        groups: Dict[Tuple[bool, bool, bool], Dict[str, int]] = defaultdict(lambda: {"vector": 0, "matrix": 0})
+        for (m, d, buf, shape), count in buckets.items():
+            groups[(m, d, buf)][shape] += count
+        for (m, d, buf), sizes in groups.items():
+            # SGD keeps vectors and matrices in fragments of their own, Adam puts both in one
+            parts = [(sizes["vector"], sizes["matrix"])] if kind != "sgd" else [(sizes["vector"], 0), (0, sizes["matrix"])]
+            for vec, mat in parts:
+                if vec + mat == 0:
+                    continue
+                dims = _dims(1, 1, 1, vec, 1, 1, 1, mat)
+                dims["K"], dims["FX"] = vec, mat                              # either may be zero
+                self._fragments.append(_Fragment(stage, "optimizer", kind, "bp_grad_opt", "with_opt", dims, (32, 32, 32), (vec, mat, vec + mat), 0,
+                                                 optimizer={"momentum": m, "weight_decay": d, "momentum_buffer": buf}, source="optimizer"))
 
     # -- accounting ---------------------------------------------------------------------------------------------------
     def _charge(self, bits_out, energy_out, level: str, direction: str, bits: int, spec: MemoryInstanceSpec, word: int, read: bool) -> None:
@@ -395,7 +410,11 @@ class NeuroMCEnergyProfiler:
     def _sizes(f: _Fragment) -> Dict[str, int]:
         d = f.loop_dims
         plane = d["OY"] * d["OX"] * d["B"] * d["T"]
-        return {"OYOXKBT": plane * d["K"], "OYOXCBT": plane * d["C"], "KT": d["K"] * d["T"], "CT": d["C"] * d["T"], "P": f.numel[0]}
+        sizes = {"OYOXKBT": plane * d["K"], "OYOXCBT": plane * d["C"], "KT": d["K"] * d["T"], "CT": d["C"] * d["T"]}
+        if f.process_key == "with_opt":
+            # Adam's update model carries a scale and a shift vector of K elements each beside the FX weight elements
+            sizes["P"] = (2 if f.op_name in ("adam", "adamw") else 1) * d["K"] + d["FX"] * d["FY"] * d["C"]
+        return sizes
 
     def _extra_counts(self, f: _Fragment) -> Dict[str, int]:
         c = {"mux": 0, "add": 0, "mul": 0, "comp": 0, "sqrt": 0}
@@ -435,10 +454,10 @@ class NeuroMCEnergyProfiler:
             return bits, energy
         for size_key, word, reg, sram in _EXTRA_VARIABLES.get((f.process_key, f.phase), {}).values():
             total = n[size_key] * word
-            # every intermediate is produced once and consumed once
+            # every intermediate is written to its SRAM once and read back once (the register file is charged for the
+            # contraction operands only)
             for direction, read in (("wl2h", False), ("rh2l", True)):
                 self._charge(bits, energy, "sram", direction, total, inst[sram], word, read)
-                self._charge(bits, energy, "reg", direction, total, inst[reg], word, read)
         return bits, energy
 
     def _unsupported_ops(self) -> List[str]:
@@ -454,6 +473,7 @@ class NeuroMCEnergyProfiler:
         bits_level = defaultdict(lambda: defaultdict(int))
         counts_core, counts_key = defaultdict(lambda: defaultdict(int)), defaultdict(lambda: defaultdict(int))
         prim = defaultdict(int)
+        prim_stage, prim_op = defaultdict(lambda: defaultdict(int)), defaultdict(lambda: defaultdict(int))
         for f in self._fragments:
             mac_e = f.mac_count * MAC_COST_PJ.get(f.core_type, 0.0)
             extra = self._extra_counts(f)
@@ -477,22 +497,34 @@ class NeuroMCEnergyProfiler:
                         level_dir[level][direction] += e
                         bits_level[level][direction] += src_bits[level][direction]
             prim["mac"] += f.mac_count
-            counts_core[f.core_type]["mac"] += f.mac_count
-            counts_key[f.process_key]["mac"] += f.mac_count
+            for table, key in ((counts_core, f.core_type), (counts_key, f.process_key)):
+                table[key]["fragments"] += 1
+                table[key]["mac"] += f.mac_count
             for k, v in extra.items():
                 prim[k] += v
+                prim_stage[f.stage][k] += v
+                prim_op[f.op_name][k] += v
                 counts_core[f.core_type][k] += v
                 counts_key[f.process_key][k] += v
-            rep.mapping_summary.append({"stage": f.stage, "phase": f.phase, "op": f.op_name, "core_type": f.core_type, "process_key": f.process_key,
-                                        "loop_dims": dict(f.loop_dims), "mac_count": f.mac_count, "energy_pj": total})
+            rep.mapping_summary.append({
+                "stage": f.stage, "phase": f.phase, "op_name": f.op_name, "core_type": f.core_type, "process_key": f.process_key,
+                "input_precision_bits": f.bits[0], "weight_precision_bits": f.bits[1], "output_precision_bits": f.bits[2],
+                "loop_dims": dict(f.loop_dims), "b_type": f.b_type, "t_type": f.t_type, "mac_count": f.mac_count, "source": f.source,
+                "optimizer_has_momentum": bool(f.optimizer.get("momentum", False)),
+                "optimizer_has_weight_decay": bool(f.optimizer.get("weight_decay", False)),
+                "optimizer_has_momentum_buffer": bool(f.optimizer.get("momentum_buffer", False)), "energy_pj": total})
         rep.energy_compute_pj = rep.energy_mac_pj + rep.energy_extra_compute_pj
         rep.energy_memory_pj = rep.energy_base_memory_pj + rep.energy_extra_memory_pj
         rep.energy_total_pj = rep.energy_compute_pj + rep.energy_memory_pj
         rep.energy_by_stage, rep.energy_by_op = dict(by_stage), dict(by_op)
         rep.energy_by_core_type, rep.energy_by_process_key = dict(by_core), dict(by_key)
         rep.energy_by_memory_level_dir = {k: dict(v) for k, v in level_dir.items()}
-        rep.memory_bits_by_level = {k: dict(v) for k, v in bits_level.items()}
-        rep.primitive_counts = dict(prim)
+        rep.memory_bits_by_level = {"preset_name": self.memory_config.preset_name,
+                                    "totals": {level: int(sum(d.values())) for level, d in bits_level.items()},
+                                    "by_level_dir": {k: dict(v) for k, v in bits_level.items()}}
+        rep.primitive_counts = {"totals": {k: int(prim[k]) for k in ("mux", "add", "mul", "comp", "sqrt", "mac")},
+                                "by_stage": {k: dict(v) for k, v in prim_stage.items()}, "by_op": {k: dict(v) for k, v in prim_op.items()},
+                                "core_type": self.core_type}
         rep.counts_by_core_type = {k: dict(v) for k, v in counts_core.items()}
         rep.counts_by_process_key = {k: dict(v) for k, v in counts_key.items()}
         return rep

@@ -74,9 +74,9 @@ def test_training_step_report_identities():
     assert {"ann_fe", "fp_soma", "wg", "ann_we", "bp_grad", "bp_grad_opt"} <= set(rep.energy_by_core_type)
     macs_conv1, macs_conv2, macs_fc = 4 * 2 * 3 * 8 * 64 * 9, 4 * 2 * 8 * 16 * 64 * 9, 4 * 2 * 1024 * 10
     # forward + weight gradient for all three, data gradient for all but the first layer
-    assert rep.primitive_counts["mac"] == 2 * (macs_conv1 + macs_conv2 + macs_fc) + macs_conv2 + macs_fc
-    assert rep.memory_bits_by_level["sram"]["rh2l"] > 0 and "dram" not in rep.memory_bits_by_level
-    assert len(rep.mapping_summary) == 7 + 9 + 8 and "total" in rep.summary()
+    assert rep.primitive_counts["totals"]["mac"] == 2 * (macs_conv1 + macs_conv2 + macs_fc) + macs_conv2 + macs_fc
+    assert rep.memory_bits_by_level["by_level_dir"]["sram"]["rh2l"] > 0 and "dram" not in rep.memory_bits_by_level["totals"]
+    assert len(rep.mapping_summary) == 7 + 9 + 2 and "total" in rep.summary()      # the update: one vector and one matrix bucket
     assert not rep.warnings
     assert all(p.grad is None for p in net.parameters())
 
@@ -124,8 +124,9 @@ def test_optimizer_models_and_config_validation():
     x, y = torch.rand(2, 8), torch.rand(2, 4)
     plain = N.estimate_neuromc_runtime_energy(lin, x, target=y, loss_fn=nn.functional.mse_loss, optimizer=torch.optim.SGD(lin.parameters(), lr=0.1))
     adam = N.estimate_neuromc_runtime_energy(lin, x, target=y, loss_fn=nn.functional.mse_loss, optimizer=torch.optim.Adam(lin.parameters()))
-    assert plain.counts_by_process_key["with_opt"] == {"mac": 0, "mux": 0, "add": 36, "mul": 36, "comp": 0, "sqrt": 0}
-    assert adam.counts_by_process_key["with_opt"]["sqrt"] == 36 and adam.energy_by_stage["optimizer"] > plain.energy_by_stage["optimizer"]
+    assert plain.counts_by_process_key["with_opt"] == {"fragments": 2, "mac": 0, "mux": 0, "add": 36, "mul": 36, "comp": 0, "sqrt": 0}
+    # Adam's model carries a scale and a shift vector per vector parameter: 32 weights + 2 * 4
+    assert adam.counts_by_process_key["with_opt"]["sqrt"] == 40 and adam.counts_by_process_key["with_opt"]["fragments"] == 1 and adam.energy_by_stage["optimizer"] > plain.energy_by_stage["optimizer"]
     with pytest.raises(ValueError):
         N.estimate_neuromc_runtime_energy(lin, x, optimizer=torch.optim.SGD(lin.parameters(), lr=0.1))
     with pytest.raises(ValueError):

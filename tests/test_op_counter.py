@@ -58,7 +58,7 @@ def test_energy_estimate_is_dominated_by_accumulates_for_spiking_layers():
     dense = O.estimate_compute_energy(net, torch.rand(2, 2, 8, 8))
     assert dense.counts["mac"] > rep.counts["mac"]            # analog input: the first convolution is all MACs
     cheap = O.estimate_compute_energy(net, spikes, config=O.ComputeEnergyConfig(cost_config=O.ComputeEnergyCostConfig.int8()))
-    assert cheap.energy_total_pj < rep.energy_total_pj and "Global" in rep.breakdown_pj
+    assert cheap.energy_total_pj < rep.energy_total_pj and "Global" in rep.per_module_pj and set(rep.breakdown_pj) == {"mac_pj", "ac_pj"}
 
 
 def test_neuron_state_counter_classifies_state_traffic():

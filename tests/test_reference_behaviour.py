@@ -369,3 +369,98 @@ def test_rnn_equals_the_reference(name):
         sum(t.sum() for t in _tensors(y)).backward()
         grads.append((y, xi.grad, [p.grad for p in m.parameters()]))
     assert _same(grads[0], grads[1], atol=1e-4)
+
+
+def _numbers(report):
+    """Every scalar of a report dataclass, keyed by its path."""
+    import dataclasses
+    out = {}
+
+    def walk(prefix, v):
+        if isinstance(v, dict):
+            for k, u in v.items():
+                walk(f"{prefix}.{k}", u)
+        elif isinstance(v, (list, tuple)):
+            for i, u in enumerate(v):
+                walk(f"{prefix}[{i}]", u)
+        elif isinstance(v, (int, float, str, bool)) or v is None:
+            out[prefix] = v
+    walk("", dataclasses.asdict(report))
+    return out
+
+
+def _close(p, q):
+    return p == q or (isinstance(p, (int, float)) and isinstance(q, (int, float)) and abs(p - q) <= 1e-9 * max(1.0, abs(q)))
+
+
+def _counter_net(lay, nm, pool):
+    torch.manual_seed(0)
+    down = [lay.MaxPool2d(2)] if pool else []
+    return torch.nn.Sequential(lay.Conv2d(3, 8, 3, padding=1, stride=1 if pool else 2), lay.BatchNorm2d(8), nm.LIFNode(), *down, lay.Conv2d(8, 8, 3, padding=1),
+                               nm.IFNode(), lay.Flatten(), lay.Linear(8 * 8 * 8, 10), nm.IFNode())
+
+
+@pytest.mark.parametrize("train", [False, True])
+def test_operation_counters_equal_the_reference(train):
+    """The five dispatch counters of both packages over the same network (forward, and forward + backward)."""
+    (on, of), _ = _packages()
+    from spikingjelly.activation_based import op_counter as rc
+    from spikingjelly_b200.activation_based import layer as olay, op_counter as oc
+    net = _counter_net(olay, on, pool=True)
+    of.set_step_mode(net, "m")
+    x = torch.rand(4, 2, 3, 16, 16)
+    for name in ("FlopCounter", "MACCounter", "ACCounter", "SynOpCounter", "MemoryAccessCounter"):
+        totals = []
+        for c in (oc, rc):
+            of.reset_net(net)
+            net.zero_grad()
+            counter = getattr(c, name)()
+            with c.DispatchCounterMode([counter]):
+                y = net(x)
+                if train:
+                    y.sum().backward()
+            totals.append(counter.get_total())
+        assert totals[0] == totals[1] and totals[0] > 0, (name, totals)
+
+
+@pytest.mark.parametrize("estimator", ["estimate_compute_energy", "estimate_lemaire_energy", "estimate_spikesim_event_energy", "estimate_neuromc_runtime_energy"])
+def test_inference_energy_reports_equal_the_reference(estimator):
+    """Every number of the four energy reports, each package profiling its own copy of the network."""
+    (on, of), (rn, rf) = _packages()
+    from spikingjelly.activation_based import layer as rlay, op_counter as rc
+    from spikingjelly_b200.activation_based import layer as olay, op_counter as oc
+    x, reports = torch.rand(4, 2, 3, 16, 16), []
+    for c, lay, nm, F_ in ((oc, olay, on, of), (rc, rlay, rn, rf)):
+        net = _counter_net(lay, nm, pool=estimator != "estimate_neuromc_runtime_energy").eval()       # the NeuroMC model has no pooling core
+        F_.set_step_mode(net, "m")
+        reports.append(_numbers(getattr(c, estimator)(net, x)))
+    ours, ref = reports
+    extra = {k for k in ours if k not in ref}
+    assert all(k.endswith(".energy_pj") or k.startswith(".per_module_pj") for k in extra), sorted(extra)[:5]     # this package's additions
+    assert len(ref) > 5 and all(_close(ours.get(k), v) for k, v in ref.items()), [(k, ours.get(k), v) for k, v in ref.items() if not _close(ours.get(k), v)][:5]
+
+
+@pytest.mark.parametrize("optimizer", ["sgd", "sgd_momentum", "adam", "adamw"])
+def test_neuromc_training_report_against_the_reference(optimizer):
+    """Forward and optimizer stages are equal.  In the backward stage the reference counts every data- and weight-gradient GEMM
+    twice, once from the layer hook and once more from its operator trace (reported as ``aten.mm.default``); this package
+    counts it once, so its total is the reference's minus that entry."""
+    (on, of), (rn, rf) = _packages()
+    from spikingjelly.activation_based import layer as rlay, op_counter as rc, surrogate as rsg
+    from spikingjelly_b200.activation_based import layer as olay, op_counter as oc, surrogate as osg
+    reports = []
+    for c, lay, nm, sg in ((oc, olay, on, osg), (rc, rlay, rn, rsg)):
+        torch.manual_seed(0)
+        net = torch.nn.Sequential(lay.Linear(8, 6), nm.IFNode(surrogate_function=sg.Sigmoid()), lay.Linear(6, 4), nm.LIFNode(surrogate_function=sg.Sigmoid())).train()
+        opt = {"sgd": lambda p: torch.optim.SGD(p, 0.1), "sgd_momentum": lambda p: torch.optim.SGD(p, 0.1, momentum=0.9, weight_decay=1e-4),
+               "adam": lambda p: torch.optim.Adam(p, 1e-3), "adamw": lambda p: torch.optim.AdamW(p, 1e-3)}[optimizer](net.parameters())
+        torch.manual_seed(1)
+        reports.append(c.estimate_neuromc_runtime_energy(net, torch.rand(2, 8), target=torch.rand(2, 4), loss_fn=torch.nn.functional.mse_loss, optimizer=opt))
+    ours, ref = reports
+    for stage in ("forward", "optimizer"):
+        assert ours.energy_by_stage[stage] == pytest.approx(ref.energy_by_stage[stage], rel=1e-9)
+    assert ours.counts_by_process_key["with_opt"] == ref.counts_by_process_key["with_opt"]
+    assert ours.counts_by_process_key["with_sg"] == ref.counts_by_process_key["with_sg"]
+    recount = ref.energy_by_op["aten.mm.default"]
+    assert recount > 0 and ours.energy_total_pj + recount == pytest.approx(ref.energy_total_pj, rel=1e-9)
+    assert {k: v for k, v in ref.energy_by_op.items() if k != "aten.mm.default"} == pytest.approx(ours.energy_by_op, rel=1e-9)
