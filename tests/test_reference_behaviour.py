@@ -464,3 +464,158 @@ def test_neuromc_training_report_against_the_reference(optimizer):
     recount = ref.energy_by_op["aten.mm.default"]
     assert recount > 0 and ours.energy_total_pj + recount == pytest.approx(ref.energy_total_pj, rel=1e-9)
     assert {k: v for k, v in ref.energy_by_op.items() if k != "aten.mm.default"} == pytest.approx(ours.energy_by_op, rel=1e-9)
+
+
+def _equal(p, q):
+    if isinstance(p, (tuple, list)):
+        return len(p) == len(q) and all(_equal(u, v) for u, v in zip(p, q))
+    if torch.is_tensor(p):
+        return torch.equal(p, q)
+    import numpy as np
+    return np.array_equal(np.asarray(p), np.asarray(q))
+
+
+CONVERSIONS = {
+    "max": ("RateCodingRecipe", dict(mode="max")), "max-unfused": ("RateCodingRecipe", dict(mode="max", fuse_flag=False)),
+    "percentile": ("RateCodingRecipe", dict(mode="99.9%")), "scaled": ("RateCodingRecipe", dict(mode=0.5)),
+    "channel-wise": ("RateCodingRecipe", dict(mode="max", channel_wise=True)), "momentum": ("RateCodingRecipe", dict(mode="max", momentum=0.5)),
+    "pre-spike-maxpool-half-threshold": ("RateCodingRecipe", dict(mode="max", pre_spike_maxpool=True, half_threshold=True)),
+    "local-threshold-balancing": ("LocalThresholdBalancingRecipe", {}),
+}
+
+
+@pytest.mark.parametrize("case", sorted(CONVERSIONS))
+def test_ann2snn_converter_equals_the_reference(case):
+    (_, of), (_, rf) = _packages()
+    from spikingjelly.activation_based import ann2snn as ra
+    from spikingjelly_b200.activation_based import ann2snn as oa
+    nn = torch.nn
+    recipe, kw = CONVERSIONS[case]
+    torch.manual_seed(1)
+    data, x, outs = [(torch.rand(4, 3, 16, 16), torch.zeros(4)) for _ in range(3)], torch.rand(4, 3, 16, 16), []
+    for A, F_ in ((oa, of), (ra, rf)):
+        torch.manual_seed(0)
+        ann = nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.BatchNorm2d(8), nn.ReLU(), nn.AvgPool2d(2), nn.Conv2d(8, 8, 3, padding=1), nn.ReLU(), nn.MaxPool2d(2),
+                            nn.Flatten(), nn.Linear(8 * 4 * 4, 10), nn.ReLU()).eval()
+        snn = A.Converter(getattr(A, recipe)(data, **kw)).convert(ann)
+        F_.reset_net(snn)
+        with torch.no_grad():
+            outs.append(sum(snn(x) for _ in range(8)))
+    assert float(outs[0].abs().sum()) > 0 and torch.allclose(outs[0], outs[1], atol=1e-5), float((outs[0] - outs[1]).abs().max())
+
+
+def test_event_helpers_equal_the_reference(monkeypatch, tmp_path):
+    """Event integration, segment indices, sequence padding, temporal deletion and the raw-file readers on synthetic events."""
+    import importlib
+    import random
+    import types
+
+    import numpy as np
+    _packages()
+    for missing in ("matplotlib", "matplotlib.pyplot", "h5py"):               # imported at the top of the reference's dataset modules
+        try:
+            importlib.import_module(missing)
+        except ImportError:
+            monkeypatch.setitem(sys.modules, missing, types.ModuleType(missing))
+    if not hasattr(sys.modules["h5py"], "File"):
+        sys.modules["h5py"].File = object
+    if not hasattr(sys.modules["matplotlib"], "pyplot"):
+        sys.modules["matplotlib"].pyplot = sys.modules["matplotlib.pyplot"]
+    import spikingjelly.datasets as rd
+    import spikingjelly_b200.datasets as od
+    rng = np.random.default_rng(0)
+    n = 5000
+    ev = {"t": np.sort(rng.integers(0, 100000, n)).astype(np.int64), "x": rng.integers(0, 32, n).astype(np.int64),
+          "y": rng.integers(0, 24, n).astype(np.int64), "p": rng.integers(0, 2, n).astype(np.int64)}
+    raw = bytearray()
+    for i in range(200):                                                     # ATIS record: x, y, polarity bit + 23-bit timestamp
+        x, y, p, ts = int(rng.integers(0, 34)), int(rng.integers(0, 34)), int(rng.integers(0, 2)), i * 37
+        raw += bytes([x, y, (p << 7) | ((ts >> 16) & 0x7F), (ts >> 8) & 0xFF, ts & 0xFF])
+    (tmp_path / "a.bin").write_bytes(raw)
+    np.savez(tmp_path / "f.npz", frames=rng.random((4, 2, 8, 8)).astype(np.float32))
+    seqs = [(torch.rand(t, 2, 4, 4), t % 3) for t in (3, 5, 2)]
+
+    def seeded(fn):
+        torch.manual_seed(0)
+        np.random.seed(0)
+        random.seed(0)
+        return fn()
+    cases = {
+        "segment_to_frame": lambda m: m.integrate_events_segment_to_frame(ev["x"], ev["y"], ev["p"], 24, 32, 10, 3000),
+        "segment_index_time": lambda m: m.cal_fixed_frames_number_segment_index(ev["t"], "time", 7),
+        "segment_index_number": lambda m: m.cal_fixed_frames_number_segment_index(ev["t"], "number", 7),
+        "fixed_frames_time": lambda m: m.integrate_events_by_fixed_frames_number(ev, "time", 7, 24, 32),
+        "fixed_frames_number": lambda m: m.integrate_events_by_fixed_frames_number(ev, "number", 7, 24, 32),
+        "fixed_duration": lambda m: m.integrate_events_by_fixed_duration(ev, 9000, 24, 32),
+        "pad_sequence_collate": lambda m: m.pad_sequence_collate(seqs),
+        "padded_sequence_mask": lambda m: m.padded_sequence_mask(torch.tensor([3, 5, 2])),
+        "random_temporal_delete": lambda m: seeded(lambda: m.random_temporal_delete(torch.arange(40).reshape(10, 4).float(), 6, batch_first=False)),
+        "RandomTemporalDelete": lambda m: seeded(lambda: m.RandomTemporalDelete(6, False)(torch.arange(40).reshape(10, 4).float())),
+        "load_ATIS_bin": lambda m: [m.load_ATIS_bin(str(tmp_path / "a.bin"))[k] for k in ("t", "x", "y", "p")],
+        "load_npz_frames": lambda m: m.load_npz_frames(str(tmp_path / "f.npz")),
+    }
+    for name, fn in cases.items():
+        assert _equal(fn(od), fn(rd)), name
+
+
+class _EncoderBlock(torch.nn.Module):
+    def __init__(self, d=16, h=4):
+        super().__init__()
+        nn = torch.nn
+        self.n1, self.attn, self.n2 = nn.LayerNorm(d), nn.MultiheadAttention(d, h, batch_first=True), nn.LayerNorm(d)
+        self.fc1, self.act, self.fc2 = nn.Linear(d, 32), nn.GELU(), nn.Linear(32, d)
+
+    def forward(self, x):
+        y = self.n1(x)
+        a, _ = self.attn(y, y, y, need_weights=False)      # (the reference's tracer refuses ``attn(...)[0]``)
+        x = x + a
+        return x + self.fc2(self.act(self.fc1(self.n2(x))))
+
+
+class _TinyTransformer(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.emb, self.b1, self.b2, self.head = torch.nn.Linear(8, 16), _EncoderBlock(), _EncoderBlock(), torch.nn.Linear(16, 5)
+
+    def forward(self, x):
+        return self.head(self.b2(self.b1(self.emb(x))).mean(1))
+
+
+TRANSFORMER_RECIPES = {
+    "td-4-steps": ("TransformerTDEquivalentRecipe", False, dict(time_steps=4), 4, 1e-5),
+    "td-any-steps": ("TransformerTDEquivalentRecipe", False, {}, 3, 1e-5),
+    "sta-equivalent": ("STATransformerRecipe", True, dict(time_steps=8, mode="equivalent"), 8, 1e-5),
+    "sta-encoder-mse": ("STATransformerRecipe", True, dict(time_steps=8, mode="spiking_encoder", threshold_mode="mse"), 8, 2e-3),
+    "sta-encoder-max-classifier": ("STATransformerRecipe", True, dict(time_steps=8, mode="spiking_encoder", threshold_mode="max", spike_classifier=True), 8, 2e-3),
+    "sta-encoder-one-batch": ("STATransformerRecipe", True, dict(time_steps=8, mode="spiking_encoder", num_calibration_batches=1), 8, 2e-3),
+    # spiking encoders truncate membrane / threshold: a membrane within rounding of a spike boundary may flip one count between the
+    # two packages, so these cases allow a few elements to differ by a spike's worth
+    "sta-encoder-scaled": ("STATransformerRecipe", True, dict(time_steps=8, mode="spiking_encoder", threshold_mode="max", threshold_scale=0.7), 8, 2e-3),
+    "sta-affine-refused": ("STATransformerRecipe", True, dict(time_steps=8, mode="spiking_affine"), 8, 0.0),
+}
+
+
+@pytest.mark.parametrize("case", sorted(TRANSFORMER_RECIPES))
+def test_transformer_conversion_recipes_equal_the_reference(case):
+    (_, of), (_, rf) = _packages()
+    from spikingjelly.activation_based import ann2snn as ra
+    from spikingjelly_b200.activation_based import ann2snn as oa
+    recipe, calibrated, kw, steps, atol = TRANSFORMER_RECIPES[case]
+    torch.manual_seed(1)
+    data = [(torch.rand(3, 6, 8), 0) for _ in range(2)]
+    x_seq, outs = torch.rand(steps, 3, 6, 8), []
+    for A, F_ in ((oa, of), (ra, rf)):
+        torch.manual_seed(0)
+        ann = _TinyTransformer().eval()
+        try:
+            snn = A.Converter(getattr(A, recipe)(data, **kw) if calibrated else getattr(A, recipe)(**kw)).convert(ann)
+            F_.reset_net(snn)
+            with torch.no_grad():
+                outs.append(snn(x_seq))
+        except ValueError as exc:
+            outs.append(str(exc))
+    if isinstance(outs[1], str):
+        assert outs[0] == outs[1]                                  # both refuse with the same message
+    else:
+        assert outs[0].shape == outs[1].shape and torch.allclose(outs[0], outs[1], atol=atol), float((outs[0] - outs[1]).abs().max())
+        assert float(((outs[0] - outs[1]).abs() > 1e-5).float().mean()) < 0.2
