@@ -619,3 +619,117 @@ def test_transformer_conversion_recipes_equal_the_reference(case):
     else:
         assert outs[0].shape == outs[1].shape and torch.allclose(outs[0], outs[1], atol=atol), float((outs[0] - outs[1]).abs().max())
         assert float(((outs[0] - outs[1]).abs() > 1e-5).float().mean()) < 0.2
+
+
+MORE_LAYER_CASES = {
+    "AdaptiveAvgPool1d": (dict(output_size=2, step_mode="m"), (5, 2, 3, 8)), "AdaptiveAvgPool3d": (dict(output_size=1, step_mode="m"), (5, 2, 3, 4, 4, 4)),
+    "AvgPool1d": (dict(kernel_size=2, step_mode="m"), (5, 2, 3, 8)), "AvgPool3d": (dict(kernel_size=2, step_mode="m"), (5, 2, 3, 4, 4, 4)),
+    "MaxPool1d": (dict(kernel_size=2, step_mode="m"), (5, 2, 3, 8)), "MaxPool3d": (dict(kernel_size=2, step_mode="m"), (5, 2, 3, 4, 4, 4)),
+    "BatchNorm3d": (dict(num_features=3, step_mode="m"), (5, 2, 3, 2, 4, 4)),
+    "BatchNormThroughTime1d": (dict(T=5, num_features=3, step_mode="m"), (5, 2, 3, 4)),
+    "BatchNormThroughTime3d": (dict(T=5, num_features=3, step_mode="m"), (5, 2, 3, 2, 4, 4)),
+    "Conv3d": (dict(in_channels=3, out_channels=4, kernel_size=3, padding=1, step_mode="m"), (5, 2, 3, 4, 4, 4)),
+    "ConvTranspose1d": (dict(in_channels=3, out_channels=4, kernel_size=3, step_mode="m"), (5, 2, 3, 8)),
+    "ConvTranspose2d": (dict(in_channels=3, out_channels=4, kernel_size=3, stride=2, step_mode="m"), (5, 2, 3, 4, 4)),
+    "ConvTranspose3d": (dict(in_channels=3, out_channels=4, kernel_size=3, step_mode="m"), (5, 2, 3, 3, 3, 3)),
+    "Delay": (dict(delay_steps=2, step_mode="m"), (5, 2, 6)), "DropConnectLinear": (dict(in_features=6, out_features=4, p=0.5), (2, 6)),
+    "NeuNorm": (dict(in_channels=3, height=4, width=4, step_mode="m"), (5, 2, 3, 4, 4)), "PrintShapeModule": (dict(), (5, 2, 6)),
+    "TemporalEffectiveBatchNorm1d": (dict(T=5, num_features=3), (5, 2, 3, 4)), "TemporalEffectiveBatchNorm3d": (dict(T=5, num_features=3), (5, 2, 3, 2, 4, 4)),
+    "ThresholdDependentBatchNorm1d": (dict(alpha=1.0, v_th=1.0, num_features=3), (5, 2, 3, 4)),
+    "ThresholdDependentBatchNorm3d": (dict(alpha=1.0, v_th=1.0, num_features=3), (5, 2, 3, 2, 4, 4)),
+    "Upsample": (dict(scale_factor=2.0, mode="nearest", step_mode="m"), (5, 2, 3, 4, 4)),
+}
+LAYER_CASES.update(MORE_LAYER_CASES)          # picked up by test_layer_equals_the_reference's parametrisation below
+
+
+@pytest.mark.parametrize("name", sorted(MORE_LAYER_CASES))
+def test_more_layers_equal_the_reference(name):
+    test_layer_equals_the_reference(name)
+
+
+def _unpool(layer_module, d):
+    nn = torch.nn
+
+    class PoolUnpool(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.pool, self.unpool = getattr(nn, f"MaxPool{d}d")(2, return_indices=True), getattr(layer_module, f"MaxUnpool{d}d")(2, step_mode="m")
+
+        def forward(self, x):
+            y, i = self.pool(x.flatten(0, 1))
+            return self.unpool(y.view(x.shape[:2] + y.shape[1:]), i.view(x.shape[:2] + i.shape[1:]))
+    return PoolUnpool()
+
+
+_SPIKES = lambda *shape: (torch.rand(shape, generator=torch.Generator().manual_seed(3)) > 0.4).float()      # noqa: E731
+_REAL = lambda *shape: torch.rand(shape, generator=torch.Generator().manual_seed(3)) * 2                    # noqa: E731
+BUILT_LAYER_CASES = {
+    "QKAttention-token": (lambda L, N: L.QKAttention(8, 2, "token"), _SPIKES(5, 2, 8, 6)),
+    "QKAttention-channel": (lambda L, N: L.QKAttention(8, 2, "channel"), _SPIKES(5, 2, 8, 6)),
+    "TokenQKAttention": (lambda L, N: L.TokenQKAttention(8, 2), _SPIKES(5, 2, 8, 6)),
+    "ChannelQKAttention": (lambda L, N: L.ChannelQKAttention(8, 2), _SPIKES(5, 2, 8, 6)),
+    "SpikingSelfAttention": (lambda L, N: L.SpikingSelfAttention(8, 2), _SPIKES(5, 2, 8, 6) * 4),
+    "SpikeCountToBinary": (lambda L, N: L.SpikeCountToBinary(3), torch.randint(0, 4, (5, 2, 6), generator=torch.Generator().manual_seed(3)).float()),
+    "SpikeCountToBinary-always": (lambda L, N: L.SpikeCountToBinary(3, True), _SPIKES(5, 2, 6)),
+    "TemporalBinSum": (lambda L, N: L.TemporalBinSum(3), _SPIKES(6, 2, 6)),
+    "TemporalBinSum-always": (lambda L, N: L.TemporalBinSum(2, True), _SPIKES(6, 2, 6)),
+    "ElementWiseRecurrentContainer": (lambda L, N: L.ElementWiseRecurrentContainer(N.IFNode(v_reset=None), lambda x, y: x + y, step_mode="m"), _REAL(5, 2, 6)),
+    "LinearRecurrentContainer": (lambda L, N: L.LinearRecurrentContainer(N.LIFNode(), 6, 6, step_mode="m"), _REAL(5, 2, 6) * 2),
+    "MultiStepContainer": (lambda L, N: L.MultiStepContainer(torch.nn.Linear(6, 4), N.IFNode()), _REAL(5, 2, 6) * 2),
+    "SeqToANNContainer": (lambda L, N: L.SeqToANNContainer(torch.nn.Linear(6, 4), torch.nn.BatchNorm1d(4)), _REAL(5, 2, 6)),
+    "TLastMultiStepContainer": (lambda L, N: L.TLastMultiStepContainer(torch.nn.Linear(6, 6), N.IFNode()), _REAL(2, 6, 5) * 2),
+    "TLastSeqToANNContainer": (lambda L, N: L.TLastSeqToANNContainer(torch.nn.Conv1d(3, 4, 3)), _REAL(2, 3, 8, 5)),
+    "StepModeContainer": (lambda L, N: L.StepModeContainer(False, "m", torch.nn.Linear(6, 4), torch.nn.ReLU()), _REAL(5, 2, 6)),
+    "StepModeContainer-stateful": (lambda L, N: L.StepModeContainer(True, "m", torch.nn.Linear(6, 4), N.IFNode()), _REAL(5, 2, 6) * 2),
+    "MaxUnpool1d": (lambda L, N: _unpool(L, 1), _REAL(5, 2, 3, 8)), "MaxUnpool2d": (lambda L, N: _unpool(L, 2), _REAL(5, 2, 3, 4, 4)),
+    "MaxUnpool3d": (lambda L, N: _unpool(L, 3), _REAL(5, 2, 3, 4, 4, 4)),
+    "OTTTSequential": (lambda L, N: L.OTTTSequential(torch.nn.Linear(6, 4), N.OTTTLIFNode(), torch.nn.Linear(4, 3)), _REAL(2, 6)),
+    "GradwithTrace": (lambda L, N: L.GradwithTrace(torch.nn.Linear(6, 4)), _REAL(2, 6)),
+    "SpikeTraceOp": (lambda L, N: L.SpikeTraceOp(torch.nn.Linear(6, 4)), _REAL(2, 6)),
+}
+
+
+@pytest.mark.parametrize("name", sorted(BUILT_LAYER_CASES))
+def test_attention_slot_container_layers_equal_the_reference(name):
+    (on, _), (rn, _) = _packages()
+    from spikingjelly.activation_based import layer as rl
+    from spikingjelly_b200.activation_based import layer as ol
+    build, x0 = BUILT_LAYER_CASES[name]
+    torch.manual_seed(0)
+    ours = build(ol, on)
+    torch.manual_seed(0)
+    ref = build(rl, rn)
+    ref.load_state_dict(ours.state_dict(), strict=True)
+    results = []
+    for m in (ours, ref):
+        m.train()
+        torch.manual_seed(7)
+        x = x0.clone().requires_grad_(True)
+        trace = torch.rand(x0.shape, generator=torch.Generator().manual_seed(5))
+        y = m([x, trace]) if name in ("GradwithTrace", "SpikeTraceOp") else m(x)         # the OTTT operators take [input, trace]
+        sum(t.sum() for t in _tensors(y)).backward()
+        results.append((y, x.grad, [p.grad for p in m.parameters()]))
+    assert _same(results[0], results[1]), name
+
+
+@pytest.mark.parametrize("kind", ["OutputMonitor", "InputMonitor", "AttributeMonitor", "GradInputMonitor", "GradOutputMonitor"])
+def test_monitor_records_equal_the_reference(kind):
+    (on, of), (rn, rf) = _packages()
+    from spikingjelly.activation_based import layer as rlay, monitor as rmon
+    from spikingjelly_b200.activation_based import layer as olay, monitor as omon
+    x, records = torch.rand(4, 2, 6, generator=torch.Generator().manual_seed(1)) * 2, []
+    for mon, lay, nm, F_ in ((omon, olay, on, of), (rmon, rlay, rn, rf)):
+        torch.manual_seed(0)
+        net = torch.nn.Sequential(lay.Linear(6, 5), nm.IFNode(), lay.Linear(5, 3), nm.LIFNode())
+        F_.set_step_mode(net, "m")
+        if kind == "AttributeMonitor":
+            m = mon.AttributeMonitor("v", False, net, instance=nm.IFNode)
+        else:
+            m = getattr(mon, kind)(net, instance=(nm.IFNode, nm.LIFNode))
+        for _ in range(2):
+            net(x.clone().requires_grad_(True)).sum().backward()
+            F_.reset_net(net)
+        records.append((list(m.monitored_layers), list(m.records), [m[name] for name in m.monitored_layers]))
+        m.remove_hooks()
+    (la, ra, ia), (lb, rb, ib) = records
+    assert la == lb and len(ra) == len(rb) > 0 and _same(ra, rb) and _same(ia, ib)
