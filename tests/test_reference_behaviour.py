@@ -733,3 +733,38 @@ def test_monitor_records_equal_the_reference(kind):
         m.remove_hooks()
     (la, ra, ia), (lb, rb, ib) = records
     assert la == lb and len(ra) == len(rb) > 0 and _same(ra, rb) and _same(ia, ib)
+
+
+def _few_spike_table(N, K=4):
+    powers = [0.5 ** (k + 1) for k in range(K)]
+    return N.FewSpikeTable(powers, powers, powers)
+
+
+TABLE_NEURON_CASES = {
+    "FewSpikeNode": (lambda N: N.FewSpikeNode(_few_spike_table(N)), 1.0, 0.0, True),
+    "HGNode": (lambda N: N.HGNode([_few_spike_table(N), _few_spike_table(N)], [0.5]), 1.0, 0.0, True),
+    "OutlierAwareThresholdNode": (lambda N: N.OutlierAwareThresholdNode(_few_spike_table(N), _few_spike_table(N), 0.6, clamp_value=2.0), 2.0, 0.0, True),
+    "STBIFNeuron-symmetric": (lambda N: N.STBIFNeuron(torch.tensor(0.3), 8, sym=True), 1.0, -0.5, False),
+    "STBIFNeuron-unsigned": (lambda N: N.STBIFNeuron(torch.tensor(0.25), 4, sym=False), 1.0, 0.0, False),
+}
+
+
+@pytest.mark.parametrize("name", sorted(TABLE_NEURON_CASES))
+def test_table_and_conversion_neurons_equal_the_reference(name):
+    """Few-spike table neurons and the ST-BIF conversion neuron: step by step and as a whole sequence."""
+    (on, of), (rn, rf) = _packages()
+    build, scale, shift, differentiable = TABLE_NEURON_CASES[name]
+    x0 = torch.rand(4, 3, 5, generator=torch.Generator().manual_seed(2)) * scale + shift
+    results = []
+    for N, F_ in ((on, of), (rn, rf)):
+        node, per_mode = build(N), []
+        for mode in ("s", "m"):
+            node.step_mode = mode
+            F_.reset_net(node)
+            x = x0.clone().requires_grad_(differentiable)
+            y = torch.stack([_first(node(x[t])) for t in range(x.shape[0])]) if mode == "s" else _first(node(x))
+            if differentiable:
+                y.sum().backward()
+            per_mode.append((y.detach(), x.grad))
+        results.append(per_mode)
+    assert float(results[0][0][0].abs().sum()) > 0 and _same(results[0], results[1]), name
