@@ -768,3 +768,47 @@ def test_table_and_conversion_neurons_equal_the_reference(name):
             per_mode.append((y.detach(), x.grad))
         results.append(per_mode)
     assert float(results[0][0][0].abs().sum()) > 0 and _same(results[0], results[1]), name
+
+
+def _plain(o):
+    """Dataclasses / containers / modules of an analysis or a plan reduced to comparable plain data."""
+    import dataclasses
+    if dataclasses.is_dataclass(o) and not isinstance(o, type):
+        return {f.name: _plain(getattr(o, f.name)) for f in dataclasses.fields(o)}
+    if isinstance(o, dict):
+        return {str(k): _plain(v) for k, v in o.items()}
+    if isinstance(o, (list, tuple, set, frozenset)):
+        return [_plain(v) for v in o]
+    if isinstance(o, (int, float, str, bool)) or o is None:
+        return o
+    return o.__name__ if isinstance(o, type) else type(o).__name__
+
+
+@pytest.mark.parametrize("model", ["mlp", "spiking_vgg11_bn", "sew_resnet18"])
+def test_distributed_analysis_and_plans_equal_the_reference(model):
+    """``analyze`` and ``plan`` are host logic: every field agrees except the free-text notes / rationale (worded here)."""
+    import importlib
+    (on, _), (rn, _) = _packages()
+    from spikingjelly.activation_based import distributed as rd, layer as rlay
+    from spikingjelly_b200.activation_based import distributed as od, layer as olay
+    analyses = []
+    for pkg, lay, nm, D in (("spikingjelly_b200", olay, on, od), ("spikingjelly", rlay, rn, rd)):
+        torch.manual_seed(0)
+        if model == "mlp":
+            net = torch.nn.Sequential(lay.Flatten(), lay.Linear(64, 32), nm.LIFNode(), lay.Linear(32, 10), nm.LIFNode())
+        else:
+            module = importlib.import_module(f"{pkg}.activation_based.model.{'spiking_vgg' if 'vgg' in model else 'sew_resnet'}")
+            net = getattr(module, model)(spiking_neuron=nm.IFNode, **({"cnf": "ADD"} if "sew" in model else {}))
+        analyses.append((D, D.analyze(net)))
+
+    def strip(d):
+        return {k: v for k, v in d.items() if k not in ("notes", "rationale")}
+    assert strip(_plain(analyses[0][1])) == strip(_plain(analyses[1][1]))
+    for mode, topology in (("dp", {"dp": 2}), ("tp", {"tp": 2}), ("fsdp2", {"dp": 2}), ("fsdp2_tp", {"dp": 2, "tp": 2}), ("none", {}), ("pp", {"pp": 2}), ("auto", {"dp": 2})):
+        plans = []
+        for D, analysis in analyses:
+            try:
+                plans.append(strip(_plain(D.plan(analysis=analysis, objective="speed", topology=topology, backend="torch", batch_size=8, model_family=None, mode=mode))))
+            except (NotImplementedError, ValueError) as exc:
+                plans.append(type(exc).__name__)
+        assert plans[0] == plans[1], (model, mode)
