@@ -812,3 +812,31 @@ def test_distributed_analysis_and_plans_equal_the_reference(model):
             except (NotImplementedError, ValueError) as exc:
                 plans.append(type(exc).__name__)
         assert plans[0] == plans[1], (model, mode)
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16", "fp16"])
+def test_precision_api_on_cpu_equals_the_reference(mode):
+    """``prepare_model_for_precision`` on the CPU: same effective mode (fp16 falls back to fp32), same policy, same forward
+    output bit for bit; after ``artifacts.backward`` the parameters agree to the compute dtype's rounding (the surrogate
+    derivative is evaluated in fp32 here and rounded once, the reference rounds after every bf16 operation)."""
+    (on, of), (rn, rf) = _packages()
+    from spikingjelly.activation_based import layer as rlay, precision as rp
+    from spikingjelly_b200.activation_based import layer as olay, precision as op
+    x, results = torch.rand(4, 3, 16, generator=torch.Generator().manual_seed(1)) * 6, []
+    for P, lay, nm, F_ in ((op, olay, on, of), (rp, rlay, rn, rf)):
+        torch.manual_seed(0)
+        net = torch.nn.Sequential(lay.Linear(16, 32), nm.LIFNode(), lay.Linear(32, 8), nm.IFNode())
+        F_.set_step_mode(net, "m")
+        art = P.prepare_model_for_precision(net, torch.device("cpu"), P.PrecisionConfig(mode=mode, strictness="warn", device="cpu"))
+        opt = torch.optim.SGD(art.model.parameters(), 0.1)
+        with art.autocast_context():
+            y = art.model(x)
+        art.backward(y.float().sum(), opt)
+        info = art.describe()
+        results.append((y.detach().float(), [p.detach().clone() for p in art.model.parameters()], art.effective_config.mode, info["policy"],
+                        info["effective_config"], info["fallback_reason"] is None))
+    ours, ref = results
+    assert ours[2:] == ref[2:]
+    assert torch.equal(ours[0], ref[0]) and float(ours[0].sum()) > 0
+    tol = dict(atol=1e-6, rtol=1e-5) if ours[2] == "fp32" else dict(atol=5e-3, rtol=1e-2)
+    assert all(torch.allclose(p, q, **tol) for p, q in zip(ours[1], ref[1]))
