@@ -840,3 +840,43 @@ def test_precision_api_on_cpu_equals_the_reference(mode):
     assert torch.equal(ours[0], ref[0]) and float(ours[0].sum()) > 0
     tol = dict(atol=1e-6, rtol=1e-5) if ours[2] == "fp32" else dict(atol=5e-3, rtol=1e-2)
     assert all(torch.allclose(p, q, **tol) for p, q in zip(ours[1], ref[1]))
+
+
+def test_memopt_compressors_containers_and_pass_equal_the_reference():
+    """Spike compressors (the stored tensor itself, not only the round trip), the gradient-checkpoint containers with and
+    without input compression, and ``memory_optimization`` at levels 0-2 on the CPU (same wrapped module tree, same output)."""
+    import dataclasses
+    (on, of), (rn, rf) = _packages()
+    from spikingjelly.activation_based import layer as rlay, memopt as rm
+    from spikingjelly_b200.activation_based import layer as olay, memopt as om
+    nn = torch.nn
+    spikes = (torch.rand(6, 4, 33, generator=torch.Generator().manual_seed(0)) > 0.6).float()
+    for name in ("NullSpikeCompressor", "BooleanSpikeCompressor", "Uint8SpikeCompressor", "BitSpikeCompressor", "SparseSpikeCompressor"):
+        a, b = getattr(om, name)(), getattr(rm, name)()
+        ca, cb = a.compress(spikes), b.compress(spikes)
+        assert _equal(ca, cb), name
+        assert torch.equal(a.decompress(ca, spikes.shape).float(), spikes) and torch.equal(b.decompress(ca, spikes.shape).float(), spikes), name
+    x = torch.rand(5, 3, 16, generator=torch.Generator().manual_seed(1)) * 4
+    for container, kw in (("GCContainer", {}), ("TCGCContainer", dict(n_chunk=2))):
+        for compressor in (None, "BitSpikeCompressor"):
+            results = []
+            for M, lay, nm, F_ in ((om, olay, on, of), (rm, rlay, rn, rf)):
+                torch.manual_seed(0)
+                inner = getattr(M, container)(getattr(M, compressor)() if compressor else None, lay.Linear(16, 16), nm.LIFNode(), **kw)
+                net = nn.Sequential(lay.Linear(16, 16), nm.IFNode(), inner, lay.Linear(16, 4)).train()
+                F_.set_step_mode(net, "m")
+                xi = x.clone().requires_grad_(True)
+                y = net(xi)
+                y.sum().backward()
+                results.append((y.detach(), xi.grad, [p.grad for p in net.parameters()]))
+            assert _same(results[0], results[1]), (container, compressor)
+    for level in (0, 1, 2):
+        results = []
+        for M, lay, nm, F_ in ((om, olay, on, of), (rm, rlay, rn, rf)):
+            torch.manual_seed(0)
+            net = nn.Sequential(lay.Linear(16, 16), nm.IFNode(), lay.Linear(16, 16), nm.LIFNode(), lay.Linear(16, 4))
+            F_.set_step_mode(net, "m")
+            net, summary = M.memory_optimization(net, (nm.IFNode, nm.LIFNode), dummy_input=(x,), level=level, return_summary=True)
+            F_.reset_net(net)
+            results.append((net(x).detach(), [type(m).__name__ for m in net.modules()], sorted(f.name for f in dataclasses.fields(summary))))
+        assert torch.allclose(results[0][0], results[1][0], atol=1e-5) and results[0][1:] == results[1][1:], level
