@@ -880,3 +880,74 @@ def test_memopt_compressors_containers_and_pass_equal_the_reference():
             F_.reset_net(net)
             results.append((net(x).detach(), [type(m).__name__ for m in net.modules()], sorted(f.name for f in dataclasses.fields(summary))))
         assert torch.allclose(results[0][0], results[1][0], atol=1e-5) and results[0][1:] == results[1][1:], level
+
+
+STEP_FUNCTIONS = ["if_step", "lif_step", "plif_step", "qif_step", "eif_step", "izhikevich_step", "klif_step", "liaf_step", "cuba_lif_step", "ilif_step",
+                  "lif_charge", "voltage_reset", "neunorm_step", "synapse_filter_step", "delay", "delay_step", "stbif_step", "activation_aware_if_step",
+                  "gated_lif_step", "lava_cuba_lif_step", "sliding_psn_step", "masked_psn_step", "mstdpet_reward_step"]
+
+
+def _step_argument(name, surrogate):
+    """A value for a parameter of a functional step, chosen by the parameter's name."""
+    g = torch.Generator().manual_seed(sum(map(ord, name)))
+    tensor = lambda scale=1.0, shift=0.0: torch.rand(3, 5, generator=g) * scale + shift       # noqa: E731
+    table = {
+        "x": lambda: tensor(3.0, -0.5), "v": lambda: tensor(1.0, -0.2), "w": lambda: tensor(0.5), "k": lambda: torch.tensor(1.5), "spike": lambda: (tensor() > 0.5).float(),
+        "current": lambda: tensor(), "current_state": lambda: tensor(), "voltage_state": lambda: tensor(), "state": lambda: tensor(), "out_i": lambda: tensor(),
+        "in_spikes": lambda: (tensor() > 0.5).float(), "weight": lambda: tensor(), "q": lambda: tensor(2.0, -1.0), "acc_q": lambda: torch.zeros(3, 5),
+        "q_threshold": lambda: torch.tensor(0.5), "pos_max": lambda: torch.tensor(3.0), "neg_min": lambda: torch.tensor(-3.0), "v_offset": lambda: tensor(0.2),
+        "alpha": lambda: torch.tensor(0.3), "beta": lambda: torch.tensor(-0.2), "gamma": lambda: torch.tensor(0.1), "linear_decay": lambda: torch.tensor(0.05),
+        "v_subreset": lambda: torch.tensor(0.4), "conduct": lambda: tensor(), "current_decay": lambda: 0.4, "voltage_decay": lambda: 0.3,
+        "tau": lambda: 2.0, "decay_input": lambda: True, "v_threshold": lambda: 1.0, "v_reset": lambda: 0.0, "detach_reset": lambda: False, "surrogate_function": lambda: surrogate,
+        "a0": lambda: 1.0, "v_rest": lambda: 0.0, "v_c": lambda: 0.8, "delta_t": lambda: 1.0, "theta_rh": lambda: 0.8, "tau_w": lambda: 4.0, "a": lambda: 0.5, "b": lambda: 0.2,
+        "scale_reset": lambda: True, "act": lambda: torch.relu, "threshold_related": lambda: True, "momentum": lambda: 0.9, "input_scale": lambda: 0.5,
+        "reciprocal_tau": lambda: 0.25, "x_seq": lambda: torch.rand(6, 3, 5, generator=g), "delay_steps": lambda: 2, "s_scale": lambda: 1.0, "v_threshold_eps": lambda: 0.01,
+        "queue": lambda: (tensor(), tensor()), "bias": lambda: torch.tensor(-0.5), "time_step": lambda: 1, "reward": lambda: 0.7, "eligibility": lambda: tensor(),
+        "trace_e": lambda: tensor(), "tau_trace": lambda: 3.0, "masked_weight": lambda: torch.rand(3, 3, generator=g),
+    }
+    return table[name]()
+
+
+@pytest.mark.parametrize("name", STEP_FUNCTIONS)
+def test_functional_step_equals_the_reference(name):
+    """The pure single-step forms (state in, state out): every returned tensor and the gradient of their sum in the inputs."""
+    _packages()
+    from spikingjelly.activation_based import functional as rf, surrogate as rsg
+    from spikingjelly_b200.activation_based import functional as of, surrogate as osg
+    results = []
+    for F_, sg in ((of, osg), (rf, rsg)):
+        fn = getattr(F_, name)
+        names = list(inspect.signature(getattr(rf, name)).parameters)              # the reference's names: both take them as keywords
+        kw = {}
+        for p in names:
+            if p in ("x", "queue", "weight", "masked_weight") and name in ("sliding_psn_step", "masked_psn_step"):
+                g = torch.Generator().manual_seed(1)
+                kw[p] = {"x": torch.rand(3, 5, generator=g), "queue": tuple(torch.rand(15, generator=g) for _ in range(2)),     # flattened past inputs
+                         "weight": torch.rand(3, generator=g), "masked_weight": torch.rand(4, 4, generator=g)}[p]
+            elif p == "bias" and name in ("sliding_psn_step", "masked_psn_step"):
+                kw[p] = torch.full((1,), -0.5) if name == "sliding_psn_step" else torch.full((4, 1), -0.5)
+            elif p == "time_step" and name == "masked_psn_step":
+                kw[p] = 2
+            elif p == "tau" and name == "gated_lif_step":
+                kw[p] = torch.tensor(0.3)
+            elif p == "v_threshold" and name in ("gated_lif_step", "activation_aware_if_step"):
+                kw[p] = torch.tensor(1.0)
+            elif p in ("current_decay", "voltage_decay") and name == "lava_cuba_lif_step":
+                kw[p] = torch.tensor(0.4)
+            elif p == "k" and name == "masked_psn_step":
+                kw[p] = 3
+            else:
+                kw[p] = _step_argument(p, sg.Sigmoid())
+        leaves = [k for k, v in kw.items() if torch.is_tensor(v) and v.is_floating_point() and v.dim() > 0]
+        for k in leaves:
+            kw[k] = kw[k].clone().requires_grad_(True)
+        try:
+            out = _tensors(fn(**kw))
+            total = sum(t.float().sum() for t in out)
+            grads = torch.autograd.grad(total, [kw[k] for k in leaves], allow_unused=True) if total.requires_grad else ()
+            results.append(([t.detach().float() for t in out], [g for g in grads if g is not None]))
+        except Exception as exc:
+            results.append(type(exc).__name__)
+    assert not isinstance(results[1], str), f"the case does not run in the reference: {results[1]}"
+    assert not isinstance(results[0], str), results[0]
+    assert len(results[1][0]) > 0 and _same(results[0], results[1])
