@@ -198,3 +198,23 @@ def test_lava_and_lynxi_examples_run_up_to_the_vendor_step(tmp_path):
         import lynpy  # noqa: F401
     except ImportError:
         assert res["device"] is None
+
+
+def test_conversion_examples_on_generated_data(tmp_path):
+    """The ANN -> SNN example scripts end to end on generated data: the converted network reaches the source network's accuracy."""
+    from spikingjelly_b200.activation_based.ann2snn.examples import cnn_mnist, imagenet_resnet18_ltb, imagenet_vit_sta, resnet18_cifar10
+    out = cnn_mnist.main(["--synthetic", "--time-steps", "16", "--skip-mode-sweep", "--device", "cpu", "--max-eval-batches", "2", "--output", str(tmp_path / "cnn.json")])
+    assert out["ann_accuracy"] > 0.8 and (tmp_path / "cnn.json").exists()
+    assert all(r["snn_accuracy"] >= out["ann_accuracy"] - 0.1 for r in out["recipes"].values())
+    out = resnet18_cifar10.main(["--synthetic", "--time-steps", "8", "--device", "cpu", "--max-eval-batches", "1"])
+    assert 0.0 <= out["snn_accuracy"] <= 1.0 and "T=8" in out["curve"]
+    out = imagenet_resnet18_ltb.main(["--synthetic", "--time-steps", "2", "--device", "cpu", "--delay-start", "auto", "--recipes", "ltb"])
+    assert out["snn"]["ltb"]["delay_start"] == 17 and "T=2" in out["snn"]["ltb"]
+    out = imagenet_vit_sta.main(["--synthetic", "--time-steps", "4", "--device", "cpu", "--modes", "equivalent"])
+    assert out["snn"]["equivalent"]["top1"] == out["ann_top1"]                 # time-difference operators: exact after every step
+
+
+def test_tempotron_example_learns_generated_digits():
+    from spikingjelly_b200.timing_based.examples import tempotron_mnist
+    history = tempotron_mnist.main(["--synthetic", "--epochs", "1", "-m", "4", "-T", "50", "--device", "cpu"])
+    assert history[-1]["test_accuracy"] > 0.9
